@@ -1,0 +1,110 @@
+"""Pins the CPU oracle against fixtures produced by the reference itself (CPU only)."""
+
+import hashlib
+
+import numpy as np
+import pytest
+
+import oracle
+from tests.golden_io import digests, quant_cases, rotation_cases
+
+CASES = quant_cases()
+
+
+@pytest.mark.parametrize("case", CASES, ids=[c.name for c in CASES])
+def test_quantizer_matches_reference(case):
+    x = case.x_f32()
+    p = oracle.quantize(x, case.mode, stats=True, nibbles=True)
+    d = case.data
+    assert np.float32(p.global_scale).view(np.uint32) == d["global_scale"].view(np.uint32)[0]
+    # both candidates, block by block (bit patterns of the fp32 errors decide the selector)
+    assert np.array_equal(p.e2_nibbles, d["e2_nibbles"])
+    assert np.array_equal(p.e0_nibbles, d["e0_nibbles"])
+    assert np.array_equal(p.e2_scales.view(np.uint32), d["e2_scales"].view(np.uint32))
+    assert np.array_equal(p.e0_scales.view(np.uint32), d["e0_scales"].view(np.uint32))
+    assert np.array_equal(p.e2_errors.view(np.uint32), d["e2_errors"].view(np.uint32))
+    assert np.array_equal(p.e0_errors.view(np.uint32), d["e0_errors"].view(np.uint32))
+    # the packed bytes
+    assert np.array_equal(p.format_ids(), d["format_ids"])
+    assert np.array_equal(p.codes, d["codes"])
+    assert np.array_equal(p.scales, d["scales"])
+    assert np.array_equal(p.fmt, d["fmt"])
+    assert np.array_equal(p.selected_scales().view(np.uint32), d["selected_scales"].view(np.uint32))
+
+
+@pytest.mark.parametrize("case", CASES, ids=[c.name for c in CASES])
+def test_dequant_matches_reference(case):
+    p = oracle.quantize(case.x_f32(), case.mode)
+    d = case.data
+    if case.dtype == "bfloat16":
+        got = oracle.dequant(p, "bf16").reshape(d["dequant"].shape)
+        assert np.array_equal(got, d["dequant"])
+    elif case.dtype == "float32":
+        got = oracle.dequant(p, "f32").reshape(d["dequant"].shape)
+        assert np.array_equal(got.view(np.uint32), d["dequant"].view(np.uint32))
+    else:  # float16: the oracle decodes to fp32, the cast is numpy's RNE
+        got = oracle.dequant(p, "f32").astype(np.float16).reshape(d["dequant"].shape)
+        assert np.array_equal(got.view(np.uint16), d["dequant"])
+
+
+def _rotation_keys():
+    return sorted(k[: -len("__x")] for k in rotation_cases() if k.endswith("__x"))
+
+
+@pytest.mark.parametrize("key", _rotation_keys())
+def test_rotation_matches_reference(key):
+    z = rotation_cases()
+    name, tag = key.split("__")
+    size = int(name.split("H")[1].split("_")[0])
+    signs = z.get(f"{name}__signs")
+    x, y = z[key + "__x"], z[key + "__y"]
+    if tag.startswith("bf16"):
+        got = oracle.fwht(oracle.bf16_bits_to_f32(x), size, signs=signs, bf16_stages=True)
+        assert np.array_equal(oracle.f32_to_bf16_bits(got), y)
+    else:
+        got = oracle.fwht(x, size, signs=signs)
+        assert np.array_equal(got.view(np.uint32), y.view(np.uint32))
+
+
+def test_zero_tensor_is_exact():
+    # reference: tests/test_quant_core.py:168-173
+    for mode in ("oracle16", "all_e2m1", "all_e0m3"):
+        p = oracle.quantize(np.zeros((9, 70), np.float32), mode)
+        assert p.global_scale == np.float32(1.0)
+        assert not oracle.dequant(p, "f32").any()
+        assert not p.codes.any() and (p.scales == 1).all()
+        assert int(p.format_ids().sum()) == (9 * 5 if mode == "all_e0m3" else 0)
+
+
+def test_linear_oracle_matches_numpy_float64():
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((5, 96)).astype(np.float32)
+    w = rng.standard_normal((7, 96)).astype(np.float32)
+    ref = (x.astype(np.float64) @ w.astype(np.float64).T).astype(np.float32)
+    assert np.array_equal(oracle.linear(x, w), ref)
+
+
+@pytest.mark.parametrize("name", sorted(digests()["cases"]))
+def test_full_size_digests(name):
+    """Full-size tensors: the oracle's packed bytes hash to what the reference produced."""
+    import torch
+    from mixfp4_b200 import synth
+
+    info = digests()["cases"][name]
+    if name.startswith("config1"):
+        w = synth.config1(0)[0]
+    elif "_q_" in name:
+        w = synth.student_t_weight(4096, 4096, 0)
+    else:
+        w = synth.student_t_weight(1024, 4096, 1)
+    raw = w.view(torch.int16).numpy().view(np.uint16)
+    if hashlib.sha256(raw.tobytes()).hexdigest() != info["input_sha256"]:
+        pytest.skip("this torch build draws different random numbers than the fixture's")
+    p = oracle.quantize(oracle.bf16_bits_to_f32(raw))
+    sha = lambda a: hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+    assert sha(p.codes) == info["codes_sha256"]
+    assert sha(p.scales) == info["scales_sha256"]
+    assert sha(p.fmt) == info["fmt_sha256"]
+    assert sha(oracle.dequant(p, "bf16")) == info["dequant_sha256"]
+    assert int(np.float32(p.global_scale).view(np.uint32)) == info["global_scale_bits"]
+    assert int(p.format_ids().sum()) == info["e0_blocks"]
