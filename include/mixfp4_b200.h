@@ -1,0 +1,134 @@
+/*
+ * mixfp4_b200 -- C ABI of the B200 (sm_100a) mixed-FP4 quantize / dequant-linear path.
+ *
+ * Plain pointers and sizes only; every pointer is a DEVICE pointer unless a
+ * parameter says otherwise.  All work is enqueued on the caller's stream (a
+ * cudaStream_t passed as void*) and nothing is synchronised.  Functions return 0
+ * on success or a negative MIXFP4_E_* code; no exception crosses the boundary and
+ * nothing is allocated behind the caller's back (kernels that need scratch
+ * memory take a caller-supplied workspace).
+ *
+ * The reference (Xrelifen/mixfp4, package project_quant) is PyTorch-only and has
+ * no FFI of its own; each entry point below names the reference function whose
+ * work it replaces.
+ *
+ * Packed weight layout (row-major, produced by mixfp4_quantize):
+ *   kpad   = mixfp4_padded_k(K)            K rounded up to a multiple of 128
+ *   codes  u8 [rows, kpad/2]   element 2j in the low nibble of byte j, element 2j+1 in
+ *                              the high nibble; nibble = sign<<3 | level index
+ *                              (E2M1 levels 0,.5,1,1.5,2,3,4,6; E0M3 levels 0..7)
+ *   scales u8 [rows, kpad/16]  E4M3 bit pattern of the block scale
+ *   fmt    u8 [rows, kpad/128] bit b of byte j <-> block 8j+b; 1 = E0M3, 0 = E2M1
+ *   global_scale f32 [1]       tensor scale (device memory)
+ * Decode contract: w = round_bf16( (level * float(scale)) * global_scale ), two fp32
+ * multiplies left to right, sign from nibble bit 3.
+ */
+#ifndef MIXFP4_B200_H_
+#define MIXFP4_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MIXFP4_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define MIXFP4_API __attribute__((visibility("default")))
+#else
+#define MIXFP4_API
+#endif
+
+enum {
+    MIXFP4_OK = 0,
+    MIXFP4_E_NULL = -1,        /* a required pointer is NULL */
+    MIXFP4_E_SHAPE = -2,       /* non-positive or inconsistent sizes / strides */
+    MIXFP4_E_ALIGN = -3,       /* pointer or stride alignment requirement violated */
+    MIXFP4_E_DTYPE = -4,       /* unknown or unsupported element type */
+    MIXFP4_E_MODE = -5,        /* unknown format-selection mode / rotation size */
+    MIXFP4_E_CUDA = -6,        /* a CUDA runtime or driver call failed; see mixfp4_last_cuda_error */
+    MIXFP4_E_WORKSPACE = -7,   /* workspace missing or too small */
+    MIXFP4_E_UNSUPPORTED = -8, /* valid request this build does not implement */
+    MIXFP4_E_DEVICE_WAIT = -9  /* a bounded device-side wait gave up (status word non-zero) */
+};
+
+/* element types */
+enum { MIXFP4_BF16 = 0, MIXFP4_F16 = 1, MIXFP4_F32 = 2 };
+
+/* format selection (project_quant/region.py:22-39 mode names) */
+enum { MIXFP4_MODE_ORACLE16 = 0, MIXFP4_MODE_ALL_E2M1 = 1, MIXFP4_MODE_ALL_E0M3 = 2 };
+
+MIXFP4_API int mixfp4_abi_version(void);
+MIXFP4_API const char* mixfp4_status_string(int status);
+/* Text of the last CUDA error seen by this library on the calling thread ("" if none). */
+MIXFP4_API const char* mixfp4_last_cuda_error(void);
+MIXFP4_API int64_t mixfp4_padded_k(int64_t k);
+
+/* Tensor-wide max |x| (first half of project_quant/scale.py:28-36 compute_global_scale).
+ * x: [rows, k] with row stride ldx elements.  amax: one float; the call first sets it
+ * to 0 on the stream and then reduces into it.  To quantize a shard with the scale of
+ * the whole tensor, reduce the shards' amax values (max) before mixfp4_quantize. */
+MIXFP4_API int mixfp4_amax(const void* x, int dtype, int64_t rows, int64_t k, int64_t ldx,
+                float* amax, void* stream);
+
+/* Block quantizer: replaces project_quant/candidates.py:62-106 build_candidates +
+ * scale.py:43-61 _one_scale_candidate (standard rule) + codebook.py:12-25,41-43 +
+ * the per-block choice and output cast of core.py:115-143.  Bit-exact with the
+ * reference's CPU arithmetic.
+ *   amax          device float from mixfp4_amax (global scale = amax / 2688, or 1 if 0)
+ *   codes/scales/fmt/global_scale   packed outputs (layout above); padding blocks are
+ *                 written too, so the buffers need no initialisation
+ *   e2_err, e0_err, e2_scale, e0_scale   optional f32 [rows, ceil(k/16)] per-block
+ *                 candidate errors and scales (GranularityResult fields), may be NULL
+ *   dequant       optional [rows, k] (row stride ld_dequant) dequantized tensor in the
+ *                 source dtype -- the reference's return value -- may be NULL */
+MIXFP4_API int mixfp4_quantize(const void* x, int dtype, int64_t rows, int64_t k, int64_t ldx, int mode,
+                    const float* amax,
+                    uint8_t* codes, uint8_t* scales, uint8_t* fmt, float* global_scale,
+                    float* e2_err, float* e0_err, float* e2_scale, float* e0_scale,
+                    void* dequant, int64_t ld_dequant, void* stream);
+
+/* Packed -> dense weight in out_dtype (the tensor the reference stores back into
+ * nn.Linear.weight, project_quant/modeling.py:629). */
+MIXFP4_API int mixfp4_dequant(const uint8_t* codes, const uint8_t* scales, const uint8_t* fmt,
+                   const float* global_scale, int64_t rows, int64_t k,
+                   void* out, int out_dtype, int64_t ldo, void* stream);
+
+/* Normalised block Hadamard along the last axis (project_quant/rotation.py:47-75
+ * fwht / apply_transform).  size in {16,32,64,128}; only whole blocks are transformed,
+ * a tail of k % size elements is copied through.  signs: optional device f32 [size]
+ * of +-1 applied before the butterflies (rotation.py:41-44).  y may alias x.
+ * stagewise != 0 rounds to the element type after every butterfly stage, which is
+ * what the reference does when it runs on a bf16/fp16 tensor; 0 keeps fp32 through all
+ * stages and rounds once at the end. */
+MIXFP4_API int mixfp4_fwht(const void* x, void* y, int dtype, int64_t rows, int64_t k, int64_t ldx,
+                int64_t ldy, int size, const float* signs, int stagewise, void* stream);
+
+/* Decode-shape dequant-linear, 1 <= M <= 16: y[M,N] = x[M,K] * W[N,K]^T with W packed
+ * (replaces F.linear on the dequantized weight, modeling.py:629 + nn.Linear.forward).
+ * x bf16 [M,K] row stride ldx; y in out_dtype (MIXFP4_F32 or MIXFP4_BF16) row stride ldy.
+ * fp32 accumulation. */
+MIXFP4_API int mixfp4_gemv(const void* x, int64_t m, int64_t ldx,
+                const uint8_t* codes, const uint8_t* scales, const uint8_t* fmt,
+                const float* global_scale, int64_t n, int64_t k,
+                void* y, int out_dtype, int64_t ldy, void* stream);
+
+/* Prefill-shape dequant-linear on the tcgen05 tensor cores (any M >= 1, meant for
+ * M >= 128).  rotation_block: 0, or 128 to apply the block-Hadamard H128 to x on the
+ * fly (the reference's forward-pre-hook, modeling.py:662-668) -- the rotated operand is
+ * bf16(FWHT_fp32(x)).  workspace: device scratch of at least
+ * mixfp4_gemm_workspace_bytes(m, n, k) bytes (may be NULL when that is 0).
+ * status: optional device int[1]; non-zero after completion if a bounded device-side
+ * wait gave up (the output is then invalid). */
+MIXFP4_API int64_t mixfp4_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k);
+MIXFP4_API int mixfp4_gemm(const void* x, int64_t m, int64_t ldx,
+                const uint8_t* codes, const uint8_t* scales, const uint8_t* fmt,
+                const float* global_scale, int64_t n, int64_t k, int rotation_block,
+                void* y, int out_dtype, int64_t ldy,
+                void* workspace, int64_t workspace_bytes, int* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MIXFP4_B200_H_ */

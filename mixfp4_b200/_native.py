@@ -1,0 +1,104 @@
+"""ctypes binding of the C-ABI library (include/mixfp4_b200.h).
+
+There is no fallback: if the shared library cannot be loaded every operation of
+the package raises.  Tensors cross the boundary as raw device pointers plus
+sizes; the stream is torch's current CUDA stream.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+from . import build as _build
+
+OK = 0
+BF16, F16, F32 = 0, 1, 2
+MODE_ORACLE16, MODE_ALL_E2M1, MODE_ALL_E0M3 = 0, 1, 2
+
+DTYPE_CODE = {torch.bfloat16: BF16, torch.float16: F16, torch.float32: F32}
+
+_lib = None
+
+
+class MixFP4Error(RuntimeError):
+    """A C-ABI call returned a negative status."""
+
+    def __init__(self, fn: str, status: int, detail: str = ""):
+        self.status = status
+        text = f"{fn} failed with status {status} ({lib().mixfp4_status_string(status).decode()})"
+        if detail:
+            text += ": " + detail
+        super().__init__(text)
+
+
+def _declare(h: ctypes.CDLL) -> None:
+    p, i64, i32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int
+    h.mixfp4_abi_version.restype = i32
+    h.mixfp4_abi_version.argtypes = []
+    h.mixfp4_status_string.restype = ctypes.c_char_p
+    h.mixfp4_status_string.argtypes = [i32]
+    h.mixfp4_last_cuda_error.restype = ctypes.c_char_p
+    h.mixfp4_last_cuda_error.argtypes = []
+    h.mixfp4_padded_k.restype = i64
+    h.mixfp4_padded_k.argtypes = [i64]
+    h.mixfp4_amax.restype = i32
+    h.mixfp4_amax.argtypes = [p, i32, i64, i64, i64, p, p]
+    h.mixfp4_quantize.restype = i32
+    h.mixfp4_quantize.argtypes = [p, i32, i64, i64, i64, i32, p, p, p, p, p, p, p, p, p, p, i64, p]
+    h.mixfp4_dequant.restype = i32
+    h.mixfp4_dequant.argtypes = [p, p, p, p, i64, i64, p, i32, i64, p]
+    h.mixfp4_fwht.restype = i32
+    h.mixfp4_fwht.argtypes = [p, p, i32, i64, i64, i64, i64, i32, p, i32, p]
+    h.mixfp4_gemv.restype = i32
+    h.mixfp4_gemv.argtypes = [p, i64, i64, p, p, p, p, i64, i64, p, i32, i64, p]
+    h.mixfp4_gemm_workspace_bytes.restype = i64
+    h.mixfp4_gemm_workspace_bytes.argtypes = [i64, i64, i64]
+    h.mixfp4_gemm.restype = i32
+    h.mixfp4_gemm.argtypes = [p, i64, i64, p, p, p, p, i64, i64, i32, p, i32, i64, p, i64, p, p]
+
+
+# every symbol include/mixfp4_b200.h declares
+EXPORTED = (
+    "mixfp4_abi_version", "mixfp4_status_string", "mixfp4_last_cuda_error", "mixfp4_padded_k",
+    "mixfp4_amax", "mixfp4_quantize", "mixfp4_dequant", "mixfp4_fwht", "mixfp4_gemv",
+    "mixfp4_gemm_workspace_bytes", "mixfp4_gemm",
+)
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded library; raises if it is missing (build it with ``python -m mixfp4_b200.build``)."""
+    global _lib
+    if _lib is None:
+        path = _build.LIB_PATH
+        if not os.path.exists(path):
+            raise RuntimeError(
+                f"{path} is missing: the CUDA library has not been built "
+                "(run `python -m mixfp4_b200.build`); mixfp4_b200 has no fallback path")
+        handle = ctypes.CDLL(path)
+        _declare(handle)
+        if handle.mixfp4_abi_version() != 1:
+            raise RuntimeError("libmixfp4_b200.so ABI version mismatch; rebuild it")
+        _lib = handle
+    return _lib
+
+
+def check(fn: str, status: int) -> None:
+    if status != OK:
+        detail = lib().mixfp4_last_cuda_error().decode() if status == -6 else ""
+        raise MixFP4Error(fn, status, detail)
+
+
+def stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def require_cuda(t: torch.Tensor, what: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{what} must be a CUDA tensor (mixfp4_b200 has no CPU path)")

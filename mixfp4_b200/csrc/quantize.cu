@@ -1,0 +1,364 @@
+// Block quantizer (E2M1-or-E0M3 per 16 elements), tensor amax and packed -> dense decode.
+//
+// Arithmetic contract (bit-exact with the reference's PyTorch CPU path):
+//   project_quant/scale.py:28-36     global = amax / 2688 (1 when the tensor is all zero)
+//   project_quant/scale.py:185       s = x / global                    (IEEE division)
+//   project_quant/scale.py:53-56     ideal = amax16|s| / qmax, clamp [2^-9, 448], E4M3 RNE
+//   project_quant/scale.py:57-58     n = s / scale; codes = E2M1 / E0M3 rounding of n
+//   project_quant/codebook.py:12-25  E2M1: floor(mantissa + 0.5) on the private mantissa
+//   project_quant/codebook.py:41-43  E0M3: round-half-even, saturate 7
+//   project_quant/scale.py:59-60     d = (code * scale) * global; err = sum (d - x)^2
+//   project_quant/core.py:116        E0M3 iff err_e0 < err_e2
+// Every fp32 operation uses a round-to-nearest intrinsic so that nothing is contracted
+// into an FMA, and the 16 squared errors are added in the order the reference's CPU
+// reduction uses (lane j + lane j+8 first, then the eight sums left to right).
+//
+// Work split: one thread owns one 16-element block (two candidates, ~40 fp32
+// instructions per element -- the kernel is bound by the fp32 pipes, not by HBM); a warp
+// owns 32 consecutive blocks of one row, so its loads cover 1 KB of contiguous bf16 and
+// its stores 256 B of codes, 32 B of scales and one 32-bit word of format bits.
+
+#include "common.cuh"
+
+namespace mixfp4 {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarpsPerCta = kThreads / 32;
+
+// ---------------------------------------------------------------------------- amax
+template <typename T>
+__global__ void __launch_bounds__(kThreads) amax_kernel(const T* __restrict__ x, int64_t rows, int64_t k,
+                                                        int64_t ldx, bool vec, unsigned int* __restrict__ out) {
+    float m = 0.0f;
+    if (vec) {
+        // rows are contiguous 16-byte multiples: walk the tensor as uint4 words
+        constexpr int kPer = 16 / sizeof(T);
+        const int64_t words_per_row = k / kPer;
+        const int64_t total = rows * words_per_row;
+        for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+             i += (int64_t)gridDim.x * blockDim.x) {
+            const int64_t r = i / words_per_row, w = i - r * words_per_row;
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + r * ldx) + w);
+            const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+            for (int j = 0; j < kPer; ++j) m = fmaxf(m, fabsf(Elem<T>::load(e + j)));
+        }
+    } else {
+        const int64_t total = rows * k;
+        for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+             i += (int64_t)gridDim.x * blockDim.x) {
+            const int64_t r = i / k, c = i - r * k;
+            m = fmaxf(m, fabsf(Elem<T>::load(x + r * ldx + c)));
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    __shared__ float warp_max[kWarpsPerCta];
+    if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int w = 1; w < kWarpsPerCta; ++w) m = fmaxf(m, warp_max[w]);
+        // non-negative floats order like their bit patterns
+        if (m > 0.0f) atomicMax(out, __float_as_uint(m));
+    }
+}
+
+// ------------------------------------------------------------------------- quantize
+struct QuantArgs {
+    const void* x;
+    int64_t rows, k, ldx;
+    int64_t groups;       // ceil(k / 16): real blocks per row
+    int64_t blocks_pad;   // kpad / 16: stored blocks per row
+    int64_t chunks;       // ceil(blocks_pad / 32): warps per row
+    int mode;
+    bool vec_in, vec_out;
+    const float* amax;
+    uint8_t* codes;
+    uint8_t* scales;
+    uint8_t* fmt;
+    float* global_scale;
+    float* e2_err;
+    float* e0_err;
+    float* e2_scale;
+    float* e0_scale;
+    void* dequant;
+    int64_t ld_dequant;
+};
+
+// E2M1 rounding of |n| exactly as codebook.py:12-25 computes it.
+__device__ __forceinline__ float e2m1_round(float mag) {
+    // exponent floor(log2 mag) clamped at 0 -> scale by 2/2^e, add 0.5 (fp32 rounding of
+    // that sum is part of the contract), floor, scale back, saturate at 6
+    const float up = mag < 2.0f ? 2.0f : (mag < 4.0f ? 1.0f : 0.5f);
+    const float down = mag < 2.0f ? 0.5f : (mag < 4.0f ? 1.0f : 2.0f);
+    const float q = __fmul_rn(floorf(__fadd_rn(__fmul_rn(mag, up), 0.5f)), down);
+    return fminf(q, 6.0f);
+}
+
+__device__ __forceinline__ uint32_t e2m1_index(float q) {
+    return q >= 1.0f ? (__float_as_uint(q) >> 22) - 252u : static_cast<uint32_t>(q + q);
+}
+
+// E0M3 rounding of |n|: round-half-even then saturate at 7 (codebook.py:41-43).
+__device__ __forceinline__ float e0m3_round(float mag) { return fminf(rintf(mag), 7.0f); }
+
+template <bool kE0>
+__device__ __forceinline__ void candidate(const float (&ax)[kGroup], const float (&s)[kGroup], float amax_s,
+                                          float gs, uint32_t& lo, uint32_t& hi, uint32_t& scale_byte,
+                                          float& scale_val, float& err, float (&dmag)[kGroup]) {
+    float ideal = __fdiv_rn(amax_s, kE0 ? 7.0f : 6.0f);
+    ideal = fminf(fmaxf(ideal, 0.001953125f), 448.0f);
+    scale_byte = __nv_cvt_float_to_fp8(ideal, __NV_SATFINITE, __NV_E4M3);
+    const float sc = e4m3_to_float(scale_byte);
+    scale_val = sc;
+    float sq[kGroup];
+    lo = 0;
+    hi = 0;
+#pragma unroll
+    for (int i = 0; i < kGroup; ++i) {
+        const float n = __fdiv_rn(s[i], sc);
+        const float mag = fabsf(n);
+        const float q = kE0 ? e0m3_round(mag) : e2m1_round(mag);
+        const uint32_t idx = kE0 ? static_cast<uint32_t>(q) : e2m1_index(q);
+        const uint32_t nib = idx | (n < 0.0f ? 8u : 0u);
+        if (i < 8) lo |= nib << (4 * i);
+        else hi |= nib << (4 * (i - 8));
+        // (d - x)^2 == (|d| - |x|)^2 bit for bit: d and x never have opposite signs
+        const float d = __fmul_rn(__fmul_rn(q, sc), gs);
+        dmag[i] = d;
+        const float e = __fsub_rn(d, ax[i]);
+        sq[i] = __fmul_rn(e, e);
+    }
+    float acc = __fadd_rn(sq[0], sq[8]);
+#pragma unroll
+    for (int j = 1; j < 8; ++j) acc = __fadd_rn(acc, __fadd_rn(sq[j], sq[j + 8]));
+    err = acc;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads) quantize_kernel(const QuantArgs a) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+    const int64_t row = warp / a.chunks;
+    if (row >= a.rows) return;                     // whole warp leaves together
+    const int64_t chunk = warp - row * a.chunks;
+    const int64_t blk = chunk * 32 + lane;         // block index inside the row
+    const bool stored = blk < a.blocks_pad;
+    const bool real = blk < a.groups;
+
+    const float amax = *a.amax;
+    const float gs = amax > 0.0f ? __fdiv_rn(amax, 2688.0f) : 1.0f;
+    if (warp == 0 && lane == 0) *a.global_scale = gs;
+
+    uint32_t lo = 0, hi = 0, scale_byte = 0x01;    // what an all-zero block quantizes to
+    bool use_e0 = false;
+
+    if (real) {
+        const T* xr = static_cast<const T*>(a.x) + row * a.ldx;
+        const int64_t c0 = blk * kGroup;
+        float x[kGroup];
+        if (a.vec_in && c0 + kGroup <= a.k) {
+            constexpr int kWords = kGroup * sizeof(T) / 16;
+            uint4 w[kWords];
+#pragma unroll
+            for (int j = 0; j < kWords; ++j) w[j] = __ldg(reinterpret_cast<const uint4*>(xr + c0) + j);
+            const T* e = reinterpret_cast<const T*>(w);
+#pragma unroll
+            for (int i = 0; i < kGroup; ++i) x[i] = Elem<T>::load(e + i);
+        } else {
+#pragma unroll
+            for (int i = 0; i < kGroup; ++i) x[i] = c0 + i < a.k ? Elem<T>::load(xr + c0 + i) : 0.0f;
+        }
+
+        float s[kGroup], ax[kGroup];
+        float amax_s = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kGroup; ++i) {
+            s[i] = __fdiv_rn(x[i], gs);
+            ax[i] = fabsf(x[i]);
+            amax_s = fmaxf(amax_s, fabsf(s[i]));
+        }
+
+        uint32_t lo2, hi2, b2, lo0, hi0, b0;
+        float sc2, sc0, err2, err0;
+        float d2[kGroup], d0[kGroup];
+        candidate<false>(ax, s, amax_s, gs, lo2, hi2, b2, sc2, err2, d2);
+        candidate<true>(ax, s, amax_s, gs, lo0, hi0, b0, sc0, err0, d0);
+        use_e0 = a.mode == MIXFP4_MODE_ORACLE16 ? (err0 < err2) : (a.mode == MIXFP4_MODE_ALL_E0M3);
+        lo = use_e0 ? lo0 : lo2;
+        hi = use_e0 ? hi0 : hi2;
+        scale_byte = use_e0 ? b0 : b2;
+
+        const int64_t g = row * a.groups + blk;
+        if (a.e2_err) a.e2_err[g] = err2;
+        if (a.e0_err) a.e0_err[g] = err0;
+        if (a.e2_scale) a.e2_scale[g] = sc2;
+        if (a.e0_scale) a.e0_scale[g] = sc0;
+
+        if (a.dequant) {
+            T* out = static_cast<T*>(a.dequant) + row * a.ld_dequant + c0;
+            T vals[kGroup];
+#pragma unroll
+            for (int i = 0; i < kGroup; ++i) {
+                const uint32_t nib = ((i < 8 ? lo : hi) >> (4 * (i & 7))) & 15u;
+                const float mag = use_e0 ? d0[i] : d2[i];
+                vals[i] = Elem<T>::round((nib & 8u) ? -mag : mag);
+            }
+            if (a.vec_out && c0 + kGroup <= a.k) {
+                constexpr int kWords = kGroup * sizeof(T) / 16;
+#pragma unroll
+                for (int j = 0; j < kWords; ++j)
+                    reinterpret_cast<uint4*>(out)[j] = reinterpret_cast<const uint4*>(vals)[j];
+            } else {
+#pragma unroll
+                for (int i = 0; i < kGroup; ++i)
+                    if (c0 + i < a.k) out[i] = vals[i];
+            }
+        }
+    }
+
+    if (stored) {
+        const int64_t ld_codes = a.blocks_pad * 8, ld_scales = a.blocks_pad;
+        *reinterpret_cast<uint2*>(a.codes + row * ld_codes + blk * 8) = make_uint2(lo, hi);
+        a.scales[row * ld_scales + blk] = static_cast<uint8_t>(scale_byte);
+    }
+    const uint32_t bits = __ballot_sync(0xffffffffu, use_e0);
+    const int64_t fmt_col = chunk * 4 + lane;      // lanes 0..3 write one format byte each
+    if (lane < 4 && fmt_col < a.blocks_pad / 8)
+        a.fmt[row * (a.blocks_pad / 8) + fmt_col] = static_cast<uint8_t>(bits >> (8 * lane));
+}
+
+// --------------------------------------------------------------------------- dequant
+template <typename T>
+__global__ void __launch_bounds__(kThreads) dequant_kernel(const uint8_t* __restrict__ codes,
+                                                           const uint8_t* __restrict__ scales,
+                                                           const uint8_t* __restrict__ fmt,
+                                                           const float* __restrict__ global_scale, int64_t rows,
+                                                           int64_t k, int64_t groups, int64_t blocks_pad,
+                                                           T* __restrict__ out, int64_t ldo, bool vec_out) {
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t row = t / groups;
+    if (row >= rows) return;
+    const int64_t blk = t - row * groups;
+    const float gs = *global_scale;
+    const uint2 c = __ldg(reinterpret_cast<const uint2*>(codes + row * blocks_pad * 8 + blk * 8));
+    const float sc = e4m3_to_float(__ldg(scales + row * blocks_pad + blk));
+    const bool e0 = (__ldg(fmt + row * (blocks_pad / 8) + (blk >> 3)) >> (blk & 7)) & 1;
+    T vals[kGroup];
+#pragma unroll
+    for (int i = 0; i < kGroup; ++i) {
+        const uint32_t nib = ((i < 8 ? c.x : c.y) >> (4 * (i & 7))) & 15u;
+        const float mag = __fmul_rn(__fmul_rn(level_value(nib & 7u, e0), sc), gs);
+        vals[i] = Elem<T>::round((nib & 8u) ? -mag : mag);
+    }
+    const int64_t c0 = blk * kGroup;
+    T* o = out + row * ldo + c0;
+    if (vec_out && c0 + kGroup <= k) {
+        constexpr int kWords = kGroup * sizeof(T) / 16;
+#pragma unroll
+        for (int j = 0; j < kWords; ++j) reinterpret_cast<uint4*>(o)[j] = reinterpret_cast<const uint4*>(vals)[j];
+    } else {
+#pragma unroll
+        for (int i = 0; i < kGroup; ++i)
+            if (c0 + i < k) o[i] = vals[i];
+    }
+}
+
+size_t elem_size(int dtype) { return dtype == MIXFP4_F32 ? 4 : 2; }
+
+bool rows_vectorizable(const void* p, int64_t ld, int dtype) {
+    return aligned(p, 16) && (ld * (int64_t)elem_size(dtype)) % 16 == 0;
+}
+
+}  // namespace
+}  // namespace mixfp4
+
+using namespace mixfp4;
+
+extern "C" int mixfp4_amax(const void* x, int dtype, int64_t rows, int64_t k, int64_t ldx, float* amax,
+                           void* stream) {
+    if (!x || !amax) return MIXFP4_E_NULL;
+    if (rows <= 0 || k <= 0 || ldx < k) return MIXFP4_E_SHAPE;
+    if (dtype < MIXFP4_BF16 || dtype > MIXFP4_F32) return MIXFP4_E_DTYPE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    MIXFP4_CUDA_CHECK(cudaMemsetAsync(amax, 0, sizeof(float), st));
+    const bool vec = rows_vectorizable(x, ldx, dtype) && (k * (int64_t)elem_size(dtype)) % 16 == 0;
+    const int64_t items = vec ? rows * (k * (int64_t)elem_size(dtype) / 16) : rows * k;
+    int64_t ctas = (items + kThreads * 4 - 1) / (kThreads * 4);
+    if (ctas < 1) ctas = 1;
+    if (ctas > 148 * 8) ctas = 148 * 8;   // a few waves of grid-stride CTAs
+    unsigned int* out = reinterpret_cast<unsigned int*>(amax);
+    switch (dtype) {
+        case MIXFP4_BF16:
+            amax_kernel<<<(unsigned)ctas, kThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), rows, k, ldx, vec, out);
+            break;
+        case MIXFP4_F16:
+            amax_kernel<<<(unsigned)ctas, kThreads, 0, st>>>(static_cast<const __half*>(x), rows, k, ldx, vec, out);
+            break;
+        default:
+            amax_kernel<<<(unsigned)ctas, kThreads, 0, st>>>(static_cast<const float*>(x), rows, k, ldx, vec, out);
+    }
+    return check_launch("amax_kernel");
+}
+
+extern "C" int mixfp4_quantize(const void* x, int dtype, int64_t rows, int64_t k, int64_t ldx, int mode,
+                               const float* amax, uint8_t* codes, uint8_t* scales, uint8_t* fmt,
+                               float* global_scale, float* e2_err, float* e0_err, float* e2_scale,
+                               float* e0_scale, void* dequant, int64_t ld_dequant, void* stream) {
+    if (!x || !amax || !codes || !scales || !fmt || !global_scale) return MIXFP4_E_NULL;
+    if (rows <= 0 || k <= 0 || ldx < k || (dequant && ld_dequant < k)) return MIXFP4_E_SHAPE;
+    if (dtype < MIXFP4_BF16 || dtype > MIXFP4_F32) return MIXFP4_E_DTYPE;
+    if (mode < MIXFP4_MODE_ORACLE16 || mode > MIXFP4_MODE_ALL_E0M3) return MIXFP4_E_MODE;
+    if (!aligned(codes, 8)) return MIXFP4_E_ALIGN;
+    QuantArgs a;
+    a.x = x; a.rows = rows; a.k = k; a.ldx = ldx;
+    a.groups = (k + kGroup - 1) / kGroup;
+    a.blocks_pad = padded_k(k) / kGroup;
+    a.chunks = (a.blocks_pad + 31) / 32;
+    a.mode = mode;
+    a.vec_in = rows_vectorizable(x, ldx, dtype);
+    a.vec_out = dequant && rows_vectorizable(dequant, ld_dequant, dtype);
+    a.amax = amax; a.codes = codes; a.scales = scales; a.fmt = fmt; a.global_scale = global_scale;
+    a.e2_err = e2_err; a.e0_err = e0_err; a.e2_scale = e2_scale; a.e0_scale = e0_scale;
+    a.dequant = dequant; a.ld_dequant = ld_dequant;
+    const int64_t warps = rows * a.chunks;
+    const int64_t ctas = (warps + kWarpsPerCta - 1) / kWarpsPerCta;
+    if (ctas > 0x7fffffffLL) return MIXFP4_E_SHAPE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case MIXFP4_BF16: quantize_kernel<__nv_bfloat16><<<(unsigned)ctas, kThreads, 0, st>>>(a); break;
+        case MIXFP4_F16: quantize_kernel<__half><<<(unsigned)ctas, kThreads, 0, st>>>(a); break;
+        default: quantize_kernel<float><<<(unsigned)ctas, kThreads, 0, st>>>(a);
+    }
+    return check_launch("quantize_kernel");
+}
+
+extern "C" int mixfp4_dequant(const uint8_t* codes, const uint8_t* scales, const uint8_t* fmt,
+                              const float* global_scale, int64_t rows, int64_t k, void* out, int out_dtype,
+                              int64_t ldo, void* stream) {
+    if (!codes || !scales || !fmt || !global_scale || !out) return MIXFP4_E_NULL;
+    if (rows <= 0 || k <= 0 || ldo < k) return MIXFP4_E_SHAPE;
+    if (out_dtype < MIXFP4_BF16 || out_dtype > MIXFP4_F32) return MIXFP4_E_DTYPE;
+    if (!aligned(codes, 8)) return MIXFP4_E_ALIGN;
+    const int64_t groups = (k + kGroup - 1) / kGroup, blocks_pad = padded_k(k) / kGroup;
+    const int64_t ctas = (rows * groups + kThreads - 1) / kThreads;
+    if (ctas > 0x7fffffffLL) return MIXFP4_E_SHAPE;
+    const bool vec = rows_vectorizable(out, ldo, out_dtype);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (out_dtype) {
+        case MIXFP4_BF16:
+            dequant_kernel<<<(unsigned)ctas, kThreads, 0, st>>>(codes, scales, fmt, global_scale, rows, k, groups,
+                                                                blocks_pad, static_cast<__nv_bfloat16*>(out), ldo, vec);
+            break;
+        case MIXFP4_F16:
+            dequant_kernel<<<(unsigned)ctas, kThreads, 0, st>>>(codes, scales, fmt, global_scale, rows, k, groups,
+                                                                blocks_pad, static_cast<__half*>(out), ldo, vec);
+            break;
+        default:
+            dequant_kernel<<<(unsigned)ctas, kThreads, 0, st>>>(codes, scales, fmt, global_scale, rows, k, groups,
+                                                                blocks_pad, static_cast<float*>(out), ldo, vec);
+    }
+    return check_launch("dequant_kernel");
+}

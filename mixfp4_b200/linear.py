@@ -1,0 +1,151 @@
+"""Mixed-FP4 dequant-linear: the layer that replaces ``nn.Linear`` on a weight the
+reference would have overwritten with its dequantized tensor
+(project_quant/modeling.py:603-639 quantize_model_weights, :629 the weight swap, and the
+activation rotation pre-hook :662-668).
+
+``mixfp4_linear`` picks the kernel by shape alone: M <= 16 runs the HBM-bound GEMV,
+larger M the tcgen05 GEMM.  There is one implementation per shape class and no
+fallback.
+"""
+
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from . import _native as nat
+from . import rotation as _rotation
+from .quant import PackedWeight, quantize_packed
+
+GEMV_MAX_M = 16
+_workspaces: dict[tuple, torch.Tensor] = {}
+_status_words: dict[str, torch.Tensor] = {}
+
+
+def _workspace(device, nbytes: int) -> torch.Tensor | None:
+    if nbytes <= 0:
+        return None
+    key = (str(device), torch.cuda.current_stream(device).cuda_stream)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def _status_word(device) -> torch.Tensor:
+    key = str(device)
+    if key not in _status_words:
+        _status_words[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status_words[key]
+
+
+def gemm_status(device=None) -> int:
+    """Value of the GEMM's device-side status word (0 = every bounded wait completed).
+    Synchronises the device."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    return int(_status_word(device).item())
+
+
+def mixfp4_linear(x: torch.Tensor, packed: PackedWeight, *, bias: torch.Tensor | None = None,
+                  rotate: bool | None = None, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """y = x @ W^T (+ bias) with W packed; x bf16 [..., K] on the GPU.
+
+    rotate: apply the weight's folded K-transform to x first (default: yes when the packed
+    weight records one).  H128 is fused into the GEMM prologue; the GEMV path and other
+    block sizes run the stand-alone FWHT kernel (fp32 stages, one rounding).
+    out_dtype: torch.float32 or torch.bfloat16 (default: x.dtype).
+    """
+    nat.require_cuda(x, "x")
+    if x.dtype != torch.bfloat16:
+        raise TypeError("x must be bfloat16")
+    if x.shape[-1] != packed.k:
+        raise ValueError(f"x has K={x.shape[-1]}, the packed weight K={packed.k}")
+    out_dtype = x.dtype if out_dtype is None else out_dtype
+    if out_dtype not in (torch.float32, torch.bfloat16):
+        raise TypeError("out_dtype must be float32 or bfloat16")
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, packed.k)
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    m = x2.shape[0]
+    spec = None
+    if rotate is None:
+        rotate = packed.rotation is not None
+    if rotate:
+        if packed.rotation is None:
+            raise ValueError("rotate=True but the packed weight records no rotation")
+        spec = _rotation.get_transform(packed.rotation)
+        if spec.block_size is None:
+            spec = None
+    y = torch.empty((m, packed.n), dtype=out_dtype, device=x.device)
+    if m == 0:
+        return y.reshape(*lead, packed.n)
+    lib = nat.lib()
+    with torch.cuda.device(x.device):
+        stream = nat.stream_ptr(x.device)
+        if m <= GEMV_MAX_M:
+            if spec is not None:
+                x2 = _rotation.apply_transform(x2, spec, rounding="once")
+            st = lib.mixfp4_gemv(x2.data_ptr(), m, x2.stride(0), packed.codes.data_ptr(), packed.scales.data_ptr(),
+                                 packed.fmt.data_ptr(), packed.global_scale.data_ptr(), packed.n, packed.k,
+                                 y.data_ptr(), nat.DTYPE_CODE[out_dtype], y.stride(0), stream)
+            nat.check("mixfp4_gemv", st)
+        else:
+            fused = 0
+            if spec is not None:
+                if spec.block_size == 128 and spec.seed is None:
+                    fused = 128
+                else:
+                    x2 = _rotation.apply_transform(x2, spec, rounding="once")
+            nbytes = lib.mixfp4_gemm_workspace_bytes(m, packed.n, packed.k)
+            ws = _workspace(x.device, nbytes)
+            st = lib.mixfp4_gemm(x2.data_ptr(), m, x2.stride(0), packed.codes.data_ptr(), packed.scales.data_ptr(),
+                                 packed.fmt.data_ptr(), packed.global_scale.data_ptr(), packed.n, packed.k, fused,
+                                 y.data_ptr(), nat.DTYPE_CODE[out_dtype], y.stride(0), nat.ptr(ws), nbytes,
+                                 _status_word(x.device).data_ptr(), stream)
+            nat.check("mixfp4_gemm", st)
+    if bias is not None:
+        y += bias.to(y.dtype)
+    return y.reshape(*lead, packed.n)
+
+
+class MixFP4Linear(nn.Module):
+    """nn.Linear whose weight lives in the packed mixed-FP4 layout."""
+
+    def __init__(self, packed: PackedWeight, bias: torch.Tensor | None = None):
+        super().__init__()
+        self.in_features, self.out_features = packed.k, packed.n
+        self.rotation = packed.rotation
+        self.register_buffer("codes", packed.codes)
+        self.register_buffer("scales", packed.scales)
+        self.register_buffer("fmt", packed.fmt)
+        self.register_buffer("global_scale", packed.global_scale)
+        self.bias = None if bias is None else nn.Parameter(bias.detach().clone(), requires_grad=False)
+
+    @property
+    def packed(self) -> PackedWeight:
+        return PackedWeight(self.codes, self.scales, self.fmt, self.global_scale, self.out_features,
+                            self.in_features, self.rotation)
+
+    @classmethod
+    @torch.no_grad()
+    def from_linear(cls, linear: nn.Linear, *, rotation: str | None = None, mode: str = "oracle16",
+                    device=None) -> "MixFP4Linear":
+        """Quantize ``linear.weight`` (optionally rotated along K first, as the reference's
+        apply_rotations does offline, modeling.py:323-344) and wrap it."""
+        device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+        w = linear.weight.detach().to(device)
+        if w.dtype not in nat.DTYPE_CODE:
+            w = w.to(torch.bfloat16)
+        if rotation is not None:
+            w = _rotation.apply_transform(w, rotation)
+        packed, _, _ = quantize_packed(w, mode=mode, rotation=rotation)
+        bias = None if linear.bias is None else linear.bias.detach().to(device)
+        return cls(packed, bias)
+
+    def forward(self, x: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+        return mixfp4_linear(x, self.packed, bias=self.bias, out_dtype=out_dtype)
+
+    def extra_repr(self) -> str:
+        return f"in_features={self.in_features}, out_features={self.out_features}, rotation={self.rotation}"

@@ -1,0 +1,354 @@
+"""Python surface of the block quantizer: the reference's ``quant_mixfp4_granularity``
+keyword API plus the packed weight type the reference does not have.
+
+Reference interface mirrored here (paths inside the reference project):
+  project_quant/core.py:53-67     quant_mixfp4_granularity signature, defaults, return types
+  project_quant/core.py:18-29     GranularityResult fields
+  project_quant/candidates.py:46-58  validate_layout error types and messages
+  project_quant/region.py:22-39   normalize_region aliases
+All arithmetic runs in the CUDA kernels behind the C ABI (mixfp4_amax +
+mixfp4_quantize); a host tensor is copied to the current CUDA device and the result is
+copied back.  Nothing here computes on the CPU.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any
+
+import torch
+
+from . import _native as nat
+from . import rotation as _rotation
+
+SCALE_GROUP_SIZE = 16
+E2M1_LEVELS = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+E0M3_LEVELS = (0.0, 1.0, 2.0, 3.0, 4.0, 5.0, 6.0, 7.0)
+TAIL_POLICY = (
+    "right_zero_pad_only_the_final_partial_K16_scale_block_then_unpad; "
+    "partial_N_or_M_and_K_format_regions_use_only_real_K16_blocks"
+)
+
+_MODE_CODE = {"oracle16": nat.MODE_ORACLE16, "all_e2m1": nat.MODE_ALL_E2M1, "all_e0m3": nat.MODE_ALL_E0M3}
+_COARSE_REGIONS = {
+    "layer", "k32_row", "k64_row", "n8k16", "n2k64", "n4k64", "n8k64", "n16k64", "n32k64", "n64k64",
+    "m16k16", "m4k64", "m8k64", "m16k64", "m32k64",
+}
+
+
+def padded_k(k: int) -> int:
+    return (k + 127) // 128 * 128
+
+
+def packed_nbytes(n: int, k: int) -> int:
+    """Algorithmic bytes of a packed [n, k] weight: 4-bit codes + one E4M3 scale and one
+    format bit per 16 elements (+ the 4-byte tensor scale)."""
+    return n * k // 2 + n * k // 16 + n * k // 128 + 4
+
+
+@dataclass
+class PackedWeight:
+    """A quantized [n, k] matrix in the packed layout of include/mixfp4_b200.h."""
+
+    codes: torch.Tensor          # uint8 [n, kpad/2]
+    scales: torch.Tensor         # uint8 [n, kpad/16]  E4M3 bytes
+    fmt: torch.Tensor            # uint8 [n, kpad/128] format bits (1 = E0M3)
+    global_scale: torch.Tensor   # float32 [1]
+    n: int
+    k: int
+    rotation: str | None = None  # transform folded into the weight along K before quantization
+
+    @property
+    def kpad(self) -> int:
+        return padded_k(self.k)
+
+    @property
+    def groups(self) -> int:
+        return (self.k + 15) // 16
+
+    @property
+    def device(self) -> torch.device:
+        return self.codes.device
+
+    def nbytes(self) -> int:
+        return packed_nbytes(self.n, self.k)
+
+    def format_ids(self) -> torch.Tensor:
+        """uint8 [n, ceil(k/16)], 1 = E0M3 (GranularityResult.format_ids of the reference)."""
+        shifts = torch.arange(8, device=self.fmt.device, dtype=torch.uint8)
+        bits = (self.fmt.unsqueeze(-1) >> shifts) & 1
+        return bits.reshape(self.n, -1)[:, : self.groups].contiguous()
+
+    def selected_scales(self) -> torch.Tensor:
+        """float32 [n, ceil(k/16)] decoded block scales."""
+        return self.scales[:, : self.groups].contiguous().view(torch.float8_e4m3fn).float()
+
+    def dequantize(self, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+        return dequantize(self, dtype)
+
+    def to(self, device) -> "PackedWeight":
+        return PackedWeight(self.codes.to(device), self.scales.to(device), self.fmt.to(device),
+                            self.global_scale.to(device), self.n, self.k, self.rotation)
+
+    def state_dict(self) -> dict:
+        return {"codes": self.codes, "scales": self.scales, "fmt": self.fmt, "global_scale": self.global_scale,
+                "n": self.n, "k": self.k, "rotation": self.rotation}
+
+    @staticmethod
+    def from_state_dict(state: dict) -> "PackedWeight":
+        return PackedWeight(state["codes"], state["scales"], state["fmt"], state["global_scale"],
+                            int(state["n"]), int(state["k"]), state.get("rotation"))
+
+    def row_shard(self, start: int, stop: int) -> "PackedWeight":
+        """Rows [start, stop) -- a column-parallel (split N) shard; shares the tensor scale."""
+        return PackedWeight(self.codes[start:stop].contiguous(), self.scales[start:stop].contiguous(),
+                            self.fmt[start:stop].contiguous(), self.global_scale, stop - start, self.k, self.rotation)
+
+    def k_shard(self, start: int, stop: int) -> "PackedWeight":
+        """Columns [start, stop) along K (multiples of 128) -- a row-parallel (split K) shard."""
+        if start % 128 or (stop % 128 and stop != self.k):
+            raise ValueError("K shards must start and end on multiples of 128")
+        pstop = padded_k(stop)
+        return PackedWeight(self.codes[:, start // 2: pstop // 2].contiguous(),
+                            self.scales[:, start // 16: pstop // 16].contiguous(),
+                            self.fmt[:, start // 128: pstop // 128].contiguous(),
+                            self.global_scale, self.n, stop - start, self.rotation)
+
+
+@dataclass
+class GranularityResult:
+    """Same fields as the reference's GranularityResult (project_quant/core.py:18-29),
+    plus ``packed``."""
+
+    dequant: torch.Tensor
+    format_ids: torch.Tensor
+    oracle_format_ids: torch.Tensor
+    selected_scales: torch.Tensor
+    selected_scale_expansion_ids: torch.Tensor
+    e2_scales: torch.Tensor
+    e0_scales: torch.Tensor
+    e2_errors: torch.Tensor
+    e0_errors: torch.Tensor
+    summary: dict[str, Any]
+    regions: list[dict[str, Any]] = field(default_factory=list)
+    packed: PackedWeight | None = None
+
+
+def normalize_region(mode: str, operand_role: str) -> str:
+    value = str(mode).lower().replace("-", "_")
+    for prefix in ("mixfp4_", "nvfp4_mixfp4_"):
+        if value.startswith(prefix):
+            value = value[len(prefix):]
+    aliases = {"nvfp4": "all_e2m1", "all_e2": "all_e2m1", "e2": "all_e2m1", "all_e0": "all_e0m3",
+               "e0": "all_e0m3", "oracle16_a": "oracle16", "k64_row_a": "k64_row"}
+    return aliases.get(value, value)
+
+
+def validate_layout(x: torch.Tensor, *, scale_group_size: int, operand_role: str) -> None:
+    if not torch.is_floating_point(x):
+        raise TypeError("x must be floating point")
+    if x.ndim < 2:
+        raise ValueError("x must preserve a row dimension and a final K dimension")
+    if operand_role == "weight_b" and x.ndim != 2:
+        raise ValueError("weight_b requires the exact [N,K] matrix layout")
+    if operand_role not in {"weight_b", "activation_a"}:
+        raise ValueError("operand_role must be 'weight_b' or 'activation_a'")
+    if scale_group_size != SCALE_GROUP_SIZE:
+        raise ValueError("the primary MixFP4 study fixes scale_group_size=16")
+    if x.shape[-1] <= 0:
+        raise ValueError("K must be positive")
+
+
+def tensor_amax(x2: torch.Tensor) -> torch.Tensor:
+    """max |x| of a 2-D CUDA tensor as a float32 [1] device tensor (no host sync)."""
+    out = torch.empty(1, dtype=torch.float32, device=x2.device)
+    with torch.cuda.device(x2.device):
+        st = nat.lib().mixfp4_amax(x2.data_ptr(), nat.DTYPE_CODE[x2.dtype], x2.shape[0], x2.shape[1],
+                                   x2.stride(0), out.data_ptr(), nat.stream_ptr(x2.device))
+    nat.check("mixfp4_amax", st)
+    return out
+
+
+def _as_rows(x: torch.Tensor) -> torch.Tensor:
+    if x.dtype not in nat.DTYPE_CODE:
+        raise TypeError(f"unsupported dtype {x.dtype}; use bfloat16, float16 or float32")
+    nat.require_cuda(x, "x")
+    k = x.shape[-1]
+    x2 = x.reshape(-1, k)
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    return x2
+
+
+def quantize_packed(x: torch.Tensor, *, mode: str = "oracle16", amax: torch.Tensor | None = None,
+                    want_dequant: bool = False, want_stats: bool = False, rotation: str | None = None):
+    """Quantize a CUDA tensor [..., K] (leading dims fold into rows) into a PackedWeight.
+
+    amax: optional float32 [1] device tensor holding max|x| of the WHOLE tensor this is a
+    shard of (see mixfp4_amax); default: this tensor's own.
+    Returns (packed, dequant_or_None, stats_or_None); stats = dict of per-block float32
+    [rows, G] tensors e2_errors, e0_errors, e2_scales, e0_scales.
+    """
+    if mode not in _MODE_CODE:
+        raise ValueError(f"unsupported mode {mode!r}")
+    x2 = _as_rows(x)
+    rows, k = x2.shape
+    kp = padded_k(k)
+    groups = (k + 15) // 16
+    dev = x2.device
+    if amax is None:
+        amax = tensor_amax(x2)
+    codes = torch.empty((rows, kp // 2), dtype=torch.uint8, device=dev)
+    scales = torch.empty((rows, kp // 16), dtype=torch.uint8, device=dev)
+    fmt = torch.empty((rows, kp // 128), dtype=torch.uint8, device=dev)
+    gs = torch.empty(1, dtype=torch.float32, device=dev)
+    stats = None
+    if want_stats:
+        stats = {name: torch.empty((rows, groups), dtype=torch.float32, device=dev)
+                 for name in ("e2_errors", "e0_errors", "e2_scales", "e0_scales")}
+    dq = torch.empty((rows, k), dtype=x2.dtype, device=dev) if want_dequant else None
+    with torch.cuda.device(dev):
+        st = nat.lib().mixfp4_quantize(
+            x2.data_ptr(), nat.DTYPE_CODE[x2.dtype], rows, k, x2.stride(0), _MODE_CODE[mode], amax.data_ptr(),
+            codes.data_ptr(), scales.data_ptr(), fmt.data_ptr(), gs.data_ptr(),
+            nat.ptr(stats["e2_errors"]) if stats else None, nat.ptr(stats["e0_errors"]) if stats else None,
+            nat.ptr(stats["e2_scales"]) if stats else None, nat.ptr(stats["e0_scales"]) if stats else None,
+            nat.ptr(dq), k, nat.stream_ptr(dev))
+    nat.check("mixfp4_quantize", st)
+    return PackedWeight(codes, scales, fmt, gs, rows, k, rotation), dq, stats
+
+
+def dequantize(packed: PackedWeight, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """Dense [n, k] tensor with exactly the values the reference's dequantized weight holds."""
+    if dtype not in nat.DTYPE_CODE:
+        raise TypeError("dtype must be bfloat16, float16 or float32")
+    nat.require_cuda(packed.codes, "packed weight")
+    out = torch.empty((packed.n, packed.k), dtype=dtype, device=packed.device)
+    with torch.cuda.device(packed.device):
+        st = nat.lib().mixfp4_dequant(packed.codes.data_ptr(), packed.scales.data_ptr(), packed.fmt.data_ptr(),
+                                      packed.global_scale.data_ptr(), packed.n, packed.k, out.data_ptr(),
+                                      nat.DTYPE_CODE[dtype], packed.k, nat.stream_ptr(packed.device))
+    nat.check("mixfp4_dequant", st)
+    return out
+
+
+def _tensor_error_metrics(source: torch.Tensor, dequant: torch.Tensor) -> dict[str, float]:
+    # formulas of project_quant/metrics.py:15-34, evaluated on the device
+    x = source.detach().float().reshape(-1)
+    q = dequant.detach().float().reshape(-1)
+    delta = q - x
+    err, sx, sq = torch.dot(delta, delta), torch.dot(x, x), torch.dot(q, q)
+    tiny = torch.finfo(torch.float32).tiny
+    cosine = torch.dot(x, q) / torch.sqrt(sx * sq).clamp_min(tiny)
+    mae, mx = delta.abs().mean(), delta.abs().max()
+    vals = torch.stack([err / x.numel(), err / sx.clamp_min(tiny), torch.sqrt(err / sx.clamp_min(tiny)),
+                        cosine, 1 - cosine, mae, mx]).tolist()
+    keys = ("mse", "nmse", "relative_l2", "cosine_similarity", "cosine_error", "mean_absolute_error",
+            "max_absolute_error")
+    out = dict(zip(keys, vals))
+    out["mean_abs_error"] = out["mean_absolute_error"]
+    out["max_abs_error"] = out["max_absolute_error"]
+    return out
+
+
+@torch.no_grad()
+def quant_mixfp4_granularity(
+    x: torch.Tensor,
+    *,
+    scale_group_size: int = SCALE_GROUP_SIZE,
+    format_region: str = "oracle16",
+    operand_role: str = "weight_b",
+    selector: str = "mse",
+    scale_rule: str = "standard",
+    calibration_stats: dict[str, Any] | None = None,
+    transform: Any = None,
+    permutation: torch.Tensor | None = None,
+    return_stats: bool = False,
+    collect_regions: bool = False,
+    region_sample_limit: int | None = None,
+) -> torch.Tensor | GranularityResult:
+    """Fake-quantize ``x`` with K16 block scales and a per-block E2M1/E0M3 choice.
+
+    Drop-in for the reference function of the same name: returns a new tensor of
+    ``x.shape`` / ``x.dtype`` (or a GranularityResult with ``return_stats=True``).
+    Supported here: format_region oracle16 / all_e2m1 / all_e0m3, selector "mse",
+    scale_rule "standard"; the coarse regions, the output-aware selector and the
+    four_over_six rule raise NotImplementedError.
+    """
+    working = x
+    if permutation is not None:
+        if operand_role != "weight_b" or x.ndim != 2:
+            raise ValueError("permutation is defined only for [N,K] weights")
+        if permutation.numel() != x.shape[0]:
+            raise ValueError("permutation length must equal N")
+        working = working.index_select(0, permutation.to(working.device))
+    mode = normalize_region(format_region, operand_role)
+    validate_layout(working, scale_group_size=scale_group_size, operand_role=operand_role)
+    if scale_rule == "four_over_six":
+        raise NotImplementedError("scale_rule='four_over_six' is not implemented in the CUDA path")
+    if scale_rule != "standard":
+        raise ValueError(f"unknown scale_rule={scale_rule!r}")
+    if selector in {"output_aware", "activation_aware"}:
+        if operand_role != "weight_b" or mode != "n8k64":
+            raise ValueError("output-aware selection is defined for N8K64 weights")
+        raise NotImplementedError("output-aware selection is not implemented in the CUDA path")
+    if selector != "mse":
+        raise ValueError(f"unknown selector={selector!r}")
+    if mode in _COARSE_REGIONS:
+        raise NotImplementedError(f"format_region={mode!r}: coarse format regions are not implemented yet")
+    if mode not in _MODE_CODE:
+        raise ValueError(f"format_region={mode!r} is invalid for {operand_role}")
+
+    host_input = not working.is_cuda
+    if host_input:
+        working = working.cuda()
+    if transform is not None:
+        working = _rotation.apply_transform(working, transform)
+
+    packed, dq, stats = quantize_packed(working, mode=mode, want_dequant=True, want_stats=return_stats)
+    dequant = dq.reshape(working.shape)
+    if host_input:
+        dequant = dequant.to(x.device)
+    if not return_stats:
+        return dequant
+
+    e2e, e0e = stats["e2_errors"], stats["e0_errors"]
+    ids = packed.format_ids()
+    oracle_ids = (e0e < e2e).to(torch.uint8)
+    margin = e2e - e0e
+    selected_err = torch.where(ids.bool(), e0e, e2e).sum()
+    oracle_err = torch.minimum(e2e, e0e).sum()
+    numel = working.numel()
+    blocks = ids.numel()
+    k = working.shape[-1]
+    rows = numel // k
+    small = torch.stack([ids.float().sum(), oracle_ids.float().sum(), margin.mean(), margin.abs().mean(),
+                         margin.median(), oracle_err, selected_err, e2e.sum(), e0e.sum(),
+                         packed.global_scale[0]]).tolist()
+    e0_count, oracle_e0 = int(small[0]), int(small[1])
+    summary: dict[str, Any] = {
+        **_tensor_error_metrics(working, dq.reshape(working.shape)),
+        "scale_group_size": scale_group_size, "scale_rule": scale_rule, "format_granularity": mode,
+        "format_region_rows": 1 if mode == "oracle16" else rows,
+        "format_region_k16_groups": 1 if mode == "oracle16" else packed.groups,
+        "format_region_k_values": 16 if mode == "oracle16" else packed.groups * 16,
+        "operand_role": operand_role, "selector": "mse", "tail_policy": TAIL_POLICY,
+        "tail_padding_values": (-k) % 16, "rows": rows, "N_or_M": rows, "K": k, "numel": numel,
+        "num_scale_blocks": blocks, "e0_count": e0_count, "e2_count": blocks - e0_count,
+        "e0_ratio": e0_count / blocks, "e2_ratio": 1.0 - e0_count / blocks,
+        "oracle_e0_count": oracle_e0, "oracle_e2_count": blocks - oracle_e0, "oracle_e0_ratio": oracle_e0 / blocks,
+        "mean_format_margin": small[2], "mean_signed_format_margin": small[2], "mean_abs_format_margin": small[3],
+        "median_format_margin": small[4], "oracle_mse": small[5] / numel, "constrained_mse": small[6] / numel,
+        "selected_mse": small[6] / numel, "oracle_error": small[5], "constrained_error": small[6],
+        "selected_weight_error": small[6], "granularity_regret": small[6] - small[5],
+        "all_e2m1_error": small[7], "all_e0m3_error": small[8], "global_scale": small[9],
+        "transform": getattr(transform, "name", transform) if transform is not None else "identity",
+        "permutation_applied": permutation is not None,
+    }
+    mv = lambda t: t.to(x.device) if host_input else t
+    return GranularityResult(
+        dequant=dequant, format_ids=mv(ids), oracle_format_ids=mv(oracle_ids),
+        selected_scales=mv(packed.selected_scales()),
+        selected_scale_expansion_ids=mv(torch.zeros_like(ids)),
+        e2_scales=mv(stats["e2_scales"]), e0_scales=mv(stats["e0_scales"]),
+        e2_errors=mv(e2e), e0_errors=mv(e0e), summary=summary, regions=[], packed=packed)

@@ -1,0 +1,97 @@
+"""CPU-only checks of the drop-in boundary: the library loads without a GPU, exports every
+symbol the header declares, validates arguments before touching CUDA, and the Python
+surface raises the reference's exception types."""
+
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+import mixfp4_b200 as mx
+from mixfp4_b200 import _native as nat
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "mixfp4_b200.h")).read()
+    declared = set(re.findall(r"MIXFP4_API\s+[\w\s\*]+?\b(mixfp4_\w+)\s*\(", header))
+    assert declared == set(nat.EXPORTED)
+    handle = nat.lib()
+    for name in declared:
+        assert getattr(handle, name) is not None
+    assert handle.mixfp4_abi_version() == 1
+    assert handle.mixfp4_padded_k(70) == 128 and handle.mixfp4_padded_k(4096) == 4096
+
+
+def test_library_has_no_torch_or_libcuda_dependency():
+    import subprocess
+    out = subprocess.run(["ldd", os.path.join(ROOT, "mixfp4_b200", "libmixfp4_b200.so")],
+                         capture_output=True, text=True).stdout
+    assert "libtorch" not in out and "libcuda.so" not in out and "libc10" not in out
+
+
+def test_c_abi_argument_validation_needs_no_gpu():
+    h = nat.lib()
+    one = ctypes.c_void_p(16)  # never dereferenced: validation fails first
+    assert h.mixfp4_amax(None, nat.BF16, 4, 16, 16, one, None) == -1
+    assert h.mixfp4_amax(one, nat.BF16, 0, 16, 16, one, None) == -2
+    assert h.mixfp4_amax(one, 7, 4, 16, 16, one, None) == -4
+    args = [one, nat.BF16, 4, 64, 64, 0, one, one, one, one, one, None, None, None, None, None, 0, None]
+    bad = list(args); bad[0] = None
+    assert h.mixfp4_quantize(*bad) == -1
+    bad = list(args); bad[4] = 32
+    assert h.mixfp4_quantize(*bad) == -2          # ldx < k
+    bad = list(args); bad[5] = 9
+    assert h.mixfp4_quantize(*bad) == -5          # unknown mode
+    bad = list(args); bad[7] = ctypes.c_void_p(20)
+    assert h.mixfp4_quantize(*bad) == -3          # codes not 8-byte aligned
+    assert h.mixfp4_fwht(one, one, nat.BF16, 4, 64, 64, 64, 48, None, 0, None) == -5
+    assert h.mixfp4_gemv(one, 17, 64, one, one, one, one, 8, 64, one, nat.F32, 8, None) == -2
+    assert h.mixfp4_gemv(one, 1, 64, one, one, one, one, 8, 64, one, nat.F16, 8, None) == -4
+    assert h.mixfp4_status_string(-3).decode().startswith("pointer or stride")
+
+
+def test_reference_error_conventions():
+    # project_quant/candidates.py:46-58 and core.py:77-80,105-106; tests/test_quant_core.py:52-53
+    x = torch.zeros((9, 70))
+    with pytest.raises(ValueError, match="fixes scale_group_size=16"):
+        mx.quant_mixfp4_granularity(x, scale_group_size=64)
+    with pytest.raises(TypeError, match="floating point"):
+        mx.quant_mixfp4_granularity(torch.zeros((4, 16), dtype=torch.int32))
+    with pytest.raises(ValueError, match="row dimension"):
+        mx.quant_mixfp4_granularity(torch.zeros(16))
+    with pytest.raises(ValueError, match=r"\[N,K\]"):
+        mx.quant_mixfp4_granularity(torch.zeros((2, 3, 16)))
+    with pytest.raises(ValueError, match="operand_role"):
+        mx.quant_mixfp4_granularity(x, operand_role="bias")
+    with pytest.raises(ValueError, match="unknown selector"):
+        mx.quant_mixfp4_granularity(x, selector="best")
+    with pytest.raises(ValueError, match="unknown scale_rule"):
+        mx.quant_mixfp4_granularity(x, scale_rule="other")
+    with pytest.raises(ValueError, match="N8K64"):
+        mx.quant_mixfp4_granularity(x, selector="output_aware")
+    with pytest.raises(ValueError, match="permutation length"):
+        mx.quant_mixfp4_granularity(x, permutation=torch.arange(3))
+    with pytest.raises(ValueError, match="invalid for"):
+        mx.quant_mixfp4_granularity(x, format_region="n3k7")
+    with pytest.raises(NotImplementedError):
+        mx.quant_mixfp4_granularity(x, format_region="n8k64")
+    with pytest.raises(ValueError, match="unknown transform"):
+        mx.get_transform("H7")
+
+
+def test_packed_byte_accounting():
+    # 4 bits + 8/16 + 1/16 bits per element = 0.5703125 B
+    assert mx.packed_nbytes(4096, 4096) == 9_568_256 + 4
+    assert mx.packed_nbytes(14336, 4096) == 33_488_896 + 4
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    from mixfp4_b200 import build
+    monkeypatch.setattr(nat, "_lib", None)
+    monkeypatch.setattr(build, "LIB_PATH", str(tmp_path / "absent.so"))
+    with pytest.raises(RuntimeError, match="no fallback"):
+        nat.lib()

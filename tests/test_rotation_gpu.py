@@ -1,0 +1,68 @@
+"""GPU parity of the FWHT kernel: bit-exact against fixtures from the reference's
+apply_transform (fp32 and bf16 inputs, whole transform bank, K tails), plus the
+properties the reference tests (tests/test_permutation_rotation.py:121-136)."""
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from mixfp4_b200 import rotation as rot
+from mixfp4_b200 import synth
+from tests.golden_io import rotation_cases
+
+pytestmark = pytest.mark.gpu
+
+
+def _keys():
+    return sorted(k[: -len("__x")] for k in rotation_cases() if k.endswith("__x"))
+
+
+@pytest.mark.parametrize("key", _keys())
+def test_apply_transform_matches_reference(key):
+    z = rotation_cases()
+    name, tag = key.split("__")
+    x, y = z[key + "__x"], z[key + "__y"]
+    if tag.startswith("bf16"):
+        xt = torch.from_numpy(x.view(np.int16).copy()).view(torch.bfloat16).cuda()
+        got = rot.apply_transform(xt, name).cpu().view(torch.int16).numpy().view(np.uint16)
+        assert np.array_equal(got, y)
+    else:
+        got = rot.apply_transform(torch.from_numpy(x.copy()).cuda(), name).cpu().numpy()
+        assert np.array_equal(got.view(np.uint32), y.view(np.uint32))
+
+
+def test_single_rounding_mode_matches_oracle():
+    x = synth.activations(37, 1000, 8, outlier_fraction=0.01)          # K tail of 104
+    got = rot.apply_transform(x.cuda(), "H128", rounding="once").cpu()
+    ref = oracle.f32_to_bf16_bits(oracle.fwht(x.float().numpy(), 128))
+    assert np.array_equal(got.view(torch.int16).numpy().view(np.uint16), ref)
+    assert torch.equal(got[:, 896:], x[:, 896:])                       # tail passes through
+
+
+def test_rotation_dense_equivalence_and_orthogonality():
+    g = torch.Generator().manual_seed(24)
+    x = torch.randn((7, 150), generator=g).cuda()
+    for spec in rot.TRANSFORM_BANK:
+        dense = rot.dense_transform_matrix(spec, 150, device="cuda")
+        torch.testing.assert_close(rot.apply_transform(x, spec), x @ dense, rtol=2e-6, atol=2e-6)
+        torch.testing.assert_close(dense.T @ dense, torch.eye(150, device="cuda"), rtol=2e-6, atol=2e-6)
+
+
+def test_high_precision_rotation_equivalence():
+    g = torch.Generator().manual_seed(25)
+    x = torch.randn((11, 150), generator=g).cuda()
+    w = torch.randn((19, 150), generator=g).cuda()
+    for spec in rot.TRANSFORM_BANK:
+        check = rot.verify_rotation_equivalence(x, w, spec)
+        assert check["passed"], check
+
+
+def test_in_place_and_involution():
+    x = synth.seeded((64, 512), 2).cuda()
+    y = rot.apply_transform(x, "H64")
+    back = rot.apply_transform(y, "H64")                               # H is symmetric orthogonal
+    torch.testing.assert_close(back, x, rtol=1e-5, atol=1e-5)
+    assert rot.fwht(x[:, :128].contiguous()).shape == (64, 128)
+    with pytest.raises(ValueError, match="power of two"):
+        rot.fwht(x[:, :100].contiguous())
