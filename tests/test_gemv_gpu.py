@@ -90,5 +90,6 @@ def test_gemv_property_linearity_full_size():
     lhs, rhs = f(x1 + x2), f(x1) + f(x2)
     assert float((lhs - rhs).norm() / rhs.norm()) <= 1e-5
     rows = slice(7000, 7064)
-    ystar = oracle_linear(x1, w[rows])
+    wq = oracle.bf16_bits_to_f32(oracle.dequant(oracle.quantize(w.float().numpy()), "bf16"))
+    ystar = oracle.linear(x1.float().numpy(), wq[rows])
     assert oracle.relative_l2(f(x1)[:, rows].numpy(), ystar) <= TOL
