@@ -1,0 +1,414 @@
+"""Benchmark of the mixed-FP4 hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (BASELINE config 2): the linear layers of a Llama-3-8B decode step at M=1 --
+32 layers x (q 4096x4096, k/v 1024x4096, o 4096x4096, gate/up 14336x4096, down
+4096x14336) = 224 mixed-FP4 GEMVs over 3.98 GB of packed weights (every weight is a
+distinct buffer, so the working set is ~30x the L2).  One step = one pass over all 224
+layers.  Weights are seeded synthetic Student-t(4) x 0.02 tensors quantized by the CUDA
+quantizer; activations are seeded N(0,1) bf16.
+
+Metric: GEMV HBM GB/s at M=1 = algorithmic bytes (packed weight 0.5703 B/element + bf16
+x + bf16 y) / device time.  `value` is timed with CUDA events around K graph replays with
+all inputs resident; `e2e` is the same pass driven through the public Python API from
+pinned HOST activations (h2d + chained layers + d2h inside the timed region).
+
+With --gpus N > 1 (launched by torch.distributed.run) the same model is tensor-parallel:
+q/k/v/gate/up split along N, o/down along K with an NCCL all-reduce; `value` is the
+whole-job rate (total algorithmic bytes of the full model / max-over-ranks time).
+
+--impl reference times the reference's CPU path (PyTorch eager port of its quantizer +
+fp32 F.linear on the dequantized weight, all host threads) on a bounded sample of the same
+workload (one of the 32 layers per step).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "mixed-FP4 linear: GEMV HBM GB/s @M=1 (Llama-3-8B decode linears)"
+UNIT = "GB/s"
+FALLBACK_HBM_GBS = 6650.0
+
+
+def layer_list():
+    from mixfp4_b200 import synth
+    out = []
+    for name, n, k, count in synth.LLAMA3_8B_LAYERS:
+        for i in range(count):
+            out.append((f"{name}{i}" if count > 1 else name, n, k))
+    return out, synth.LLAMA3_8B_NUM_LAYERS
+
+
+def algorithmic_bytes(n: int, k: int, m: int, out_bytes: int = 2) -> int:
+    from mixfp4_b200.quant import packed_nbytes
+    return packed_nbytes(n, k) + 2 * m * k + out_bytes * m * n
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index: int = 0):
+        self.index = index
+        self.rows: list[str] = []
+        self.proc = None
+
+    def start(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for row in self.rows:
+            parts = [p.strip() for p in row.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------- GPU arm
+def build_model(device, rank: int, world: int, m: int):
+    """Quantize the (sharded) synthetic 8B linear stack on the device.  Returns a list of
+    layers, each a dict name -> (PackedWeight, kind)."""
+    import mixfp4_b200 as mx
+    layers, nlayers = layer_list()
+    gen = torch.Generator(device=device)
+    model = []
+    for li in range(nlayers):
+        entry = {}
+        for idx, (name, n, k) in enumerate(layers):
+            gen.manual_seed(1000 * li + idx)
+            # Student-t(4) = z / sqrt(chi2_4 / 4), drawn on the device (7e9 elements in total)
+            z = torch.randn((n, k), generator=gen, device=device)
+            chi = torch.zeros((n, k), device=device)
+            for _ in range(4):
+                d = torch.randn((n, k), generator=gen, device=device)
+                chi.addcmul_(d, d)
+            w = (z / torch.sqrt(chi / 4) * 0.02).to(torch.bfloat16)
+            del z, chi
+            row_parallel = name in ("o", "down")
+            amax = mx.tensor_amax(w)
+            if world > 1:
+                if row_parallel:       # split K
+                    step = k // world
+                    w = w[:, rank * step:(rank + 1) * step].contiguous()
+                else:                  # split N
+                    step = n // world
+                    w = w[rank * step:(rank + 1) * step].contiguous()
+            packed, _, _ = mx.quantize_packed(w, amax=amax)
+            entry[name] = packed
+            del w
+        model.append(entry)
+    torch.cuda.synchronize(device)
+    return model
+
+
+def decode_pass(model, h, world: int, out_dtype=torch.bfloat16):
+    """One token through all linears, chained the way a decoder layer chains them
+    (attention, norms and activation functions are not part of this path and are skipped)."""
+    import torch.distributed as dist
+    import mixfp4_b200 as mx
+    x, out = h, None
+    for layer in model:
+        # every layer starts from the same input so that 32 chained layers of random weights
+        # stay finite; inside a layer the seven linears keep their data dependencies
+        q = mx.mixfp4_linear(x, layer["q"])
+        mx.mixfp4_linear(x, layer["kv0"])
+        mx.mixfp4_linear(x, layer["kv1"])
+        o = mx.mixfp4_linear(q, layer["o"])
+        if world > 1:
+            dist.all_reduce(o)
+        g = mx.mixfp4_linear(o, layer["gate_up0"])
+        mx.mixfp4_linear(o, layer["gate_up1"])
+        out = mx.mixfp4_linear(g, layer["down"])
+        if world > 1:
+            dist.all_reduce(out)
+    return out
+
+
+def run_ours(args):
+    import torch.distributed as dist
+    import mixfp4_b200 as mx
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    m = args.m
+    layers, nlayers = layer_list()
+    total_bytes = nlayers * sum(algorithmic_bytes(n, k, m) for _, n, k in layers)
+    launches_per_step = nlayers * len(layers)
+
+    model = build_model(dev, rank, world, m)
+    x_host = torch.randn((m, 4096), generator=torch.Generator().manual_seed(7)).to(torch.bfloat16).pin_memory()
+    x_dev = x_host.to(dev)
+    out_host = torch.empty((m, 4096), dtype=torch.bfloat16).pin_memory()
+
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        static_out = decode_pass(model, x_dev, world)          # warm-up outside capture
+        torch.cuda.synchronize(dev)
+        with torch.cuda.graph(graph, stream=side):
+            static_out = decode_pass(model, x_dev, world)
+    torch.cuda.synchronize(dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    # ---- device-resident timing: K graph replays
+    for _ in range(max(args.warmup, 3)):
+        graph.replay()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    e1.record()
+    barrier()
+    dev_ms = e0.elapsed_time(e1) / args.steps
+
+    # ---- end to end: pinned host x -> device, replay, device -> pinned host, every step
+    for _ in range(3):
+        x_dev.copy_(x_host, non_blocking=True); graph.replay(); out_host.copy_(static_out, non_blocking=True)
+    barrier()
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2.record()
+    for _ in range(args.steps):
+        x_dev.copy_(x_host, non_blocking=True)
+        graph.replay()
+        out_host.copy_(static_out, non_blocking=True)
+        torch.cuda.current_stream(dev).synchronize()
+    e3.record()
+    barrier()
+    e2e_ms = e2.elapsed_time(e3) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+
+    if world > 1:
+        t = torch.tensor([dev_ms, e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dev_ms, e2e_ms = t.tolist()
+
+    extra = {}
+    if rank == 0 and world == 1 and not args.no_extra:
+        extra = secondary_numbers(dev)
+
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        value = total_bytes / (dev_ms * 1e-3) / 1e9
+        per_gpu = value / world
+        line = {
+            "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": round(dev_ms, 4), "higher_is_better": True,
+            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "impl": "ours",
+            "config": {"workload": "llama3-8b decode linears, M=%d, 32 layers x 7 GEMVs, mixed E2M1/E0M3 K16 blocks" % m,
+                       "parallelism": "tp%d" % world if world > 1 else "single",
+                       "l2": "working set 3.98 GB of distinct weights >> 126 MB L2 (no flush needed)",
+                       "timing": "cuda events around graph replays, max over ranks"},
+            "clocks": clocks,
+            "e2e": {"value": round(total_bytes / (e2e_ms * 1e-3) / 1e9, 1), "unit": UNIT,
+                    "ms_per_step": round(e2e_ms, 4), "h2d_bytes_per_step": x_host.numel() * 2,
+                    "d2h_bytes_per_step": out_host.numel() * 2},
+            "gpu_launches": launches_per_step * args.steps,
+            "roofline": {"bound": "hbm", "achieved": round(per_gpu, 1), "peak": peak, "unit": "GB/s",
+                         "frac": round(per_gpu / peak, 4), "peak_kind": peak_kind, "kernel": "gemv_async_kernel",
+                         "traffic": None,
+                         "note": "achieved = algorithmic bytes of the %d GEMV launches of a step / CUDA-event time" % launches_per_step},
+            "cpu_baseline": cpu_baseline(m, budget_s=12.0) if world == 1 and not args.no_cpu else None,
+            "extra": extra,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def secondary_numbers(dev) -> dict:
+    """Other kernels of the path, device-timed on inputs larger than L2: the quantizer and
+    the prefill GEMM at M=4096 (reported beside the headline, not part of `value`)."""
+    import mixfp4_b200 as mx
+    out = {}
+
+    def timeit(fn, iters):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(dev)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize(dev)
+        return a.elapsed_time(b) / iters * 1e-3
+
+    ws = [(torch.randn((14336, 4096), device=dev) * 0.02).to(torch.bfloat16) for _ in range(4)]  # 470 MB
+    state = {"i": 0}
+
+    def quant():
+        state["i"] = (state["i"] + 1) % len(ws)
+        mx.quantize_packed(ws[state["i"]])
+
+    t = timeit(quant, 12)
+    n, k = 14336, 4096
+    out["quantize_gbs"] = round((2 * n * k + mx.packed_nbytes(n, k)) / t / 1e9, 1)
+    out["quantize_ms_14336x4096"] = round(t * 1e3, 4)
+    try:
+        packed = mx.quantize_packed(ws[0][:4096])[0]
+        x = torch.randn((4096, 4096), device=dev).to(torch.bfloat16)
+        t = timeit(lambda: mx.mixfp4_linear(x, packed), 10)
+        out["gemm_tflops_m4096_4096x4096"] = round(2 * 4096 ** 3 / t / 1e12, 1)
+    except Exception as exc:  # the tensor-core kernel may not be built yet
+        out["gemm_tflops_m4096_4096x4096"] = None
+        out["gemm_note"] = str(exc)[:120]
+    return out
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_layer_sample(m: int):
+    """One decoder layer's seven weights (seeded, CPU) quantized by the eager-op port of the
+    reference quantizer; returns (fp32 dequantized weights, activations, quantize seconds)."""
+    from mixfp4_b200 import synth
+    from oracle import torch_port
+    layers, _ = layer_list()
+    torch.set_num_threads(os.cpu_count() or 1)
+    ws, t_quant, elems = [], 0.0, 0
+    for idx, (name, n, k) in enumerate(layers):
+        w = (torch.randn((n, k), generator=torch.Generator().manual_seed(idx)) * 0.02).to(torch.bfloat16)
+        t0 = time.perf_counter()
+        dq = torch_port.quantize_dequant(w)
+        t_quant += time.perf_counter() - t0
+        elems += n * k
+        ws.append(dq.float())
+    xs = {k: torch.randn((m, k), generator=torch.Generator().manual_seed(99)).to(torch.bfloat16)
+          for k in (4096, 14336)}
+    return ws, xs, t_quant, elems
+
+
+def cpu_linear_step(ws, xs):
+    from oracle import torch_port
+    for w in ws:
+        torch_port.linear(xs[w.shape[1]], w)
+
+
+def cpu_baseline(m: int, budget_s: float = 12.0) -> dict:
+    layers, _ = layer_list()
+    ws, xs, t_quant, elems = cpu_layer_sample(m)
+    cpu_linear_step(ws, xs)
+    reps, t0 = 0, time.perf_counter()
+    while True:
+        cpu_linear_step(ws, xs)
+        reps += 1
+        if time.perf_counter() - t0 > max(1.0, budget_s - t_quant) or reps >= 200:
+            break
+    t_lin = (time.perf_counter() - t0) / reps
+    layer_bytes = sum(algorithmic_bytes(n, k, m) for _, n, k in layers)
+    return {"value": round(layer_bytes / t_lin / 1e9, 2), "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
+            "sample": "1 of 32 layers (7 linears, 218M weights): eager-op port of the reference quantizer once "
+                      "(%.2f s, %.1f M elements/s) + %d passes of fp32 F.linear on the dequantized weights"
+                      % (t_quant, elems / t_quant / 1e6, reps),
+            "quantize_melem_per_s": round(elems / t_quant / 1e6, 1), "linear_ms_per_layer": round(t_lin * 1e3, 3)}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    m = args.m
+    layers, _ = layer_list()
+    ws, xs, t_quant, elems = cpu_layer_sample(m)
+    for _ in range(max(args.warmup, 1)):
+        cpu_linear_step(ws, xs)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_linear_step(ws, xs)
+    ms = (time.perf_counter() - t0) / args.steps * 1e3
+    layer_bytes = sum(algorithmic_bytes(n, k, m) for _, n, k in layers)
+    value = round(layer_bytes / (ms * 1e-3) / 1e9, 2)
+    sample = ("each step = 1 of the 32 layers (7 fp32 F.linear calls on dequantized weights, %d host threads); "
+              "weights quantized once by the eager-op port of the reference quantizer in %.2f s" % (os.cpu_count(), t_quant))
+    print(json.dumps({
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": int(os.environ.get("WORLD_SIZE", "1")),
+        "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": round(ms, 3), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "impl": "reference",
+        "config": {"workload": "llama3-8b decode linears, M=%d, CPU sample of 1/32 of the model per step" % m},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": os.cpu_count(), "kind": "port", "sample": sample,
+                         "quantize_melem_per_s": round(elems / t_quant / 1e6, 1)},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--m", type=int, default=1, help="decode batch (1..16)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-extra", action="store_true", help="skip the secondary kernel numbers")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -108,3 +108,21 @@ def test_full_size_digests(name):
     assert sha(oracle.dequant(p, "bf16")) == info["dequant_sha256"]
     assert int(np.float32(p.global_scale).view(np.uint32)) == info["global_scale_bits"]
     assert int(p.format_ids().sum()) == info["e0_blocks"]
+
+
+def test_torch_port_matches_c_oracle():
+    """The eager-op port that the benchmark times produces the same bytes as the C oracle."""
+    import torch
+    from mixfp4_b200 import synth
+    from oracle import torch_port
+
+    for w in (synth.student_t_weight(96, 400, 4), synth.seeded((17, 79), 3), synth.gaussian_outlier_weight(64, 256, 2)):
+        out, parts = torch_port.quantize_dequant(w, return_parts=True)
+        p = oracle.quantize(w.float().numpy(), stats=True)
+        assert np.array_equal(parts["format_ids"].numpy(), p.format_ids())
+        assert np.array_equal(parts["e2_errors"].numpy().view(np.uint32), p.e2_errors.view(np.uint32))
+        assert np.array_equal(parts["e0_errors"].numpy().view(np.uint32), p.e0_errors.view(np.uint32))
+        assert np.array_equal(parts["scales"].numpy(), p.selected_scales())
+        ref = oracle.dequant(p, "bf16" if w.dtype == torch.bfloat16 else "f32")
+        got = out.view(torch.int16).numpy().view(np.uint16) if w.dtype == torch.bfloat16 else out.numpy()
+        assert np.array_equal(got.reshape(-1), ref.reshape(-1))
