@@ -1,0 +1,53 @@
+// Packed-code decode shared by the GEMV and GEMM kernels.
+//
+// A 256-entry table (4 KB, built per launch from the tensor scale) maps
+// (format bit << 7 | E4M3 scale byte) to the block's eight magnitudes
+// bf16((level * scale) * global) -- bit-identical to the reference's dequantized weight
+// (project_quant/scale.py:59 followed by the bf16 cast of core.py:143) -- stored as 8 low
+// bytes (x, y) and 8 high bytes (z, w).  Eight 4-bit codes become four bf16x2 registers
+// with byte permutes only.
+#pragma once
+
+#include "common.cuh"
+
+namespace mixfp4 {
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+
+// One table entry: the eight bf16 magnitudes of a block as low bytes (x, y) / high bytes (z, w).
+__device__ __forceinline__ uint4 make_lut_entry(uint32_t scale_byte, bool e0m3, float gs) {
+    const float sc = e4m3_to_float(scale_byte);
+    uint32_t lo[2] = {0, 0}, hi[2] = {0, 0};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const float v = __fmul_rn(__fmul_rn(level_value(j, e0m3), sc), gs);
+        const uint32_t bits = __bfloat16_as_ushort(__float2bfloat16_rn(v));
+        lo[j >> 2] |= (bits & 0xffu) << (8 * (j & 3));
+        hi[j >> 2] |= (bits >> 8) << (8 * (j & 3));
+    }
+    return make_uint4(lo[0], lo[1], hi[0], hi[1]);
+}
+
+// Eight codes (nibble j = element j) -> four bf16x2 registers (elements 01, 23, 45, 67).
+__device__ __forceinline__ void decode8(uint32_t w, const uint4& t, uint32_t (&p)[4]) {
+    const uint32_t mag = w & 0x77777777u;
+    const uint32_t mag_hi = mag >> 16;
+    const uint32_t w4 = w << 4;
+    uint32_t lo_a = prmt(t.x, t.y, mag), hi_a = prmt(t.z, t.w, mag);
+    uint32_t lo_b = prmt(t.x, t.y, mag_hi), hi_b = prmt(t.z, t.w, mag_hi);
+    // byte i of sign_a is 0xFF iff element i is negative (selector nibble 8+j = replicate the
+    // top bit of byte j of {w, w4}); same for elements 4..7 in sign_b
+    const uint32_t sign_a = prmt(w, w4, 0x9D8Cu), sign_b = prmt(w, w4, 0xBFAEu);
+    hi_a |= sign_a & 0x80808080u;
+    hi_b |= sign_b & 0x80808080u;
+    p[0] = prmt(lo_a, hi_a, 0x5140u);
+    p[1] = prmt(lo_a, hi_a, 0x7362u);
+    p[2] = prmt(lo_b, hi_b, 0x5140u);
+    p[3] = prmt(lo_b, hi_b, 0x7362u);
+}
+
+}  // namespace mixfp4

@@ -1,10 +1,459 @@
-// Prefill-shape dequant-linear (tcgen05).  Placeholder until the tensor-core kernel lands:
-// the entry points exist so that the ABI is complete, and report MIXFP4_E_UNSUPPORTED.
+// Prefill-shape dequant-linear on the Blackwell tensor cores:
+//   y[M,N] = x[M,K] * W[N,K]^T,  x bf16, W packed mixed-FP4, fp32 accumulation in TMEM.
+// Replaces F.linear on the dequantized weight (project_quant/modeling.py:629) and, with
+// rotation_block = 128, the activation pre-hook (modeling.py:662-668).
+//
+// Tile: one CTA computes a 128 (M) x 128 (N) tile, K in steps of 64.  Warp roles:
+//   warp 0      TMA producer: one lane issues cp.async.bulk.tensor.2d loads of the x tile
+//               (128 rows x 64 bf16, 128-byte swizzle) into a 6-stage shared-memory ring.
+//   warp 1      MMA issuer: allocates 128 TMEM columns, then one lane issues four
+//               tcgen05.mma.cta_group::1.kind::f16 (128x128x16, bf16 x bf16 -> fp32) per
+//               stage and commits the stage's "empty" barrier; after the last K step it
+//               commits the accumulator barrier.
+//   warps 2-9   weight transcoders, then epilogue.  Each thread owns half a row of the
+//               128 x 64 weight tile: it loads 16 B of codes, 2 scale bytes and the format
+//               byte straight from global memory one K step ahead, decodes them with the
+//               shared (format, scale) -> bf16 table into exactly the reference's
+//               dequantized bf16 values and writes them into the K-major 128B-swizzled
+//               operand layout tcgen05 reads (conflict-free 16-byte stores), fences the
+//               async proxy and arrives on the stage's "full" barrier.  At the end the
+//               same warps read the accumulator with tcgen05.ld and store y.
+// Every mbarrier wait is bounded (wall-clock limit); on expiry the kernel records a code
+// in the caller's status word, stops issuing work, waits for its own TMA loads, frees
+// TMEM and returns.
+//
+// Tensor-pipe roofline: 2*M*N*K flops against the measured dense bf16 peak.  The weight
+// tile is transcoded once per CTA, i.e. N*K elements are decoded M/128 times over.
+
+#include <cuda.h>
+#include <stdlib.h>
+
 #include "common.cuh"
+#include "decode.cuh"
 
-extern "C" int64_t mixfp4_gemm_workspace_bytes(int64_t, int64_t, int64_t) { return 0; }
+namespace mixfp4 {
+namespace {
 
-extern "C" int mixfp4_gemm(const void*, int64_t, int64_t, const uint8_t*, const uint8_t*, const uint8_t*,
-                           const float*, int64_t, int64_t, int, void*, int, int64_t, void*, int64_t, int*, void*) {
-    return MIXFP4_E_UNSUPPORTED;
+constexpr int BM = 128, BN = 128, BK = 64;
+constexpr int kStages = 6;
+constexpr int kDecodeWarps = 8;
+constexpr int kThreads = (2 + kDecodeWarps) * 32;
+constexpr uint32_t kABytes = BM * BK * 2, kBBytes = BN * BK * 2;
+constexpr uint32_t kTmemCols = 128;
+constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s: far beyond any legitimate wait
+
+// shared-memory map (offsets from a 1024-aligned base)
+constexpr uint32_t kOffA = 0;
+constexpr uint32_t kOffB = kStages * kABytes;
+constexpr uint32_t kOffLut = kOffB + kStages * kBBytes;
+constexpr uint32_t kOffBar = kOffLut + 4096;                 // full_a[S] full_b[S] empty[S] accum
+constexpr uint32_t kOffMisc = kOffBar + (3 * kStages + 1) * 8;   // tmem base, abort flag
+constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;        // + alignment slack
+
+struct GemmArgs {
+    const uint8_t* codes;
+    const uint8_t* scales;
+    const uint8_t* fmt;
+    const float* global_scale;
+    int64_t m, n, k, kpad;
+    void* y;
+    int out_dtype;
+    int64_t ldy;
+    int* status;
+};
+
+// ------------------------------------------------------------------------- PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+struct WaitCtx {
+    volatile int* abort_flag;   // shared memory
+    int* status;                // global, may be null
+};
+
+// Bounded wait: false if the limit expired or another thread of the CTA already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 63u) == 0) {
+            if (*ctx.abort_flag) return false;
+            if (global_timer_ns() - t0 > kWaitLimitNs) {
+                *ctx.abort_flag = 1;
+                if (ctx.status) atomicCAS(ctx.status, 0, code);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+
+// D[tmem] (+)= A[smem desc] * B[smem desc], bf16 inputs, fp32 accumulate.
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// mbarrier arrive once all previously issued tcgen05.mma of this thread have completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 32 TMEM lanes x 32 columns of 32-bit: thread i of the warp gets lane base+i, columns c..c+31.
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major bf16 tile with 128-byte swizzle: rows are
+// 128 B apart inside an 8-row group, groups 1024 B apart (stride byte offset), descriptor
+// version 1 (sm_100), layout type 2 (SWIZZLE_128B).  The tile base must be 1024-aligned;
+// a K step of 16 elements advances the start address by 32 B.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+    const uint64_t lo = ((saddr & 0x3ffffu) >> 4) | (1ull << 16);
+    const uint64_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+    return lo | (hi << 32);
+}
+
+// Instruction descriptor, kind::f16: D fp32 (bits 4-5 = 1), A and B bf16 (bits 7-9, 10-12 = 1),
+// both K-major (bits 15, 16 = 0), N >> 3 at bits 17-22, M >> 4 at bits 24-28.
+constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                                ((uint32_t)(BM >> 4) << 24);
+
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint4 lds128_lut(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
+// ------------------------------------------------------------------------------ kernel
+__global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
+                                                           const GemmArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* gen = smem_raw + (base - raw);            // generic pointer to the aligned base
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+    const int num_kt = static_cast<int>(a.kpad / BK);
+
+    auto full_a = [&](int s) { return base + kOffBar + 8u * s; };
+    auto full_b = [&](int s) { return base + kOffBar + 8u * (kStages + s); };
+    auto empty = [&](int s) { return base + kOffBar + 8u * (2 * kStages + s); };
+    const uint32_t accum_bar = base + kOffBar + 8u * (3 * kStages);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + kOffMisc);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + kOffMisc + 4);
+    const WaitCtx ctx{abort_flag, a.status};
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(full_a(s), 1);
+            mbar_init(full_b(s), kDecodeWarps);
+            mbar_init(empty(s), 1);
+        }
+        mbar_init(accum_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_proxy();
+    }
+    if (warp == 1) tmem_alloc(base + kOffMisc, kTmemCols);
+    if (warp >= 2) {   // the (format, scale) -> magnitudes table: 256 entries, 256 transcoder threads
+        const int e = threadIdx.x - 64;
+        reinterpret_cast<uint4*>(gen + kOffLut)[e] = make_lut_entry(e & 127, e >> 7, *a.global_scale);
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            int issued = 0;
+            for (int kt = 0; kt < num_kt; ++kt) {
+                const int s = kt % kStages;
+                const uint32_t ph = (kt / kStages) & 1;
+                if (!mbar_wait(empty(s), ph ^ 1, ctx, 1)) break;
+                mbar_arrive_expect_tx(full_a(s), kABytes);
+                tma_load_2d(base + kOffA + s * kABytes, &tmap_x, full_a(s), kt * BK, (int)m0);
+                issued = kt + 1;
+            }
+            // never leave with a bulk copy still writing into this CTA's shared memory
+            for (int kt = max(0, issued - kStages); kt < issued; ++kt)
+                if (!mbar_wait(full_a(kt % kStages), (kt / kStages) & 1, ctx, 2)) break;
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            bool ok = true;
+            for (int kt = 0; kt < num_kt && ok; ++kt) {
+                const int s = kt % kStages;
+                const uint32_t ph = (kt / kStages) & 1;
+                ok = mbar_wait(full_a(s), ph, ctx, 3) && mbar_wait(full_b(s), ph, ctx, 4);
+                if (!ok) break;
+                tcgen05_fence_after();
+                const uint64_t da = make_smem_desc(base + kOffA + s * kABytes);
+                const uint64_t db = make_smem_desc(base + kOffB + s * kBBytes);
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k)      // +32 B per K step of 16: +2 in the address field
+                    umma_bf16(tmem_base, da + 2u * k, db + 2u * k, kInstrDesc, (kt | k) != 0 ? 1u : 0u);
+                umma_commit(empty(s));                  // frees the stage when these MMAs are done
+            }
+            if (ok) umma_commit(accum_bar);
+        }
+    } else {
+        // -------------------------------------------------- weight transcoders / epilogue
+        const int dt = threadIdx.x - 64;                // 0..255
+        const int row = dt & 127, half = dt >> 7;       // tile row, which 32-element half of the K step
+        const uint32_t last_row = (uint32_t)a.n - 1;
+        const uint32_t grow = min(n0 + row, last_row);  // rows past N re-read the last row; never stored
+        const uint8_t* cptr = a.codes + (size_t)grow * (a.kpad / 2) + half * 16;
+        const uint8_t* sptr = a.scales + (size_t)grow * (a.kpad / 16) + half * 2;
+        const uint8_t* fptr = a.fmt + (size_t)grow * (a.kpad / 128);
+        const uint32_t lut_base = base + kOffLut;
+        // destination of this thread's four 16-byte chunks: row r, logical chunk c -> c ^ (r & 7)
+        const uint32_t row_off = (row >> 3) * 1024u + (row & 7) * 128u;
+        const uint32_t sw = row & 7;
+
+        uint4 codes = __ldg(reinterpret_cast<const uint4*>(cptr));
+        uint32_t sc2 = __ldg(reinterpret_cast<const unsigned short*>(sptr));
+        uint32_t fb = __ldg(fptr);
+        bool ok = true;
+        for (int kt = 0; kt < num_kt; ++kt) {
+            const int s = kt % kStages;
+            const uint32_t ph = (kt / kStages) & 1;
+            uint4 ncodes = codes;
+            uint32_t nsc2 = sc2, nfb = fb;
+            if (kt + 1 < num_kt) {                      // next K step's packed data, one step ahead
+                ncodes = __ldg(reinterpret_cast<const uint4*>(cptr + (size_t)(kt + 1) * 32));
+                nsc2 = __ldg(reinterpret_cast<const unsigned short*>(sptr + (size_t)(kt + 1) * 4));
+                nfb = __ldg(fptr + ((kt + 1) >> 1));
+            }
+            ok = mbar_wait(empty(s), ph ^ 1, ctx, 5);
+            if (!ok) break;
+            const uint32_t dst = base + kOffB + s * kBBytes + row_off;
+            const uint32_t fbits = fb >> ((kt & 1) * 4 + half * 2);     // this thread's 2 blocks
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+                const uint32_t idx = (((fbits >> b) & 1u) << 7) | ((sc2 >> (8 * b)) & 0x7fu);
+                const uint4 tab = lds128_lut(lut_base + idx * 16);
+#pragma unroll
+                for (int w = 0; w < 2; ++w) {
+                    const int i = 2 * b + w;
+                    uint32_t p[4];
+                    decode8(i == 0 ? codes.x : i == 1 ? codes.y : i == 2 ? codes.z : codes.w, tab, p);
+                    const uint32_t chunk = (uint32_t)(half * 4 + i) ^ sw;
+                    sts128(dst + chunk * 16, p[0], p[1], p[2], p[3]);
+                }
+            }
+            fence_async_proxy();                        // generic-proxy stores -> visible to tcgen05
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full_b(s));
+            codes = ncodes; sc2 = nsc2; fb = nfb;
+        }
+
+        // epilogue: TMEM lane quarter = warp % 4 (hardware rule), column half by warp group
+        if (ok && mbar_wait(accum_bar, 0, ctx, 6)) {
+            tcgen05_fence_after();
+            const int q = warp & 3, ch = (warp - 2) >> 2;
+            const int64_t mrow = (int64_t)m0 + q * 32 + lane;
+#pragma unroll 1
+            for (int c = 0; c < 2; ++c) {
+                const int col0 = ch * 64 + c * 32;
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)col0, r);
+                const int64_t ncol = (int64_t)n0 + col0;
+                if (mrow < a.m && ncol < a.n) {
+                    const bool full = ncol + 32 <= a.n;
+                    if (a.out_dtype == MIXFP4_F32) {
+                        float* out = static_cast<float*>(a.y) + mrow * a.ldy + ncol;
+                        if (full && (a.ldy & 3) == 0 && (reinterpret_cast<uintptr_t>(a.y) & 15) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                reinterpret_cast<uint4*>(out)[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (ncol + j < a.n) out[j] = __uint_as_float(r[j]);
+                        }
+                    } else {
+                        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(a.y) + mrow * a.ldy + ncol;
+                        uint32_t pk[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                            pk[j] = *reinterpret_cast<const uint32_t*>(&v);
+                        }
+                        if (full && (a.ldy & 7) == 0 && (reinterpret_cast<uintptr_t>(a.y) & 15) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                reinterpret_cast<uint4*>(out)[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (ncol + j < a.n)
+                                    out[j] = __ushort_as_bfloat16((unsigned short)((pk[j >> 1] >> (16 * (j & 1))) & 0xffffu));
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+int64_t x_staging_bytes(int64_t m, int64_t k) { return m * ((k + 7) / 8 * 8) * 2; }
+
+}  // namespace
+}  // namespace mixfp4
+
+using namespace mixfp4;
+
+extern "C" int64_t mixfp4_gemm_workspace_bytes(int64_t m, int64_t /*n*/, int64_t k) {
+    if (m <= 0 || k <= 0) return 0;
+    return (x_staging_bytes(m, k) + 255) / 256 * 256;
+}
+
+extern "C" int mixfp4_gemm(const void* x, int64_t m, int64_t ldx, const uint8_t* codes, const uint8_t* scales,
+                           const uint8_t* fmt, const float* global_scale, int64_t n, int64_t k, int rotation_block,
+                           void* y, int out_dtype, int64_t ldy, void* workspace, int64_t workspace_bytes,
+                           int* status, void* stream) {
+    if (!x || !codes || !scales || !fmt || !global_scale || !y) return MIXFP4_E_NULL;
+    if (m <= 0 || n <= 0 || k <= 0 || ldx < k || ldy < n) return MIXFP4_E_SHAPE;
+    if (m > 0x7fffffffLL || n > 0x7fffffffLL || k > 0x7fffffffLL) return MIXFP4_E_SHAPE;
+    if (out_dtype != MIXFP4_F32 && out_dtype != MIXFP4_BF16) return MIXFP4_E_DTYPE;
+    if (rotation_block != 0 && rotation_block != 128) return MIXFP4_E_MODE;
+    if (!aligned(codes, 16) || !aligned(scales, 2)) return MIXFP4_E_ALIGN;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+    // The TMA descriptor needs a 16-byte aligned base and row pitch; the rotation needs a
+    // place to put bf16(H128 x).  Both go through the caller's workspace.
+    const void* xa = x;
+    int64_t lda = ldx;
+    const bool tma_ok = aligned(x, 16) && (ldx % 8 == 0);
+    if (rotation_block == 128 || !tma_ok) {
+        const int64_t need = x_staging_bytes(m, k);
+        if (!workspace || workspace_bytes < need) return MIXFP4_E_WORKSPACE;
+        if (!aligned(workspace, 16)) return MIXFP4_E_ALIGN;
+        lda = (k + 7) / 8 * 8;
+        if (rotation_block == 128) {
+            const int rc = mixfp4_fwht(x, workspace, MIXFP4_BF16, m, k, ldx, lda, 128, nullptr, 0, stream);
+            if (rc != MIXFP4_OK) return rc;
+        } else {
+            MIXFP4_CUDA_CHECK(cudaMemcpy2DAsync(workspace, lda * 2, x, ldx * 2, k * 2, m, cudaMemcpyDeviceToDevice, st));
+        }
+        xa = workspace;
+    }
+
+    EncodeTiledFn encode = encode_tiled_fn();
+    if (!encode) return record_error_text("cuTensorMapEncodeTiled is not available from the driver");
+    CUtensorMap tmap;
+    const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)m};
+    const cuuint64_t strides[1] = {(cuuint64_t)lda * 2};
+    const cuuint32_t box[2] = {BK, BM};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult cr = encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(xa), dims, strides, box,
+                               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) return record_error_text("cuTensorMapEncodeTiled failed");
+
+    static bool configured = false;
+    if (!configured) {
+        MIXFP4_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+        configured = true;
+    }
+    GemmArgs a;
+    a.codes = codes; a.scales = scales; a.fmt = fmt; a.global_scale = global_scale;
+    a.m = m; a.n = n; a.k = k; a.kpad = padded_k(k);
+    a.y = y; a.out_dtype = out_dtype; a.ldy = ldy; a.status = status;
+    const dim3 grid((unsigned)((n + BN - 1) / BN), (unsigned)((m + BM - 1) / BM));
+    if (grid.y > 65535) return MIXFP4_E_SHAPE;
+    gemm_kernel<<<grid, kThreads, kSmemBytes, st>>>(tmap, a);
+    return check_launch("gemm_kernel");
 }

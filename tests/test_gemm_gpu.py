@@ -1,0 +1,111 @@
+"""GPU parity of the prefill-shape dequant-linear (mixfp4_gemm, tcgen05) through the C ABI.
+
+Oracle: y* = x.float() @ dequant.float().T with the reference's bf16 dequantized weight
+(double accumulation).  Tolerance: relative Frobenius error <= 1e-3 on fp32 outputs; bf16
+outputs within one bf16 ulp of y*.  With the H128 rotation the oracle activation is
+bf16(FWHT_fp32(x)) (one rounding) and the weight is quantized after the reference's own
+bf16 rotation."""
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import mixfp4_b200 as mx
+from mixfp4_b200 import linear as mxl
+from mixfp4_b200 import synth
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3
+
+
+def dequant_oracle(w: torch.Tensor) -> np.ndarray:
+    return oracle.bf16_bits_to_f32(oracle.dequant(oracle.quantize(w.float().numpy()), "bf16"))
+
+
+@pytest.mark.parametrize("m,n,k", [
+    (128, 128, 64), (128, 128, 128), (128, 128, 512), (256, 256, 1024), (17, 128, 256), (160, 50, 70),
+    (300, 200, 131), (129, 257, 1000), (512, 1024, 4096), (384, 128, 14336),
+])
+def test_gemm_matches_oracle(m, n, k):
+    w = synth.student_t_weight(n, k, seed=n + k)
+    x = synth.activations(m, k, seed=m, outlier_fraction=0.01)
+    packed, _, _ = mx.quantize_packed(w.cuda())
+    y = mx.mixfp4_linear(x.cuda(), packed, out_dtype=torch.float32)
+    assert mxl.gemm_status() == 0
+    ystar = oracle.linear(x.float().numpy(), dequant_oracle(w))
+    assert y.shape == (m, n)
+    assert oracle.relative_l2(y.cpu().numpy(), ystar) <= TOL
+
+
+def test_gemm_fp32_accumulation_is_tight():
+    w, x = synth.config1(0, n=256, k=4096, m=256)
+    packed, _, _ = mx.quantize_packed(w.cuda())
+    y = mx.mixfp4_linear(x.cuda(), packed, out_dtype=torch.float32).cpu().numpy()
+    assert oracle.relative_l2(y, oracle.linear(x.float().numpy(), dequant_oracle(w))) <= 5e-6
+
+
+def test_gemm_bf16_output_within_one_ulp():
+    w = synth.student_t_weight(256, 512, 5)
+    x = synth.activations(200, 512, 6)
+    packed, _, _ = mx.quantize_packed(w.cuda())
+    y = mx.mixfp4_linear(x.cuda(), packed).float().cpu().numpy()
+    ystar = oracle.linear(x.float().numpy(), dequant_oracle(w))
+    assert np.all(np.abs(y - ystar) <= np.abs(ystar) * 2.0 ** -7 + 1e-30)
+
+
+def test_gemm_agrees_with_gemv_rows():
+    """The two kernels decode the same weights: a GEMM row equals the GEMV of that row up to
+    fp32 summation order."""
+    w = synth.student_t_weight(512, 2048, 11)
+    x = synth.activations(130, 2048, 12)
+    packed, _, _ = mx.quantize_packed(w.cuda())
+    big = mx.mixfp4_linear(x.cuda(), packed, out_dtype=torch.float32)
+    small = mx.mixfp4_linear(x[:16].cuda(), packed, out_dtype=torch.float32)
+    assert float((big[:16] - small).norm() / small.norm()) <= 1e-5
+
+
+def test_gemm_unaligned_x_uses_workspace():
+    w = synth.student_t_weight(128, 200, 7)
+    packed, _, _ = mx.quantize_packed(w.cuda())
+    base = synth.activations(150, 260, 8).cuda()
+    x = base[:, 3:203]                                   # unaligned start, pitch not 16-byte
+    y = mx.mixfp4_linear(x, packed, out_dtype=torch.float32).cpu().numpy()
+    ystar = oracle.linear(x.float().cpu().numpy(), dequant_oracle(w))
+    assert oracle.relative_l2(y, ystar) <= TOL
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 384, 1024), (130, 100, 640)])
+def test_gemm_with_online_h128_rotation(m, n, k):
+    """Config 3: weights rotated offline (the reference's bf16 FWHT), then quantized;
+    activations with outlier channels rotated on the fly."""
+    w = synth.student_t_weight(n, k, 21)
+    x = synth.activations(m, k, 22, outlier_fraction=0.01)
+    lin = torch.nn.Linear(k, n, bias=False)
+    lin.weight.data = w
+    layer = mx.MixFP4Linear.from_linear(lin, rotation="H128")
+    y = layer(x.cuda(), out_dtype=torch.float32).cpu().numpy()
+    assert mxl.gemm_status() == 0
+    wr = oracle.fwht(w.float().numpy(), 128, bf16_stages=True)                    # bf16 values
+    wq = oracle.bf16_bits_to_f32(oracle.dequant(oracle.quantize(wr), "bf16"))
+    xr = oracle.bf16_bits_to_f32(oracle.f32_to_bf16_bits(oracle.fwht(x.float().numpy(), 128)))
+    ystar = oracle.linear(xr, wq)
+    assert oracle.relative_l2(y, ystar) <= TOL
+    # and the rotation is (nearly) transparent: against the un-rotated product the only
+    # difference is quantization error of the rotated vs plain weight, both small
+    plain = oracle.linear(x.float().numpy(), w.float().numpy())
+    assert oracle.relative_l2(y, plain) <= 0.2
+
+
+def test_c_abi_workspace_contract():
+    from mixfp4_b200 import _native as nat
+    lib = nat.lib()
+    assert lib.mixfp4_gemm_workspace_bytes(300, 128, 131) >= 300 * 136 * 2
+    w = synth.student_t_weight(128, 256, 1).cuda()
+    packed, _, _ = mx.quantize_packed(w)
+    x = synth.activations(128, 256, 2).cuda()
+    y = torch.empty((128, 128), dtype=torch.float32, device="cuda")
+    st = lib.mixfp4_gemm(x.data_ptr(), 128, 256, packed.codes.data_ptr(), packed.scales.data_ptr(),
+                         packed.fmt.data_ptr(), packed.global_scale.data_ptr(), 128, 256, 128, y.data_ptr(),
+                         nat.F32, 128, None, 0, None, torch.cuda.current_stream().cuda_stream)
+    assert st == -7        # rotation requested without a workspace
