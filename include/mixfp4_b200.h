@@ -50,7 +50,8 @@ enum {
     MIXFP4_E_CUDA = -6,        /* a CUDA runtime or driver call failed; see mixfp4_last_cuda_error */
     MIXFP4_E_WORKSPACE = -7,   /* workspace missing or too small */
     MIXFP4_E_UNSUPPORTED = -8, /* valid request this build does not implement */
-    MIXFP4_E_DEVICE_WAIT = -9  /* a bounded device-side wait gave up (status word non-zero) */
+    MIXFP4_E_DEVICE_WAIT = -9, /* a bounded device-side wait gave up (status word non-zero) */
+    MIXFP4_E_TOO_LARGE = -10   /* request exceeds a fixed built-in capacity */
 };
 
 /* element types */
@@ -127,6 +128,31 @@ MIXFP4_API int mixfp4_gemm(const void* x, int64_t m, int64_t ldx,
                 const float* global_scale, int64_t n, int64_t k, int rotation_block,
                 void* y, int out_dtype, int64_t ldy,
                 void* workspace, int64_t workspace_bytes, int* status, void* stream);
+
+/* Allocation-free form of the H128-rotated prefill linear.  No counterpart in the
+ * reference: it exists for hosts that must not (or cannot) allocate device memory around
+ * the call -- an inference server that handed its whole memory budget to its own arena at
+ * start-up, a plugin running inside another runtime's allocator, a real-time loop where
+ * cudaMalloc's implicit synchronisation is unacceptable.  It computes exactly what
+ * mixfp4_gemm(..., rotation_block = 128, ...) computes, but the buffer that holds the
+ * rotated activations bf16(H128 x) is a fixed array inside the library instead of a
+ * caller-supplied workspace.  The call makes no cudaMalloc/cudaFree and calls no routine
+ * that allocates.
+ *   Limit: m * round_up(k, 8) * 2 bytes must not exceed
+ *   mixfp4_gemm_h128_static_max_bytes() (8 MiB, e.g. 1024 x 4096); larger requests return
+ *   MIXFP4_E_TOO_LARGE and do nothing.  Every GPU that loads the library holds those 8 MiB
+ *   until the process exits.
+ *   The first call on each device looks up the array's device address (the device must be
+ *   current); make that first call outside any stream capture.
+ *   All calls on a device share the one array and it keeps whatever the last call left in
+ *   it.  Each call rewrites every element it later reads, so nothing needs clearing, but
+ *   two calls whose kernels can overlap on the GPU (different streams, no ordering) race on
+ *   the array and corrupt each other: order them. */
+MIXFP4_API int64_t mixfp4_gemm_h128_static_max_bytes(void);
+MIXFP4_API int mixfp4_gemm_h128_static(const void* x, int64_t m, int64_t ldx,
+                const uint8_t* codes, const uint8_t* scales, const uint8_t* fmt,
+                const float* global_scale, int64_t n, int64_t k,
+                void* y, int out_dtype, int64_t ldy, int* status, void* stream);
 
 #ifdef __cplusplus
 }

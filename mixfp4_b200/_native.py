@@ -58,13 +58,17 @@ def _declare(h: ctypes.CDLL) -> None:
     h.mixfp4_gemm_workspace_bytes.argtypes = [i64, i64, i64]
     h.mixfp4_gemm.restype = i32
     h.mixfp4_gemm.argtypes = [p, i64, i64, p, p, p, p, i64, i64, i32, p, i32, i64, p, i64, p, p]
+    h.mixfp4_gemm_h128_static_max_bytes.restype = i64
+    h.mixfp4_gemm_h128_static_max_bytes.argtypes = []
+    h.mixfp4_gemm_h128_static.restype = i32
+    h.mixfp4_gemm_h128_static.argtypes = [p, i64, i64, p, p, p, p, i64, i64, p, i32, i64, p, p]
 
 
 # every symbol include/mixfp4_b200.h declares
 EXPORTED = (
     "mixfp4_abi_version", "mixfp4_status_string", "mixfp4_last_cuda_error", "mixfp4_padded_k",
     "mixfp4_amax", "mixfp4_quantize", "mixfp4_dequant", "mixfp4_fwht", "mixfp4_gemv",
-    "mixfp4_gemm_workspace_bytes", "mixfp4_gemm",
+    "mixfp4_gemm_workspace_bytes", "mixfp4_gemm", "mixfp4_gemm_h128_static_max_bytes", "mixfp4_gemm_h128_static",
 )
 
 

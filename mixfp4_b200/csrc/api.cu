@@ -39,6 +39,7 @@ extern "C" const char* mixfp4_status_string(int status) {
         case MIXFP4_E_WORKSPACE: return "workspace missing or too small";
         case MIXFP4_E_UNSUPPORTED: return "not supported by this build";
         case MIXFP4_E_DEVICE_WAIT: return "a bounded device-side wait gave up";
+        case MIXFP4_E_TOO_LARGE: return "request exceeds the built-in capacity of this entry point";
         default: return "unknown status";
     }
 }

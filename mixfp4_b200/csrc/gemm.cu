@@ -28,6 +28,8 @@
 #include <cuda.h>
 #include <stdlib.h>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "decode.cuh"
 
@@ -456,4 +458,55 @@ extern "C" int mixfp4_gemm(const void* x, int64_t m, int64_t ldx, const uint8_t*
     if (grid.y > 65535) return MIXFP4_E_SHAPE;
     gemm_kernel<<<grid, kThreads, kSmemBytes, st>>>(tmap, a);
     return check_launch("gemm_kernel");
+}
+
+// ------------------------------------------------------------- allocation-free variant
+// Staging buffer of mixfp4_gemm_h128_static: lives in the library image, so every GPU that
+// loads the library carries these 8 MiB until the process exits.
+namespace mixfp4 {
+namespace {
+constexpr int64_t kStaticScratchBytes = 8ll << 20;
+static __device__ __align__(256) uint8_t g_static_scratch[kStaticScratchBytes];
+constexpr int kMaxDevices = 64;
+
+// Device address of g_static_scratch on the current device.  In host code the symbol name
+// is only a handle, so the address is looked up once per device (with that device current)
+// and remembered.
+int static_scratch_address(void** out) {
+    static std::mutex lock;
+    static void* addr[kMaxDevices] = {};
+    int dev = 0;
+    MIXFP4_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return MIXFP4_E_UNSUPPORTED;
+    std::lock_guard<std::mutex> guard(lock);
+    if (!addr[dev]) {
+        void* p = nullptr;
+        MIXFP4_CUDA_CHECK(cudaGetSymbolAddress(&p, g_static_scratch));
+        addr[dev] = p;
+    }
+    *out = addr[dev];
+    return MIXFP4_OK;
+}
+}  // namespace
+}  // namespace mixfp4
+
+extern "C" int64_t mixfp4_gemm_h128_static_max_bytes(void) { return mixfp4::kStaticScratchBytes; }
+
+extern "C" int mixfp4_gemm_h128_static(const void* x, int64_t m, int64_t ldx, const uint8_t* codes,
+                                       const uint8_t* scales, const uint8_t* fmt, const float* global_scale,
+                                       int64_t n, int64_t k, void* y, int out_dtype, int64_t ldy, int* status,
+                                       void* stream) {
+    if (!x || !codes || !scales || !fmt || !global_scale || !y) return MIXFP4_E_NULL;
+    if (m <= 0 || n <= 0 || k <= 0 || ldx < k || ldy < n) return MIXFP4_E_SHAPE;
+    const int64_t lda = (k + 7) / 8 * 8;
+    if (m * lda * 2 > kStaticScratchBytes) return MIXFP4_E_TOO_LARGE;
+    void* scratch = nullptr;
+    int rc = static_scratch_address(&scratch);
+    if (rc != MIXFP4_OK) return rc;
+    // rotated activations bf16(H128 x) -> static buffer (every element the GEMM reads is
+    // rewritten here, so nothing left over from an earlier call is ever consumed)
+    rc = mixfp4_fwht(x, scratch, MIXFP4_BF16, m, k, ldx, lda, 128, nullptr, 0, stream);
+    if (rc != MIXFP4_OK) return rc;
+    return mixfp4_gemm(scratch, m, lda, codes, scales, fmt, global_scale, n, k, 0, y, out_dtype, ldy, nullptr, 0,
+                       status, stream);
 }
