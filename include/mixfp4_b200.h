@@ -32,7 +32,7 @@
 extern "C" {
 #endif
 
-#define MIXFP4_ABI_VERSION 1
+#define MIXFP4_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define MIXFP4_API __attribute__((visibility("default")))
@@ -56,6 +56,23 @@ enum {
 
 /* element types */
 enum { MIXFP4_BF16 = 0, MIXFP4_F16 = 1, MIXFP4_F32 = 2 };
+
+/* Packed layouts.  CANONICAL is the layout above (what mixfp4_quantize writes and what
+ * parity is hashed on).  KERNEL is a bit permutation of it that the linear kernels decode
+ * with fewer instructions: same array shapes, but inside every 32-bit word of `codes`
+ * (8 elements) bit 3 of nibble 2i+1 holds the sign of element i and bit 3 of nibble 2i the
+ * sign of element 4+i (i = 0..3), and bit 7 of every scale byte holds the block's format
+ * bit (the `fmt` array is not used).  mixfp4_repack converts either way. */
+enum { MIXFP4_LAYOUT_CANONICAL = 0, MIXFP4_LAYOUT_KERNEL = 1 };
+
+/* flags of the linear entry points */
+enum {
+    /* Programmatic dependent launch: the kernel may start while the previous kernel in the
+     * stream is still draining.  It prefetches the packed weight early and reads x only
+     * after the previous kernel has completed.  Set it only if the previous kernel in the
+     * stream does not write this call's packed weight, decode table or global scale. */
+    MIXFP4_FLAG_OVERLAP_PREVIOUS = 1
+};
 
 /* format selection (project_quant/region.py:22-39 mode names) */
 enum { MIXFP4_MODE_ORACLE16 = 0, MIXFP4_MODE_ALL_E2M1 = 1, MIXFP4_MODE_ALL_E0M3 = 2 };
@@ -93,8 +110,21 @@ MIXFP4_API int mixfp4_quantize(const void* x, int dtype, int64_t rows, int64_t k
 /* Packed -> dense weight in out_dtype (the tensor the reference stores back into
  * nn.Linear.weight, project_quant/modeling.py:629). */
 MIXFP4_API int mixfp4_dequant(const uint8_t* codes, const uint8_t* scales, const uint8_t* fmt,
-                   const float* global_scale, int64_t rows, int64_t k,
+                   const float* global_scale, int64_t rows, int64_t k, int layout,
                    void* out, int out_dtype, int64_t ldo, void* stream);
+
+/* Layout conversion (no reference counterpart: the reference has no packed form).
+ * to_layout = MIXFP4_LAYOUT_KERNEL: reads codes/scales/fmt, writes codes_out/scales_out
+ * (fmt_out unused).  to_layout = MIXFP4_LAYOUT_CANONICAL: reads codes/scales (fmt unused),
+ * writes codes_out/scales_out/fmt_out.  A pure bit permutation; round trip is the identity. */
+MIXFP4_API int mixfp4_repack(const uint8_t* codes, const uint8_t* scales, const uint8_t* fmt,
+                  int64_t rows, int64_t k, int to_layout,
+                  uint8_t* codes_out, uint8_t* scales_out, uint8_t* fmt_out, void* stream);
+
+/* Decode table of a packed weight: 256 entries x 16 B indexed by (format << 7 | E4M3 scale
+ * byte) holding the block's eight bf16 magnitudes bf16((level * scale) * global).  Optional
+ * input of the linear kernels (they build it per launch when given NULL). */
+MIXFP4_API int mixfp4_decode_table(const float* global_scale, void* lut, void* stream);
 
 /* Normalised block Hadamard along the last axis (project_quant/rotation.py:47-75
  * fwht / apply_transform).  size in {16,32,64,128}; only whole blocks are transformed,
@@ -109,11 +139,12 @@ MIXFP4_API int mixfp4_fwht(const void* x, void* y, int dtype, int64_t rows, int6
 /* Decode-shape dequant-linear, 1 <= M <= 16: y[M,N] = x[M,K] * W[N,K]^T with W packed
  * (replaces F.linear on the dequantized weight, modeling.py:629 + nn.Linear.forward).
  * x bf16 [M,K] row stride ldx; y in out_dtype (MIXFP4_F32 or MIXFP4_BF16) row stride ldy.
- * fp32 accumulation. */
+ * fp32 accumulation.  layout: MIXFP4_LAYOUT_*; fmt may be NULL for the kernel layout.
+ * lut: optional table from mixfp4_decode_table.  flags: MIXFP4_FLAG_*. */
 MIXFP4_API int mixfp4_gemv(const void* x, int64_t m, int64_t ldx,
                 const uint8_t* codes, const uint8_t* scales, const uint8_t* fmt,
-                const float* global_scale, int64_t n, int64_t k,
-                void* y, int out_dtype, int64_t ldy, void* stream);
+                const float* global_scale, int64_t n, int64_t k, int layout, const void* lut,
+                void* y, int out_dtype, int64_t ldy, int flags, void* stream);
 
 /* Prefill-shape dequant-linear on the tcgen05 tensor cores (any M >= 1, meant for
  * M >= 128).  rotation_block: 0, or 128 to apply the block-Hadamard H128 to x on the
@@ -125,9 +156,9 @@ MIXFP4_API int mixfp4_gemv(const void* x, int64_t m, int64_t ldx,
 MIXFP4_API int64_t mixfp4_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k);
 MIXFP4_API int mixfp4_gemm(const void* x, int64_t m, int64_t ldx,
                 const uint8_t* codes, const uint8_t* scales, const uint8_t* fmt,
-                const float* global_scale, int64_t n, int64_t k, int rotation_block,
-                void* y, int out_dtype, int64_t ldy,
-                void* workspace, int64_t workspace_bytes, int* status, void* stream);
+                const float* global_scale, int64_t n, int64_t k, int layout, const void* lut,
+                int rotation_block, void* y, int out_dtype, int64_t ldy,
+                void* workspace, int64_t workspace_bytes, int* status, int flags, void* stream);
 
 /* Allocation-free form of the H128-rotated prefill linear.  No counterpart in the
  * reference: it exists for hosts that must not (or cannot) allocate device memory around
@@ -151,7 +182,7 @@ MIXFP4_API int mixfp4_gemm(const void* x, int64_t m, int64_t ldx,
 MIXFP4_API int64_t mixfp4_gemm_h128_static_max_bytes(void);
 MIXFP4_API int mixfp4_gemm_h128_static(const void* x, int64_t m, int64_t ldx,
                 const uint8_t* codes, const uint8_t* scales, const uint8_t* fmt,
-                const float* global_scale, int64_t n, int64_t k,
+                const float* global_scale, int64_t n, int64_t k, int layout, const void* lut,
                 void* y, int out_dtype, int64_t ldy, int* status, void* stream);
 
 #ifdef __cplusplus

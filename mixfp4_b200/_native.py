@@ -17,6 +17,8 @@ from . import build as _build
 OK = 0
 BF16, F16, F32 = 0, 1, 2
 MODE_ORACLE16, MODE_ALL_E2M1, MODE_ALL_E0M3 = 0, 1, 2
+LAYOUT_CANONICAL, LAYOUT_KERNEL = 0, 1
+FLAG_OVERLAP_PREVIOUS = 1
 
 DTYPE_CODE = {torch.bfloat16: BF16, torch.float16: F16, torch.float32: F32}
 
@@ -49,25 +51,30 @@ def _declare(h: ctypes.CDLL) -> None:
     h.mixfp4_quantize.restype = i32
     h.mixfp4_quantize.argtypes = [p, i32, i64, i64, i64, i32, p, p, p, p, p, p, p, p, p, p, i64, p]
     h.mixfp4_dequant.restype = i32
-    h.mixfp4_dequant.argtypes = [p, p, p, p, i64, i64, p, i32, i64, p]
+    h.mixfp4_dequant.argtypes = [p, p, p, p, i64, i64, i32, p, i32, i64, p]
+    h.mixfp4_repack.restype = i32
+    h.mixfp4_repack.argtypes = [p, p, p, i64, i64, i32, p, p, p, p]
+    h.mixfp4_decode_table.restype = i32
+    h.mixfp4_decode_table.argtypes = [p, p, p]
     h.mixfp4_fwht.restype = i32
     h.mixfp4_fwht.argtypes = [p, p, i32, i64, i64, i64, i64, i32, p, i32, p]
     h.mixfp4_gemv.restype = i32
-    h.mixfp4_gemv.argtypes = [p, i64, i64, p, p, p, p, i64, i64, p, i32, i64, p]
+    h.mixfp4_gemv.argtypes = [p, i64, i64, p, p, p, p, i64, i64, i32, p, p, i32, i64, i32, p]
     h.mixfp4_gemm_workspace_bytes.restype = i64
     h.mixfp4_gemm_workspace_bytes.argtypes = [i64, i64, i64]
     h.mixfp4_gemm.restype = i32
-    h.mixfp4_gemm.argtypes = [p, i64, i64, p, p, p, p, i64, i64, i32, p, i32, i64, p, i64, p, p]
+    h.mixfp4_gemm.argtypes = [p, i64, i64, p, p, p, p, i64, i64, i32, p, i32, p, i32, i64, p, i64, p, i32, p]
     h.mixfp4_gemm_h128_static_max_bytes.restype = i64
     h.mixfp4_gemm_h128_static_max_bytes.argtypes = []
     h.mixfp4_gemm_h128_static.restype = i32
-    h.mixfp4_gemm_h128_static.argtypes = [p, i64, i64, p, p, p, p, i64, i64, p, i32, i64, p, p]
+    h.mixfp4_gemm_h128_static.argtypes = [p, i64, i64, p, p, p, p, i64, i64, i32, p, p, i32, i64, p, p]
 
 
 # every symbol include/mixfp4_b200.h declares
 EXPORTED = (
     "mixfp4_abi_version", "mixfp4_status_string", "mixfp4_last_cuda_error", "mixfp4_padded_k",
-    "mixfp4_amax", "mixfp4_quantize", "mixfp4_dequant", "mixfp4_fwht", "mixfp4_gemv",
+    "mixfp4_amax", "mixfp4_quantize", "mixfp4_dequant", "mixfp4_repack", "mixfp4_decode_table", "mixfp4_fwht",
+    "mixfp4_gemv",
     "mixfp4_gemm_workspace_bytes", "mixfp4_gemm", "mixfp4_gemm_h128_static_max_bytes", "mixfp4_gemm_h128_static",
 )
 
@@ -83,7 +90,7 @@ def lib() -> ctypes.CDLL:
                 "(run `python -m mixfp4_b200.build`); mixfp4_b200 has no fallback path")
         handle = ctypes.CDLL(path)
         _declare(handle)
-        if handle.mixfp4_abi_version() != 1:
+        if handle.mixfp4_abi_version() != 2:
             raise RuntimeError("libmixfp4_b200.so ABI version mismatch; rebuild it")
         _lib = handle
     return _lib

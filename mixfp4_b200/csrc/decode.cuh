@@ -50,4 +50,51 @@ __device__ __forceinline__ void decode8(uint32_t w, const uint4& t, uint32_t (&p
     p[3] = prmt(lo_b, hi_b, 0x7362u);
 }
 
+// Kernel layout ("KL") of the packed weight -- a pure bit permutation of the canonical
+// layout that makes the decode cheaper:
+//   codes:  inside every 32-bit word (8 elements) the 3-bit magnitudes stay in their
+//           nibbles, but bit 3 of nibble 2i+1 holds the sign of element i (i = 0..3) and
+//           bit 3 of nibble 2i holds the sign of element 4+i, so one mask (elements 0..3)
+//           and one shift+mask (elements 4..7) put the signs on bit 7 of the high bytes;
+//   scales: bit 7 of the E4M3 byte (always 0 for a block scale) carries the block's format
+//           bit, so the byte is the table index and no format array is read.
+__host__ __device__ __forceinline__ uint32_t codes_to_kernel_layout(uint32_t w) {
+    uint32_t out = w & 0x77777777u;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        out |= ((w >> (4 * i + 3)) & 1u) << (8 * i + 7);          // sign of element i
+        out |= ((w >> (4 * (4 + i) + 3)) & 1u) << (8 * i + 3);    // sign of element 4 + i
+    }
+    return out;
+}
+__host__ __device__ __forceinline__ uint32_t codes_from_kernel_layout(uint32_t w) {
+    uint32_t out = w & 0x77777777u;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        out |= ((w >> (8 * i + 7)) & 1u) << (4 * i + 3);
+        out |= ((w >> (8 * i + 3)) & 1u) << (4 * (4 + i) + 3);
+    }
+    return out;
+}
+
+// Eight kernel-layout codes -> four bf16x2 registers (elements 01, 23, 45, 67).
+__device__ __forceinline__ void decode8_kl(uint32_t w, const uint4& t, uint32_t (&p)[4]) {
+    const uint32_t mag = w & 0x77777777u;
+    const uint32_t mag_hi = mag >> 16;
+    uint32_t lo_a = prmt(t.x, t.y, mag), hi_a = prmt(t.z, t.w, mag);
+    uint32_t lo_b = prmt(t.x, t.y, mag_hi), hi_b = prmt(t.z, t.w, mag_hi);
+    hi_a |= w & 0x80808080u;
+    hi_b |= (w << 4) & 0x80808080u;
+    p[0] = prmt(lo_a, hi_a, 0x5140u);
+    p[1] = prmt(lo_a, hi_a, 0x7362u);
+    p[2] = prmt(lo_b, hi_b, 0x5140u);
+    p[3] = prmt(lo_b, hi_b, 0x7362u);
+}
+
+template <bool kKernelLayout>
+__device__ __forceinline__ void decode_word(uint32_t w, const uint4& t, uint32_t (&p)[4]) {
+    if constexpr (kKernelLayout) decode8_kl(w, t, p);
+    else decode8(w, t, p);
+}
+
 }  // namespace mixfp4

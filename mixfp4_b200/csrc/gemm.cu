@@ -57,6 +57,7 @@ struct GemmArgs {
     const uint8_t* scales;
     const uint8_t* fmt;
     const float* global_scale;
+    const uint4* lut;           // optional prebuilt decode table
     int64_t m, n, k, kpad;
     void* y;
     int out_dtype;
@@ -191,6 +192,7 @@ __device__ __forceinline__ uint4 lds128_lut(uint32_t addr) {
 }
 
 // ------------------------------------------------------------------------------ kernel
+template <bool kKL>
 __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
                                                            const GemmArgs a) {
     extern __shared__ uint8_t smem_raw[];
@@ -224,7 +226,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     if (warp == 1) tmem_alloc(base + kOffMisc, kTmemCols);
     if (warp >= 2) {   // the (format, scale) -> magnitudes table: 256 entries, 256 transcoder threads
         const int e = threadIdx.x - 64;
-        reinterpret_cast<uint4*>(gen + kOffLut)[e] = make_lut_entry(e & 127, e >> 7, *a.global_scale);
+        reinterpret_cast<uint4*>(gen + kOffLut)[e] = a.lut ? __ldg(a.lut + e) : make_lut_entry(e & 127, e >> 7, *a.global_scale);
     }
     tcgen05_fence_before();
     __syncthreads();
@@ -274,7 +276,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         const uint32_t grow = min(n0 + row, last_row);  // rows past N re-read the last row; never stored
         const uint8_t* cptr = a.codes + (size_t)grow * (a.kpad / 2) + half * 16;
         const uint8_t* sptr = a.scales + (size_t)grow * (a.kpad / 16) + half * 2;
-        const uint8_t* fptr = a.fmt + (size_t)grow * (a.kpad / 128);
+        const uint8_t* fptr = kKL ? a.scales : a.fmt + (size_t)grow * (a.kpad / 128);   // unused for the kernel layout
         const uint32_t lut_base = base + kOffLut;
         // destination of this thread's four 16-byte chunks: row r, logical chunk c -> c ^ (r & 7)
         const uint32_t row_off = (row >> 3) * 1024u + (row & 7) * 128u;
@@ -282,7 +284,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
 
         uint4 codes = __ldg(reinterpret_cast<const uint4*>(cptr));
         uint32_t sc2 = __ldg(reinterpret_cast<const unsigned short*>(sptr));
-        uint32_t fb = __ldg(fptr);
+        uint32_t fb = kKL ? 0u : __ldg(fptr);
         bool ok = true;
         for (int kt = 0; kt < num_kt; ++kt) {
             const int s = kt % kStages;
@@ -292,7 +294,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
             if (kt + 1 < num_kt) {                      // next K step's packed data, one step ahead
                 ncodes = __ldg(reinterpret_cast<const uint4*>(cptr + (size_t)(kt + 1) * 32));
                 nsc2 = __ldg(reinterpret_cast<const unsigned short*>(sptr + (size_t)(kt + 1) * 4));
-                nfb = __ldg(fptr + ((kt + 1) >> 1));
+                if constexpr (!kKL) nfb = __ldg(fptr + ((kt + 1) >> 1));
             }
             ok = mbar_wait(empty(s), ph ^ 1, ctx, 5);
             if (!ok) break;
@@ -300,13 +302,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
             const uint32_t fbits = fb >> ((kt & 1) * 4 + half * 2);     // this thread's 2 blocks
 #pragma unroll
             for (int b = 0; b < 2; ++b) {
-                const uint32_t idx = (((fbits >> b) & 1u) << 7) | ((sc2 >> (8 * b)) & 0x7fu);
+                const uint32_t idx = kKL ? ((sc2 >> (8 * b)) & 0xffu)
+                                         : ((((fbits >> b) & 1u) << 7) | ((sc2 >> (8 * b)) & 0x7fu));
                 const uint4 tab = lds128_lut(lut_base + idx * 16);
 #pragma unroll
                 for (int w = 0; w < 2; ++w) {
                     const int i = 2 * b + w;
                     uint32_t p[4];
-                    decode8(i == 0 ? codes.x : i == 1 ? codes.y : i == 2 ? codes.z : codes.w, tab, p);
+                    decode_word<kKL>(i == 0 ? codes.x : i == 1 ? codes.y : i == 2 ? codes.z : codes.w, tab, p);
                     const uint32_t chunk = (uint32_t)(half * 4 + i) ^ sw;
                     sts128(dst + chunk * 16, p[0], p[1], p[2], p[3]);
                 }
@@ -403,15 +406,17 @@ extern "C" int64_t mixfp4_gemm_workspace_bytes(int64_t m, int64_t /*n*/, int64_t
 }
 
 extern "C" int mixfp4_gemm(const void* x, int64_t m, int64_t ldx, const uint8_t* codes, const uint8_t* scales,
-                           const uint8_t* fmt, const float* global_scale, int64_t n, int64_t k, int rotation_block,
-                           void* y, int out_dtype, int64_t ldy, void* workspace, int64_t workspace_bytes,
-                           int* status, void* stream) {
-    if (!x || !codes || !scales || !fmt || !global_scale || !y) return MIXFP4_E_NULL;
+                           const uint8_t* fmt, const float* global_scale, int64_t n, int64_t k, int layout,
+                           const void* lut, int rotation_block, void* y, int out_dtype, int64_t ldy, void* workspace,
+                           int64_t workspace_bytes, int* status, int flags, void* stream) {
+    (void)flags;
+    if (layout != MIXFP4_LAYOUT_CANONICAL && layout != MIXFP4_LAYOUT_KERNEL) return MIXFP4_E_MODE;
+    if (!x || !codes || !scales || (!fmt && layout == MIXFP4_LAYOUT_CANONICAL) || !global_scale || !y) return MIXFP4_E_NULL;
     if (m <= 0 || n <= 0 || k <= 0 || ldx < k || ldy < n) return MIXFP4_E_SHAPE;
     if (m > 0x7fffffffLL || n > 0x7fffffffLL || k > 0x7fffffffLL) return MIXFP4_E_SHAPE;
     if (out_dtype != MIXFP4_F32 && out_dtype != MIXFP4_BF16) return MIXFP4_E_DTYPE;
     if (rotation_block != 0 && rotation_block != 128) return MIXFP4_E_MODE;
-    if (!aligned(codes, 16) || !aligned(scales, 2)) return MIXFP4_E_ALIGN;
+    if (!aligned(codes, 16) || !aligned(scales, 2) || (lut && !aligned(lut, 16))) return MIXFP4_E_ALIGN;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 
     // The TMA descriptor needs a 16-byte aligned base and row pitch; the rotation needs a
@@ -447,16 +452,19 @@ extern "C" int mixfp4_gemm(const void* x, int64_t m, int64_t ldx, const uint8_t*
 
     static bool configured = false;
     if (!configured) {
-        MIXFP4_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+        MIXFP4_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+        MIXFP4_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
         configured = true;
     }
     GemmArgs a;
     a.codes = codes; a.scales = scales; a.fmt = fmt; a.global_scale = global_scale;
+    a.lut = static_cast<const uint4*>(lut);
     a.m = m; a.n = n; a.k = k; a.kpad = padded_k(k);
     a.y = y; a.out_dtype = out_dtype; a.ldy = ldy; a.status = status;
     const dim3 grid((unsigned)((n + BN - 1) / BN), (unsigned)((m + BM - 1) / BM));
     if (grid.y > 65535) return MIXFP4_E_SHAPE;
-    gemm_kernel<<<grid, kThreads, kSmemBytes, st>>>(tmap, a);
+    if (layout == MIXFP4_LAYOUT_KERNEL) gemm_kernel<true><<<grid, kThreads, kSmemBytes, st>>>(tmap, a);
+    else gemm_kernel<false><<<grid, kThreads, kSmemBytes, st>>>(tmap, a);
     return check_launch("gemm_kernel");
 }
 
@@ -494,9 +502,9 @@ extern "C" int64_t mixfp4_gemm_h128_static_max_bytes(void) { return mixfp4::kSta
 
 extern "C" int mixfp4_gemm_h128_static(const void* x, int64_t m, int64_t ldx, const uint8_t* codes,
                                        const uint8_t* scales, const uint8_t* fmt, const float* global_scale,
-                                       int64_t n, int64_t k, void* y, int out_dtype, int64_t ldy, int* status,
-                                       void* stream) {
-    if (!x || !codes || !scales || !fmt || !global_scale || !y) return MIXFP4_E_NULL;
+                                       int64_t n, int64_t k, int layout, const void* lut, void* y, int out_dtype,
+                                       int64_t ldy, int* status, void* stream) {
+    if (!x || !codes || !scales || !global_scale || !y) return MIXFP4_E_NULL;
     if (m <= 0 || n <= 0 || k <= 0 || ldx < k || ldy < n) return MIXFP4_E_SHAPE;
     const int64_t lda = (k + 7) / 8 * 8;
     if (m * lda * 2 > kStaticScratchBytes) return MIXFP4_E_TOO_LARGE;
@@ -507,6 +515,6 @@ extern "C" int mixfp4_gemm_h128_static(const void* x, int64_t m, int64_t ldx, co
     // rewritten here, so nothing left over from an earlier call is ever consumed)
     rc = mixfp4_fwht(x, scratch, MIXFP4_BF16, m, k, ldx, lda, 128, nullptr, 0, stream);
     if (rc != MIXFP4_OK) return rc;
-    return mixfp4_gemm(scratch, m, lda, codes, scales, fmt, global_scale, n, k, 0, y, out_dtype, ldy, nullptr, 0,
-                       status, stream);
+    return mixfp4_gemm(scratch, m, lda, codes, scales, fmt, global_scale, n, k, layout, lut, 0, y, out_dtype, ldy,
+                       nullptr, 0, status, 0, stream);
 }

@@ -19,6 +19,7 @@
 // its stores 256 B of codes, 32 B of scales and one 32-bit word of format bits.
 
 #include "common.cuh"
+#include "decode.cuh"
 
 namespace mixfp4 {
 namespace {
@@ -231,7 +232,7 @@ __global__ void __launch_bounds__(kThreads) quantize_kernel(const QuantArgs a) {
 }
 
 // --------------------------------------------------------------------------- dequant
-template <typename T>
+template <typename T, bool kKL>
 __global__ void __launch_bounds__(kThreads) dequant_kernel(const uint8_t* __restrict__ codes,
                                                            const uint8_t* __restrict__ scales,
                                                            const uint8_t* __restrict__ fmt,
@@ -243,9 +244,17 @@ __global__ void __launch_bounds__(kThreads) dequant_kernel(const uint8_t* __rest
     if (row >= rows) return;
     const int64_t blk = t - row * groups;
     const float gs = *global_scale;
-    const uint2 c = __ldg(reinterpret_cast<const uint2*>(codes + row * blocks_pad * 8 + blk * 8));
-    const float sc = e4m3_to_float(__ldg(scales + row * blocks_pad + blk));
-    const bool e0 = (__ldg(fmt + row * (blocks_pad / 8) + (blk >> 3)) >> (blk & 7)) & 1;
+    uint2 c = __ldg(reinterpret_cast<const uint2*>(codes + row * blocks_pad * 8 + blk * 8));
+    const uint32_t sbyte = __ldg(scales + row * blocks_pad + blk);
+    bool e0;
+    if constexpr (kKL) {
+        c.x = codes_from_kernel_layout(c.x);
+        c.y = codes_from_kernel_layout(c.y);
+        e0 = (sbyte >> 7) & 1;
+    } else {
+        e0 = (__ldg(fmt + row * (blocks_pad / 8) + (blk >> 3)) >> (blk & 7)) & 1;
+    }
+    const float sc = e4m3_to_float(sbyte & 0x7fu);
     T vals[kGroup];
 #pragma unroll
     for (int i = 0; i < kGroup; ++i) {
@@ -264,6 +273,55 @@ __global__ void __launch_bounds__(kThreads) dequant_kernel(const uint8_t* __rest
         for (int i = 0; i < kGroup; ++i)
             if (c0 + i < k) o[i] = vals[i];
     }
+}
+
+// ---------------------------------------------------------------------------- repack
+// canonical <-> kernel layout (see decode.cuh); one thread per block, a warp covers 32
+// consecutive blocks of a row like the quantizer, so the format bits of 32 blocks are one
+// ballot word.
+template <bool kToKernel>
+__global__ void __launch_bounds__(kThreads) repack_kernel(const uint8_t* __restrict__ codes,
+                                                          const uint8_t* __restrict__ scales,
+                                                          const uint8_t* __restrict__ fmt, int64_t rows,
+                                                          int64_t blocks_pad, int64_t chunks,
+                                                          uint8_t* __restrict__ codes_out,
+                                                          uint8_t* __restrict__ scales_out,
+                                                          uint8_t* __restrict__ fmt_out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+    const int64_t row = warp / chunks;
+    if (row >= rows) return;
+    const int64_t chunk = warp - row * chunks;
+    const int64_t blk = chunk * 32 + lane;
+    const bool stored = blk < blocks_pad;
+    bool fbit = false;
+    if (stored) {
+        uint2 c = __ldg(reinterpret_cast<const uint2*>(codes + row * blocks_pad * 8 + blk * 8));
+        uint32_t sb = __ldg(scales + row * blocks_pad + blk);
+        if constexpr (kToKernel) {
+            fbit = (__ldg(fmt + row * (blocks_pad / 8) + (blk >> 3)) >> (blk & 7)) & 1;
+            c.x = codes_to_kernel_layout(c.x);
+            c.y = codes_to_kernel_layout(c.y);
+            sb = (sb & 0x7fu) | (fbit ? 0x80u : 0u);
+        } else {
+            fbit = (sb >> 7) & 1;
+            c.x = codes_from_kernel_layout(c.x);
+            c.y = codes_from_kernel_layout(c.y);
+            sb &= 0x7fu;
+        }
+        *reinterpret_cast<uint2*>(codes_out + row * blocks_pad * 8 + blk * 8) = c;
+        scales_out[row * blocks_pad + blk] = static_cast<uint8_t>(sb);
+    }
+    if constexpr (!kToKernel) {
+        const uint32_t bits = __ballot_sync(0xffffffffu, fbit);
+        const int64_t col = chunk * 4 + lane;
+        if (lane < 4 && col < blocks_pad / 8) fmt_out[row * (blocks_pad / 8) + col] = static_cast<uint8_t>(bits >> (8 * lane));
+    }
+}
+
+__global__ void decode_table_kernel(const float* __restrict__ global_scale, uint4* __restrict__ lut) {
+    const int e = threadIdx.x;
+    lut[e] = make_lut_entry(e & 127, e >> 7, *global_scale);
 }
 
 size_t elem_size(int dtype) { return dtype == MIXFP4_F32 ? 4 : 2; }
@@ -336,9 +394,10 @@ extern "C" int mixfp4_quantize(const void* x, int dtype, int64_t rows, int64_t k
 }
 
 extern "C" int mixfp4_dequant(const uint8_t* codes, const uint8_t* scales, const uint8_t* fmt,
-                              const float* global_scale, int64_t rows, int64_t k, void* out, int out_dtype,
-                              int64_t ldo, void* stream) {
-    if (!codes || !scales || !fmt || !global_scale || !out) return MIXFP4_E_NULL;
+                              const float* global_scale, int64_t rows, int64_t k, int layout, void* out,
+                              int out_dtype, int64_t ldo, void* stream) {
+    if (layout != MIXFP4_LAYOUT_CANONICAL && layout != MIXFP4_LAYOUT_KERNEL) return MIXFP4_E_MODE;
+    if (!codes || !scales || (!fmt && layout == MIXFP4_LAYOUT_CANONICAL) || !global_scale || !out) return MIXFP4_E_NULL;
     if (rows <= 0 || k <= 0 || ldo < k) return MIXFP4_E_SHAPE;
     if (out_dtype < MIXFP4_BF16 || out_dtype > MIXFP4_F32) return MIXFP4_E_DTYPE;
     if (!aligned(codes, 8)) return MIXFP4_E_ALIGN;
@@ -347,18 +406,47 @@ extern "C" int mixfp4_dequant(const uint8_t* codes, const uint8_t* scales, const
     if (ctas > 0x7fffffffLL) return MIXFP4_E_SHAPE;
     const bool vec = rows_vectorizable(out, ldo, out_dtype);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define MIXFP4_LAUNCH_DEQUANT(T)                                                                             \
+    do {                                                                                                    \
+        if (layout == MIXFP4_LAYOUT_KERNEL)                                                                 \
+            dequant_kernel<T, true><<<(unsigned)ctas, kThreads, 0, st>>>(codes, scales, fmt, global_scale, rows, k, \
+                                                                         groups, blocks_pad, static_cast<T*>(out), ldo, vec); \
+        else                                                                                                \
+            dequant_kernel<T, false><<<(unsigned)ctas, kThreads, 0, st>>>(codes, scales, fmt, global_scale, rows, k, \
+                                                                          groups, blocks_pad, static_cast<T*>(out), ldo, vec); \
+    } while (0)
     switch (out_dtype) {
-        case MIXFP4_BF16:
-            dequant_kernel<<<(unsigned)ctas, kThreads, 0, st>>>(codes, scales, fmt, global_scale, rows, k, groups,
-                                                                blocks_pad, static_cast<__nv_bfloat16*>(out), ldo, vec);
-            break;
-        case MIXFP4_F16:
-            dequant_kernel<<<(unsigned)ctas, kThreads, 0, st>>>(codes, scales, fmt, global_scale, rows, k, groups,
-                                                                blocks_pad, static_cast<__half*>(out), ldo, vec);
-            break;
-        default:
-            dequant_kernel<<<(unsigned)ctas, kThreads, 0, st>>>(codes, scales, fmt, global_scale, rows, k, groups,
-                                                                blocks_pad, static_cast<float*>(out), ldo, vec);
+        case MIXFP4_BF16: MIXFP4_LAUNCH_DEQUANT(__nv_bfloat16); break;
+        case MIXFP4_F16: MIXFP4_LAUNCH_DEQUANT(__half); break;
+        default: MIXFP4_LAUNCH_DEQUANT(float);
     }
+#undef MIXFP4_LAUNCH_DEQUANT
     return check_launch("dequant_kernel");
+}
+
+extern "C" int mixfp4_repack(const uint8_t* codes, const uint8_t* scales, const uint8_t* fmt, int64_t rows, int64_t k,
+                             int to_layout, uint8_t* codes_out, uint8_t* scales_out, uint8_t* fmt_out, void* stream) {
+    if (to_layout != MIXFP4_LAYOUT_CANONICAL && to_layout != MIXFP4_LAYOUT_KERNEL) return MIXFP4_E_MODE;
+    if (!codes || !scales || !codes_out || !scales_out) return MIXFP4_E_NULL;
+    if (to_layout == MIXFP4_LAYOUT_KERNEL ? !fmt : !fmt_out) return MIXFP4_E_NULL;
+    if (rows <= 0 || k <= 0) return MIXFP4_E_SHAPE;
+    if (!aligned(codes, 8) || !aligned(codes_out, 8)) return MIXFP4_E_ALIGN;
+    const int64_t blocks_pad = padded_k(k) / kGroup, chunks = (blocks_pad + 31) / 32;
+    const int64_t ctas = (rows * chunks + kWarpsPerCta - 1) / kWarpsPerCta;
+    if (ctas > 0x7fffffffLL) return MIXFP4_E_SHAPE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (to_layout == MIXFP4_LAYOUT_KERNEL)
+        repack_kernel<true><<<(unsigned)ctas, kThreads, 0, st>>>(codes, scales, fmt, rows, blocks_pad, chunks, codes_out,
+                                                                 scales_out, fmt_out);
+    else
+        repack_kernel<false><<<(unsigned)ctas, kThreads, 0, st>>>(codes, scales, fmt, rows, blocks_pad, chunks, codes_out,
+                                                                  scales_out, fmt_out);
+    return check_launch("repack_kernel");
+}
+
+extern "C" int mixfp4_decode_table(const float* global_scale, void* lut, void* stream) {
+    if (!global_scale || !lut) return MIXFP4_E_NULL;
+    if (!aligned(lut, 16)) return MIXFP4_E_ALIGN;
+    decode_table_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(global_scale, static_cast<uint4*>(lut));
+    return check_launch("decode_table_kernel");
 }

@@ -48,13 +48,17 @@ def gemm_status(device=None) -> int:
 
 
 def mixfp4_linear(x: torch.Tensor, packed: PackedWeight, *, bias: torch.Tensor | None = None,
-                  rotate: bool | None = None, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+                  rotate: bool | None = None, out_dtype: torch.dtype | None = None,
+                  overlap_previous: bool = False) -> torch.Tensor:
     """y = x @ W^T (+ bias) with W packed; x bf16 [..., K] on the GPU.
 
     rotate: apply the weight's folded K-transform to x first (default: yes when the packed
     weight records one).  H128 is fused into the GEMM prologue; the GEMV path and other
     block sizes run the stand-alone FWHT kernel (fp32 stages, one rounding).
     out_dtype: torch.float32 or torch.bfloat16 (default: x.dtype).
+    overlap_previous: launch the decode kernel as a programmatic dependent of the previous
+    kernel in the stream (its weight prefetch overlaps that kernel's tail).  Only valid when
+    the previous kernel does not write this layer's packed weight.
     """
     nat.require_cuda(x, "x")
     if x.dtype != torch.bfloat16:
@@ -88,8 +92,9 @@ def mixfp4_linear(x: torch.Tensor, packed: PackedWeight, *, bias: torch.Tensor |
             if spec is not None:
                 x2 = _rotation.apply_transform(x2, spec, rounding="once")
             st = lib.mixfp4_gemv(x2.data_ptr(), m, x2.stride(0), packed.codes.data_ptr(), packed.scales.data_ptr(),
-                                 packed.fmt.data_ptr(), packed.global_scale.data_ptr(), packed.n, packed.k,
-                                 y.data_ptr(), nat.DTYPE_CODE[out_dtype], y.stride(0), stream)
+                                 nat.ptr(packed.fmt), packed.global_scale.data_ptr(), packed.n, packed.k,
+                                 packed.layout_code, nat.ptr(packed.lut), y.data_ptr(), nat.DTYPE_CODE[out_dtype],
+                                 y.stride(0), nat.FLAG_OVERLAP_PREVIOUS if overlap_previous else 0, stream)
             nat.check("mixfp4_gemv", st)
         else:
             fused = 0
@@ -101,9 +106,10 @@ def mixfp4_linear(x: torch.Tensor, packed: PackedWeight, *, bias: torch.Tensor |
             nbytes = lib.mixfp4_gemm_workspace_bytes(m, packed.n, packed.k)
             ws = _workspace(x.device, nbytes)
             st = lib.mixfp4_gemm(x2.data_ptr(), m, x2.stride(0), packed.codes.data_ptr(), packed.scales.data_ptr(),
-                                 packed.fmt.data_ptr(), packed.global_scale.data_ptr(), packed.n, packed.k, fused,
-                                 y.data_ptr(), nat.DTYPE_CODE[out_dtype], y.stride(0), nat.ptr(ws), nbytes,
-                                 _status_word(x.device).data_ptr(), stream)
+                                 nat.ptr(packed.fmt), packed.global_scale.data_ptr(), packed.n, packed.k,
+                                 packed.layout_code, nat.ptr(packed.lut), fused, y.data_ptr(),
+                                 nat.DTYPE_CODE[out_dtype], y.stride(0), nat.ptr(ws), nbytes,
+                                 _status_word(x.device).data_ptr(), 0, stream)
             nat.check("mixfp4_gemm", st)
     if bias is not None:
         y += bias.to(y.dtype)
@@ -116,17 +122,18 @@ class MixFP4Linear(nn.Module):
     def __init__(self, packed: PackedWeight, bias: torch.Tensor | None = None):
         super().__init__()
         self.in_features, self.out_features = packed.k, packed.n
+        packed = packed.to_kernel_layout()          # the layers keep the layout the kernels decode fastest
         self.rotation = packed.rotation
         self.register_buffer("codes", packed.codes)
         self.register_buffer("scales", packed.scales)
-        self.register_buffer("fmt", packed.fmt)
+        self.register_buffer("lut", packed.lut)
         self.register_buffer("global_scale", packed.global_scale)
         self.bias = None if bias is None else nn.Parameter(bias.detach().clone(), requires_grad=False)
 
     @property
     def packed(self) -> PackedWeight:
-        return PackedWeight(self.codes, self.scales, self.fmt, self.global_scale, self.out_features,
-                            self.in_features, self.rotation)
+        return PackedWeight(self.codes, self.scales, None, self.global_scale, self.out_features,
+                            self.in_features, self.rotation, "kernel", self.lut)
 
     @classmethod
     @torch.no_grad()
@@ -144,8 +151,9 @@ class MixFP4Linear(nn.Module):
         bias = None if linear.bias is None else linear.bias.detach().to(device)
         return cls(packed, bias)
 
-    def forward(self, x: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
-        return mixfp4_linear(x, self.packed, bias=self.bias, out_dtype=out_dtype)
+    def forward(self, x: torch.Tensor, out_dtype: torch.dtype | None = None,
+                overlap_previous: bool = False) -> torch.Tensor:
+        return mixfp4_linear(x, self.packed, bias=self.bias, out_dtype=out_dtype, overlap_previous=overlap_previous)
 
     def extra_repr(self) -> str:
         return f"in_features={self.in_features}, out_features={self.out_features}, rotation={self.rotation}"

@@ -57,6 +57,8 @@ class PackedWeight:
     n: int
     k: int
     rotation: str | None = None  # transform folded into the weight along K before quantization
+    layout: str = "canonical"    # "canonical" (parity-hashed) or "kernel" (bit-permuted for the linear kernels)
+    lut: torch.Tensor | None = None   # optional decode table (uint8 [4096]) from mixfp4_decode_table
 
     @property
     def kpad(self) -> int:
@@ -73,46 +75,85 @@ class PackedWeight:
     def nbytes(self) -> int:
         return packed_nbytes(self.n, self.k)
 
+    @property
+    def layout_code(self) -> int:
+        return nat.LAYOUT_KERNEL if self.layout == "kernel" else nat.LAYOUT_CANONICAL
+
     def format_ids(self) -> torch.Tensor:
         """uint8 [n, ceil(k/16)], 1 = E0M3 (GranularityResult.format_ids of the reference)."""
+        if self.layout == "kernel":
+            return (self.scales[:, : self.groups] >> 7).contiguous()
         shifts = torch.arange(8, device=self.fmt.device, dtype=torch.uint8)
         bits = (self.fmt.unsqueeze(-1) >> shifts) & 1
         return bits.reshape(self.n, -1)[:, : self.groups].contiguous()
 
     def selected_scales(self) -> torch.Tensor:
         """float32 [n, ceil(k/16)] decoded block scales."""
-        return self.scales[:, : self.groups].contiguous().view(torch.float8_e4m3fn).float()
+        return (self.scales[:, : self.groups] & 0x7F).contiguous().view(torch.float8_e4m3fn).float()
 
     def dequantize(self, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
         return dequantize(self, dtype)
 
     def to(self, device) -> "PackedWeight":
-        return PackedWeight(self.codes.to(device), self.scales.to(device), self.fmt.to(device),
-                            self.global_scale.to(device), self.n, self.k, self.rotation)
+        mv = lambda t: None if t is None else t.to(device)
+        return PackedWeight(mv(self.codes), mv(self.scales), mv(self.fmt), mv(self.global_scale), self.n, self.k,
+                            self.rotation, self.layout, mv(self.lut))
 
     def state_dict(self) -> dict:
         return {"codes": self.codes, "scales": self.scales, "fmt": self.fmt, "global_scale": self.global_scale,
-                "n": self.n, "k": self.k, "rotation": self.rotation}
+                "n": self.n, "k": self.k, "rotation": self.rotation, "layout": self.layout}
 
     @staticmethod
     def from_state_dict(state: dict) -> "PackedWeight":
         return PackedWeight(state["codes"], state["scales"], state["fmt"], state["global_scale"],
-                            int(state["n"]), int(state["k"]), state.get("rotation"))
+                            int(state["n"]), int(state["k"]), state.get("rotation"), state.get("layout", "canonical"))
+
+    def with_decode_table(self) -> "PackedWeight":
+        """Attach the 4 KB (format, scale) -> bf16 magnitudes table so that the linear kernels
+        copy it instead of rebuilding it in every launch."""
+        if self.lut is None:
+            lut = torch.empty(4096, dtype=torch.uint8, device=self.device)
+            with torch.cuda.device(self.device):
+                st = nat.lib().mixfp4_decode_table(self.global_scale.data_ptr(), lut.data_ptr(), nat.stream_ptr(self.device))
+            nat.check("mixfp4_decode_table", st)
+            self.lut = lut
+        return self
+
+    def _repack(self, to: str) -> "PackedWeight":
+        if self.layout == to:
+            return self
+        codes, scales = torch.empty_like(self.codes), torch.empty_like(self.scales)
+        fmt = None if to == "kernel" else torch.empty((self.n, self.kpad // 128), dtype=torch.uint8, device=self.device)
+        with torch.cuda.device(self.device):
+            st = nat.lib().mixfp4_repack(self.codes.data_ptr(), self.scales.data_ptr(), nat.ptr(self.fmt), self.n, self.k,
+                                         nat.LAYOUT_KERNEL if to == "kernel" else nat.LAYOUT_CANONICAL,
+                                         codes.data_ptr(), scales.data_ptr(), nat.ptr(fmt), nat.stream_ptr(self.device))
+        nat.check("mixfp4_repack", st)
+        return PackedWeight(codes, scales, fmt, self.global_scale, self.n, self.k, self.rotation, to, self.lut)
+
+    def to_kernel_layout(self) -> "PackedWeight":
+        """Bit-permuted copy for the GEMV/GEMM kernels (signs regrouped inside each 32-bit code
+        word, format bit folded into bit 7 of the scale byte; no format array), with its table."""
+        return self._repack("kernel").with_decode_table()
+
+    def to_canonical(self) -> "PackedWeight":
+        return self._repack("canonical")
 
     def row_shard(self, start: int, stop: int) -> "PackedWeight":
         """Rows [start, stop) -- a column-parallel (split N) shard; shares the tensor scale."""
-        return PackedWeight(self.codes[start:stop].contiguous(), self.scales[start:stop].contiguous(),
-                            self.fmt[start:stop].contiguous(), self.global_scale, stop - start, self.k, self.rotation)
+        fmt = None if self.fmt is None else self.fmt[start:stop].contiguous()
+        return PackedWeight(self.codes[start:stop].contiguous(), self.scales[start:stop].contiguous(), fmt,
+                            self.global_scale, stop - start, self.k, self.rotation, self.layout, self.lut)
 
     def k_shard(self, start: int, stop: int) -> "PackedWeight":
         """Columns [start, stop) along K (multiples of 128) -- a row-parallel (split K) shard."""
         if start % 128 or (stop % 128 and stop != self.k):
             raise ValueError("K shards must start and end on multiples of 128")
         pstop = padded_k(stop)
+        fmt = None if self.fmt is None else self.fmt[:, start // 128: pstop // 128].contiguous()
         return PackedWeight(self.codes[:, start // 2: pstop // 2].contiguous(),
-                            self.scales[:, start // 16: pstop // 16].contiguous(),
-                            self.fmt[:, start // 128: pstop // 128].contiguous(),
-                            self.global_scale, self.n, stop - start, self.rotation)
+                            self.scales[:, start // 16: pstop // 16].contiguous(), fmt,
+                            self.global_scale, self.n, stop - start, self.rotation, self.layout, self.lut)
 
 
 @dataclass
@@ -225,9 +266,9 @@ def dequantize(packed: PackedWeight, dtype: torch.dtype = torch.bfloat16) -> tor
     nat.require_cuda(packed.codes, "packed weight")
     out = torch.empty((packed.n, packed.k), dtype=dtype, device=packed.device)
     with torch.cuda.device(packed.device):
-        st = nat.lib().mixfp4_dequant(packed.codes.data_ptr(), packed.scales.data_ptr(), packed.fmt.data_ptr(),
-                                      packed.global_scale.data_ptr(), packed.n, packed.k, out.data_ptr(),
-                                      nat.DTYPE_CODE[dtype], packed.k, nat.stream_ptr(packed.device))
+        st = nat.lib().mixfp4_dequant(packed.codes.data_ptr(), packed.scales.data_ptr(), nat.ptr(packed.fmt),
+                                      packed.global_scale.data_ptr(), packed.n, packed.k, packed.layout_code,
+                                      out.data_ptr(), nat.DTYPE_CODE[dtype], packed.k, nat.stream_ptr(packed.device))
     nat.check("mixfp4_dequant", st)
     return out
 

@@ -22,7 +22,7 @@ def test_library_exports_every_declared_symbol():
     handle = nat.lib()
     for name in declared:
         assert getattr(handle, name) is not None
-    assert handle.mixfp4_abi_version() == 1
+    assert handle.mixfp4_abi_version() == 2
     assert handle.mixfp4_padded_k(70) == 128 and handle.mixfp4_padded_k(4096) == 4096
 
 
@@ -49,8 +49,12 @@ def test_c_abi_argument_validation_needs_no_gpu():
     bad = list(args); bad[7] = ctypes.c_void_p(20)
     assert h.mixfp4_quantize(*bad) == -3          # codes not 8-byte aligned
     assert h.mixfp4_fwht(one, one, nat.BF16, 4, 64, 64, 64, 48, None, 0, None) == -5
-    assert h.mixfp4_gemv(one, 17, 64, one, one, one, one, 8, 64, one, nat.F32, 8, None) == -2
-    assert h.mixfp4_gemv(one, 1, 64, one, one, one, one, 8, 64, one, nat.F16, 8, None) == -4
+    assert h.mixfp4_gemv(one, 17, 64, one, one, one, one, 8, 64, 0, None, one, nat.F32, 8, 0, None) == -2
+    assert h.mixfp4_gemv(one, 1, 64, one, one, one, one, 8, 64, 0, None, one, nat.F16, 8, 0, None) == -4
+    assert h.mixfp4_gemv(one, 1, 64, one, one, None, one, 8, 64, 0, None, one, nat.F32, 8, 0, None) == -1   # canonical needs fmt
+    assert h.mixfp4_gemv(one, 1, 64, one, one, None, one, 8, 64, 3, None, one, nat.F32, 8, 0, None) == -5   # unknown layout
+    assert h.mixfp4_repack(one, one, None, 4, 64, 1, one, one, None, None) == -1
+    assert h.mixfp4_decode_table(None, one, None) == -1
     assert h.mixfp4_status_string(-3).decode().startswith("pointer or stride")
 
 

@@ -106,6 +106,6 @@ def test_c_abi_workspace_contract():
     x = synth.activations(128, 256, 2).cuda()
     y = torch.empty((128, 128), dtype=torch.float32, device="cuda")
     st = lib.mixfp4_gemm(x.data_ptr(), 128, 256, packed.codes.data_ptr(), packed.scales.data_ptr(),
-                         packed.fmt.data_ptr(), packed.global_scale.data_ptr(), 128, 256, 128, y.data_ptr(),
-                         nat.F32, 128, None, 0, None, torch.cuda.current_stream().cuda_stream)
+                         packed.fmt.data_ptr(), packed.global_scale.data_ptr(), 128, 256, 0, None, 128, y.data_ptr(),
+                         nat.F32, 128, None, 0, None, 0, torch.cuda.current_stream().cuda_stream)
     assert st == -7        # rotation requested without a workspace

@@ -29,14 +29,14 @@ def _both(x, packed, out_dtype=torch.float32):
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     args = (packed.codes.data_ptr(), packed.scales.data_ptr(), packed.fmt.data_ptr(), packed.global_scale.data_ptr())
     y_static = torch.empty((m, n), dtype=out_dtype, device="cuda")
-    rc = lib.mixfp4_gemm_h128_static(x.data_ptr(), m, x.stride(0), *args, n, k, y_static.data_ptr(),
-                                     nat.DTYPE_CODE[out_dtype], n, status.data_ptr(), stream)
+    rc = lib.mixfp4_gemm_h128_static(x.data_ptr(), m, x.stride(0), *args, n, k, packed.layout_code, None,
+                                     y_static.data_ptr(), nat.DTYPE_CODE[out_dtype], n, status.data_ptr(), stream)
     assert rc == 0, lib.mixfp4_status_string(rc)
     nbytes = lib.mixfp4_gemm_workspace_bytes(m, n, k)
     ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
     y_ws = torch.empty((m, n), dtype=out_dtype, device="cuda")
-    rc = lib.mixfp4_gemm(x.data_ptr(), m, x.stride(0), *args, n, k, 128, y_ws.data_ptr(),
-                         nat.DTYPE_CODE[out_dtype], n, ws.data_ptr(), nbytes, status.data_ptr(), stream)
+    rc = lib.mixfp4_gemm(x.data_ptr(), m, x.stride(0), *args, n, k, packed.layout_code, None, 128, y_ws.data_ptr(),
+                         nat.DTYPE_CODE[out_dtype], n, ws.data_ptr(), nbytes, status.data_ptr(), 0, stream)
     assert rc == 0, lib.mixfp4_status_string(rc)
     torch.cuda.synchronize()
     assert int(status.item()) == 0
@@ -61,6 +61,7 @@ def test_static_scratch_variant_rejects_oversize_requests():
     assert cap == 8 << 20
     one = 256                       # never dereferenced: the size check comes first
     too_big_m = cap // (4096 * 2) + 1
-    rc = lib.mixfp4_gemm_h128_static(one, too_big_m, 4096, one, one, one, one, 128, 4096, one, nat.F32, 128, None, None)
+    rc = lib.mixfp4_gemm_h128_static(one, too_big_m, 4096, one, one, one, one, 128, 4096, 0, None, one, nat.F32, 128,
+                                     None, None)
     assert rc == -10
     assert b"capacity" in lib.mixfp4_status_string(rc)
