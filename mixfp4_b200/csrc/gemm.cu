@@ -3,7 +3,9 @@
 // Replaces F.linear on the dequantized weight (project_quant/modeling.py:629) and, with
 // rotation_block = 128, the activation pre-hook (modeling.py:662-668).
 //
-// Tile: one CTA computes a 128 (M) x 128 (N) tile, K in steps of 64.  Warp roles:
+// Tile: one CTA computes (1 or 2) x 128 rows of x by 128 or 256 weight rows, K in steps of 64;
+// with two 128-row sub-tiles the transcoded weight tile feeds two accumulators, which
+// halves the transcode work per flop.  Warp roles (figures for the 128 x 128 tile):
 //   warp 0      TMA producer: one lane issues cp.async.bulk.tensor.2d loads of the x tile
 //               (128 rows x 64 bf16, 128-byte swizzle) into a 6-stage shared-memory ring.
 //   warp 1      MMA issuer: allocates 128 TMEM columns, then one lane issues four
@@ -26,6 +28,7 @@
 // tile is transcoded once per CTA, i.e. N*K elements are decoded M/128 times over.
 
 #include <cuda.h>
+#include <stdio.h>
 #include <stdlib.h>
 
 #include <mutex>
@@ -36,21 +39,35 @@
 namespace mixfp4 {
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 64;
-constexpr int kStages = 6;
+constexpr int BK = 64;                     // K elements per pipeline stage (one 128-byte swizzle row)
 constexpr int kDecodeWarps = 8;
 constexpr int kThreads = (2 + kDecodeWarps) * 32;
-constexpr uint32_t kABytes = BM * BK * 2, kBBytes = BN * BK * 2;
-constexpr uint32_t kTmemCols = 128;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s: far beyond any legitimate wait
 
-// shared-memory map (offsets from a 1024-aligned base)
-constexpr uint32_t kOffA = 0;
-constexpr uint32_t kOffB = kStages * kABytes;
-constexpr uint32_t kOffLut = kOffB + kStages * kBBytes;
-constexpr uint32_t kOffBar = kOffLut + 4096;                 // full_a[S] full_b[S] empty[S] accum
-constexpr uint32_t kOffMisc = kOffBar + (3 * kStages + 1) * 8;   // tmem base, abort flag
-constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;        // + alignment slack
+// Tile configuration: kMT sub-tiles of 128 rows of x (each its own TMEM accumulator, all
+// sharing the transcoded weight tile) by kBN weight rows.
+template <int kMT, int kBN>
+struct Cfg {
+    static constexpr int BM = 128 * kMT, BN = kBN;
+    static constexpr uint32_t kABytes = BM * BK * 2, kBBytes = BN * BK * 2;
+    static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+    static constexpr int kStages = (196608 / kStageBytes) < 6 ? (196608 / kStageBytes) : 6;
+    static constexpr uint32_t kTmemCols = kMT * kBN;            // 128, 256 or 512: powers of two
+    // shared-memory map (offsets from a 1024-aligned base)
+    static constexpr uint32_t kOffA = 0;
+    static constexpr uint32_t kOffB = kStages * kABytes;
+    static constexpr uint32_t kOffLut = kOffB + kStages * kBBytes;
+    static constexpr uint32_t kOffBar = kOffLut + 4096;         // full_a[S] full_b[S] empty[S] accum
+    static constexpr uint32_t kOffMisc = kOffBar + (3 * kStages + 1) * 8;   // tmem base, abort flag
+    static constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;   // + alignment slack
+    // tcgen05 instruction descriptor, kind::f16: D fp32 (bits 4-5 = 1), A and B bf16 (bits 7-9
+    // and 10-12 = 1), both K-major (bits 15, 16 = 0), N >> 3 at bits 17-22, M >> 4 at bits 24-28.
+    static constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) |
+                                           ((uint32_t)(128 >> 4) << 24);
+    // transcoders: 256 threads over kBN rows
+    static constexpr int kThreadsPerRow = 256 / kBN;            // 2 or 1
+    static constexpr int kWords = 8 / kThreadsPerRow;           // 32-bit code words per thread and K step
+};
 
 struct GemmArgs {
     const uint8_t* codes;
@@ -177,11 +194,6 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
     return lo | (hi << 32);
 }
 
-// Instruction descriptor, kind::f16: D fp32 (bits 4-5 = 1), A and B bf16 (bits 7-9, 10-12 = 1),
-// both K-major (bits 15, 16 = 0), N >> 3 at bits 17-22, M >> 4 at bits 24-28.
-constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
-                                ((uint32_t)(BM >> 4) << 24);
-
 __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
@@ -192,24 +204,26 @@ __device__ __forceinline__ uint4 lds128_lut(uint32_t addr) {
 }
 
 // ------------------------------------------------------------------------------ kernel
-template <bool kKL>
+template <int kMT, int kBN, bool kKL>
 __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
                                                            const GemmArgs a) {
+    using C = Cfg<kMT, kBN>;
+    constexpr int kStages = C::kStages;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t* gen = smem_raw + (base - raw);            // generic pointer to the aligned base
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+    const uint32_t n0 = blockIdx.x * C::BN, m0 = blockIdx.y * C::BM;
     const int num_kt = static_cast<int>(a.kpad / BK);
 
-    auto full_a = [&](int s) { return base + kOffBar + 8u * s; };
-    auto full_b = [&](int s) { return base + kOffBar + 8u * (kStages + s); };
-    auto empty = [&](int s) { return base + kOffBar + 8u * (2 * kStages + s); };
-    const uint32_t accum_bar = base + kOffBar + 8u * (3 * kStages);
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + kOffMisc);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + kOffMisc + 4);
+    auto full_a = [&](int s) { return base + C::kOffBar + 8u * s; };
+    auto full_b = [&](int s) { return base + C::kOffBar + 8u * (kStages + s); };
+    auto empty = [&](int s) { return base + C::kOffBar + 8u * (2 * kStages + s); };
+    const uint32_t accum_bar = base + C::kOffBar + 8u * (3 * kStages);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + C::kOffMisc);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + C::kOffMisc + 4);
     const WaitCtx ctx{abort_flag, a.status};
 
     if (threadIdx.x == 0) {
@@ -223,10 +237,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_proxy();
     }
-    if (warp == 1) tmem_alloc(base + kOffMisc, kTmemCols);
+    if (warp == 1) tmem_alloc(base + C::kOffMisc, C::kTmemCols);
     if (warp >= 2) {   // the (format, scale) -> magnitudes table: 256 entries, 256 transcoder threads
         const int e = threadIdx.x - 64;
-        reinterpret_cast<uint4*>(gen + kOffLut)[e] = a.lut ? __ldg(a.lut + e) : make_lut_entry(e & 127, e >> 7, *a.global_scale);
+        reinterpret_cast<uint4*>(gen + C::kOffLut)[e] =
+            a.lut ? __ldg(a.lut + e) : make_lut_entry(e & 127, e >> 7, *a.global_scale);
     }
     tcgen05_fence_before();
     __syncthreads();
@@ -241,8 +256,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                 const int s = kt % kStages;
                 const uint32_t ph = (kt / kStages) & 1;
                 if (!mbar_wait(empty(s), ph ^ 1, ctx, 1)) break;
-                mbar_arrive_expect_tx(full_a(s), kABytes);
-                tma_load_2d(base + kOffA + s * kABytes, &tmap_x, full_a(s), kt * BK, (int)m0);
+                mbar_arrive_expect_tx(full_a(s), C::kABytes);
+                tma_load_2d(base + C::kOffA + s * C::kABytes, &tmap_x, full_a(s), kt * BK, (int)m0);
                 issued = kt + 1;
             }
             // never leave with a bulk copy still writing into this CTA's shared memory
@@ -259,77 +274,98 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                 ok = mbar_wait(full_a(s), ph, ctx, 3) && mbar_wait(full_b(s), ph, ctx, 4);
                 if (!ok) break;
                 tcgen05_fence_after();
-                const uint64_t da = make_smem_desc(base + kOffA + s * kABytes);
-                const uint64_t db = make_smem_desc(base + kOffB + s * kBBytes);
+                const uint64_t db = make_smem_desc(base + C::kOffB + s * C::kBBytes);
 #pragma unroll
-                for (int k = 0; k < BK / 16; ++k)      // +32 B per K step of 16: +2 in the address field
-                    umma_bf16(tmem_base, da + 2u * k, db + 2u * k, kInstrDesc, (kt | k) != 0 ? 1u : 0u);
+                for (int mt = 0; mt < kMT; ++mt) {     // 128-row sub-tile mt starts 16 KB further
+                    const uint64_t da = make_smem_desc(base + C::kOffA + s * C::kABytes + mt * 16384u);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)  // +32 B per K step of 16: +2 in the address field
+                        umma_bf16(tmem_base + mt * kBN, da + 2u * k, db + 2u * k, C::kInstrDesc,
+                                  (kt | k) != 0 ? 1u : 0u);
+                }
                 umma_commit(empty(s));                  // frees the stage when these MMAs are done
             }
             if (ok) umma_commit(accum_bar);
         }
     } else {
         // -------------------------------------------------- weight transcoders / epilogue
+        constexpr int kWords = C::kWords, kBlocks = kWords / 2;
         const int dt = threadIdx.x - 64;                // 0..255
-        const int row = dt & 127, half = dt >> 7;       // tile row, which 32-element half of the K step
+        const int row = dt % kBN, part = dt / kBN;      // tile row, which part of the K step
         const uint32_t last_row = (uint32_t)a.n - 1;
         const uint32_t grow = min(n0 + row, last_row);  // rows past N re-read the last row; never stored
-        const uint8_t* cptr = a.codes + (size_t)grow * (a.kpad / 2) + half * 16;
-        const uint8_t* sptr = a.scales + (size_t)grow * (a.kpad / 16) + half * 2;
+        const uint8_t* cptr = a.codes + (size_t)grow * (a.kpad / 2) + part * (kWords * 4);
+        const uint8_t* sptr = a.scales + (size_t)grow * (a.kpad / 16) + part * kBlocks;
         const uint8_t* fptr = kKL ? a.scales : a.fmt + (size_t)grow * (a.kpad / 128);   // unused for the kernel layout
-        const uint32_t lut_base = base + kOffLut;
-        // destination of this thread's four 16-byte chunks: row r, logical chunk c -> c ^ (r & 7)
+        const uint32_t lut_base = base + C::kOffLut;
+        // destination of this thread's 16-byte chunks: row r, logical chunk c -> c ^ (r & 7)
         const uint32_t row_off = (row >> 3) * 1024u + (row & 7) * 128u;
         const uint32_t sw = row & 7;
 
-        uint4 codes = __ldg(reinterpret_cast<const uint4*>(cptr));
-        uint32_t sc2 = __ldg(reinterpret_cast<const unsigned short*>(sptr));
+        auto load_codes = [&](uint32_t (&w)[kWords], int kt) {
+#pragma unroll
+            for (int j = 0; j < kWords / 4; ++j) {
+                const uint4 v = __ldg(reinterpret_cast<const uint4*>(cptr + (size_t)kt * 32) + j);
+                w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+            }
+        };
+        auto load_scales = [&](int kt) -> uint32_t {
+            if constexpr (kBlocks == 2) return __ldg(reinterpret_cast<const unsigned short*>(sptr + (size_t)kt * 4));
+            else return __ldg(reinterpret_cast<const unsigned int*>(sptr + (size_t)kt * 4));
+        };
+
+        uint32_t codes[kWords], ncodes[kWords];
+        load_codes(codes, 0);
+        uint32_t scs = load_scales(0);
         uint32_t fb = kKL ? 0u : __ldg(fptr);
         bool ok = true;
         for (int kt = 0; kt < num_kt; ++kt) {
             const int s = kt % kStages;
             const uint32_t ph = (kt / kStages) & 1;
-            uint4 ncodes = codes;
-            uint32_t nsc2 = sc2, nfb = fb;
+            uint32_t nscs = scs, nfb = fb;
             if (kt + 1 < num_kt) {                      // next K step's packed data, one step ahead
-                ncodes = __ldg(reinterpret_cast<const uint4*>(cptr + (size_t)(kt + 1) * 32));
-                nsc2 = __ldg(reinterpret_cast<const unsigned short*>(sptr + (size_t)(kt + 1) * 4));
+                load_codes(ncodes, kt + 1);
+                nscs = load_scales(kt + 1);
                 if constexpr (!kKL) nfb = __ldg(fptr + ((kt + 1) >> 1));
             }
             ok = mbar_wait(empty(s), ph ^ 1, ctx, 5);
             if (!ok) break;
-            const uint32_t dst = base + kOffB + s * kBBytes + row_off;
-            const uint32_t fbits = fb >> ((kt & 1) * 4 + half * 2);     // this thread's 2 blocks
+            const uint32_t dst = base + C::kOffB + s * C::kBBytes + row_off;
+            const uint32_t fbits = fb >> ((kt & 1) * 4 + part * kBlocks);     // this thread's blocks
 #pragma unroll
-            for (int b = 0; b < 2; ++b) {
-                const uint32_t idx = kKL ? ((sc2 >> (8 * b)) & 0xffu)
-                                         : ((((fbits >> b) & 1u) << 7) | ((sc2 >> (8 * b)) & 0x7fu));
+            for (int b = 0; b < kBlocks; ++b) {
+                const uint32_t idx = kKL ? ((scs >> (8 * b)) & 0xffu)
+                                         : ((((fbits >> b) & 1u) << 7) | ((scs >> (8 * b)) & 0x7fu));
                 const uint4 tab = lds128_lut(lut_base + idx * 16);
 #pragma unroll
                 for (int w = 0; w < 2; ++w) {
                     const int i = 2 * b + w;
                     uint32_t p[4];
-                    decode_word<kKL>(i == 0 ? codes.x : i == 1 ? codes.y : i == 2 ? codes.z : codes.w, tab, p);
-                    const uint32_t chunk = (uint32_t)(half * 4 + i) ^ sw;
+                    decode_word<kKL>(codes[i], tab, p);
+                    const uint32_t chunk = (uint32_t)(part * kWords + i) ^ sw;
                     sts128(dst + chunk * 16, p[0], p[1], p[2], p[3]);
                 }
             }
             fence_async_proxy();                        // generic-proxy stores -> visible to tcgen05
             __syncwarp();
             if (lane == 0) mbar_arrive(full_b(s));
-            codes = ncodes; sc2 = nsc2; fb = nfb;
+#pragma unroll
+            for (int i = 0; i < kWords; ++i) codes[i] = ncodes[i];
+            scs = nscs; fb = nfb;
         }
 
         // epilogue: TMEM lane quarter = warp % 4 (hardware rule), column half by warp group
         if (ok && mbar_wait(accum_bar, 0, ctx, 6)) {
             tcgen05_fence_after();
             const int q = warp & 3, ch = (warp - 2) >> 2;
-            const int64_t mrow = (int64_t)m0 + q * 32 + lane;
+            constexpr int kChunks = kBN / 64;           // 32-column chunks per warp and sub-tile
 #pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
-                const int col0 = ch * 64 + c * 32;
+            for (int it = 0; it < kMT * kChunks; ++it) {
+                const int mt = it / kChunks, c = it % kChunks;
+                const int64_t mrow = (int64_t)m0 + mt * 128 + q * 32 + lane;
+                const int col0 = ch * (kBN / 2) + c * 32;
                 uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)col0, r);
+                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(mt * kBN + col0), r);
                 const int64_t ncol = (int64_t)n0 + col0;
                 if (mrow < a.m && ncol < a.n) {
                     const bool full = ncol + 32 <= a.n;
@@ -372,7 +408,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     __syncthreads();
     if (warp == 1) {
         tcgen05_fence_after();
-        tmem_dealloc(tmem_base, kTmemCols);
+        tmem_dealloc(tmem_base, C::kTmemCols);
     }
 }
 
@@ -394,6 +430,32 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 int64_t x_staging_bytes(int64_t m, int64_t k) { return m * ((k + 7) / 8 * 8) * 2; }
+
+template <int kMT, int kBN, bool kKL>
+int launch_gemm(const void* xa, int64_t lda, const GemmArgs& a, cudaStream_t st) {
+    using C = Cfg<kMT, kBN>;
+    EncodeTiledFn encode = encode_tiled_fn();
+    if (!encode) return record_error_text("cuTensorMapEncodeTiled is not available from the driver");
+    CUtensorMap tmap;
+    const cuuint64_t dims[2] = {(cuuint64_t)a.k, (cuuint64_t)a.m};
+    const cuuint64_t strides[1] = {(cuuint64_t)lda * 2};
+    const cuuint32_t box[2] = {BK, (cuuint32_t)C::BM};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult cr = encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(xa), dims, strides, box,
+                               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) return record_error_text("cuTensorMapEncodeTiled failed");
+    static bool configured = false;          // one per instantiation
+    if (!configured) {
+        MIXFP4_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel<kMT, kBN, kKL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)C::kSmemBytes));
+        configured = true;
+    }
+    const dim3 grid((unsigned)((a.n + C::BN - 1) / C::BN), (unsigned)((a.m + C::BM - 1) / C::BM));
+    if (grid.y > 65535) return MIXFP4_E_SHAPE;
+    gemm_kernel<kMT, kBN, kKL><<<grid, kThreads, C::kSmemBytes, st>>>(tmap, a);
+    return check_launch("gemm_kernel");
+}
 
 }  // namespace
 }  // namespace mixfp4
@@ -438,35 +500,35 @@ extern "C" int mixfp4_gemm(const void* x, int64_t m, int64_t ldx, const uint8_t*
         xa = workspace;
     }
 
-    EncodeTiledFn encode = encode_tiled_fn();
-    if (!encode) return record_error_text("cuTensorMapEncodeTiled is not available from the driver");
-    CUtensorMap tmap;
-    const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)m};
-    const cuuint64_t strides[1] = {(cuuint64_t)lda * 2};
-    const cuuint32_t box[2] = {BK, BM};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult cr = encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(xa), dims, strides, box,
-                               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (cr != CUDA_SUCCESS) return record_error_text("cuTensorMapEncodeTiled failed");
-
-    static bool configured = false;
-    if (!configured) {
-        MIXFP4_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
-        MIXFP4_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
-        configured = true;
-    }
     GemmArgs a;
     a.codes = codes; a.scales = scales; a.fmt = fmt; a.global_scale = global_scale;
     a.lut = static_cast<const uint4*>(lut);
     a.m = m; a.n = n; a.k = k; a.kpad = padded_k(k);
     a.y = y; a.out_dtype = out_dtype; a.ldy = ldy; a.status = status;
-    const dim3 grid((unsigned)((n + BN - 1) / BN), (unsigned)((m + BM - 1) / BM));
-    if (grid.y > 65535) return MIXFP4_E_SHAPE;
-    if (layout == MIXFP4_LAYOUT_KERNEL) gemm_kernel<true><<<grid, kThreads, kSmemBytes, st>>>(tmap, a);
-    else gemm_kernel<false><<<grid, kThreads, kSmemBytes, st>>>(tmap, a);
-    return check_launch("gemm_kernel");
+    // Tile choice: estimated time = waves over the 148 SMs x relative time of one tile (measured:
+    // a tile with two 128-row sub-tiles or 256 weight rows amortises the transcode better).
+    int mt = 1, bn = 128;
+    {
+        const int mts[4] = {1, 2, 1, 2}, bns[4] = {128, 128, 256, 256};
+        const double cost[4] = {1.0, 1.35, 1.78, 2.2};
+        double best = 1e300;
+        for (int i = 0; i < 4; ++i) {
+            const int64_t tiles = ((m + 128 * mts[i] - 1) / (128 * mts[i])) * ((n + bns[i] - 1) / bns[i]);
+            const double t = (double)((tiles + 147) / 148) * cost[i];
+            if (t < best) { best = t; mt = mts[i]; bn = bns[i]; }
+        }
+    }
+    if (const char* e = getenv("MIXFP4_GEMM_TILE")) {   // TEMP tuning knob: "<mt>x<bn>"
+        int emt = 0, ebn = 0;
+        if (sscanf(e, "%dx%d", &emt, &ebn) == 2 && (emt == 1 || emt == 2) && (ebn == 128 || ebn == 256)) { mt = emt; bn = ebn; }
+    }
+    const bool kl = layout == MIXFP4_LAYOUT_KERNEL;
+    if (mt == 1 && bn == 128) return kl ? launch_gemm<1, 128, true>(xa, lda, a, st) : launch_gemm<1, 128, false>(xa, lda, a, st);
+    if (mt == 1 && bn == 256) return kl ? launch_gemm<1, 256, true>(xa, lda, a, st) : launch_gemm<1, 256, false>(xa, lda, a, st);
+    if (mt == 2 && bn == 128) return kl ? launch_gemm<2, 128, true>(xa, lda, a, st) : launch_gemm<2, 128, false>(xa, lda, a, st);
+    return kl ? launch_gemm<2, 256, true>(xa, lda, a, st) : launch_gemm<2, 256, false>(xa, lda, a, st);
 }
+
 
 // ------------------------------------------------------------- allocation-free variant
 // Staging buffer of mixfp4_gemm_h128_static: lives in the library image, so every GPU that

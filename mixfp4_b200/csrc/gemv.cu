@@ -25,6 +25,9 @@
 // 4-bit codes (one 32-bit word) become four bf16x2 registers with byte permutes
 // (decode.cuh).  The accumulation is the tensor core's fp32.
 
+#include <stdio.h>
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "decode.cuh"
 
@@ -89,63 +92,82 @@ __device__ __forceinline__ void sts128(uint32_t addr, const uint4& v) {
 // [row half][lane] 16 B, then the scales [row 0..15] 8 B.
 __host__ __device__ inline uint32_t stage_bytes(int64_t m) { return (uint32_t)m * 256u + 1024u + 128u; }
 
-template <int kWarps, int kNTiles, bool kKL>
+template <int kWarps, int kNTiles, bool kKL, int kU>
 __global__ void __launch_bounds__(kWarps * 32, kWarps == 16 ? 2 : 3) gemv_kernel(const GemvArgs a) {
     extern __shared__ __align__(16) uint8_t smem[];
-    // lut 4096 | red kWarps*16*8*kNTiles*4 | rings kWarps*kDepth*stage | (canonical) fmt bytes 16*ld_fmt
+    // lut 4096 | red kWarps*16*8*kNTiles*4 | rings kWarps*kDepth*kU*stage | (canonical) fmt bytes 16*ld_fmt
     constexpr int kRedBytes = kWarps * kRowsPerCta * 8 * kNTiles * 4;
     float* red = reinterpret_cast<float*>(smem + 4096);
     const uint32_t x_bytes = (uint32_t)a.m * 256u, stage = stage_bytes(a.m);
     const uint32_t off_codes = x_bytes, off_scales = x_bytes + 1024u, x_chunk = (uint32_t)a.m * 64u;
-    uint8_t* fmt_tab = smem + 4096 + kRedBytes + kWarps * kDepth * stage;
+    uint8_t* fmt_tab = smem + 4096 + kRedBytes + kWarps * kDepth * kU * stage;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const uint32_t row0 = blockIdx.x * kRowsPerCta;
     const uint32_t ld_codes = (uint32_t)(a.kpad >> 1), ld_scales = (uint32_t)(a.kpad >> 4);
     const uint32_t ld_fmt = (uint32_t)(a.kpad >> 7);
-    const int steps = static_cast<int>(a.kpad / kStepK);
+    const int subs = static_cast<int>(a.kpad / kStepK);     // 128-element sub-steps along K
+    const int steps = (subs + kU - 1) / kU;
     const uint32_t last_row = (uint32_t)a.n - 1;
     // rows past N re-read the last row; their sums are never stored
     const uint32_t r0 = min(row0 + g, last_row), r1 = min(row0 + g + 8, last_row);
     const uint8_t* cptr[2] = {a.codes + (size_t)r0 * ld_codes + t * 16, a.codes + (size_t)r1 * ld_codes + t * 16};
     const uint8_t* sptr = a.scales + (size_t)(t == 0 ? r0 : r1) * ld_scales;   // used by lanes t < 2
     const uint32_t lut_base = (uint32_t)__cvta_generic_to_shared(smem);
-    const uint32_t ring = lut_base + 4096 + kRedBytes + warp * kDepth * stage;
+    const uint32_t ring = lut_base + 4096 + kRedBytes + warp * kDepth * kU * stage;
     const uint32_t k_lim = (uint32_t)a.k;
     bool x_ok[kNTiles];
     const __nv_bfloat16* xptr[kNTiles];
+    uint32_t xrow_off[kNTiles];
 #pragma unroll
     for (int nt = 0; nt < kNTiles; ++nt) {
         x_ok[nt] = g + 8 * nt < a.m;
         xptr[nt] = a.x + (size_t)(x_ok[nt] ? g + 8 * nt : 0) * a.ldx + t * 32;
+        xrow_off[nt] = (x_ok[nt] ? (uint32_t)(g + 8 * nt) * 64u : 0u) + t * 16;
     }
+    const bool full_k = a.k == a.kpad;                  // no K tail: every x chunk is in range
 
-    auto issue_weights = [&](int step) {
-        const uint32_t base = ring + (uint32_t)(step / kWarps % kDepth) * stage;
+    // A step is kU consecutive 128-element sub-steps handled back to back (shared waits and
+    // loop overhead); ring slot = kU sub-step stages.
+    const uint32_t slot_bytes = kU * stage;
+    auto issue_weights = [&](int step, uint32_t slot) {
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
-            cp_async16_stream(base + off_codes + h * 512 + lane * 16, cptr[h] + (size_t)step * 64);
-        if (t < 2) cp_async8(base + off_scales + (g + 8 * t) * 8, sptr + (size_t)step * 8);
+        for (int j = 0; j < kU; ++j) {
+            const int sub = step * kU + j;
+            if (sub >= subs) break;
+            const uint32_t base = ring + slot * slot_bytes + j * stage;
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+                cp_async16_stream(base + off_codes + h * 512 + lane * 16, cptr[h] + (size_t)sub * 64);
+            if (t < 2) cp_async8(base + off_scales + (g + 8 * t) * 8, sptr + (size_t)sub * 8);
+        }
     };
-    auto issue_x = [&](int step) {
-        const uint32_t base = ring + (uint32_t)(step / kWarps % kDepth) * stage;
+    auto issue_x = [&](int step, uint32_t slot) {
 #pragma unroll
-        for (int nt = 0; nt < kNTiles; ++nt) {
-            if (!x_ok[nt]) continue;
+        for (int j = 0; j < kU; ++j) {
+            const int sub = step * kU + j;
+            if (sub >= subs) break;
+            const uint32_t base = ring + slot * slot_bytes + j * stage;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const uint32_t kk = (uint32_t)step * kStepK + t * 32 + c * 8;
-                const uint32_t dst = base + c * x_chunk + (g + 8 * nt) * 64 + t * 16;
-                const __nv_bfloat16* src = xptr[nt] + (size_t)step * kStepK + c * 8;
-                if (a.x_vec) {   // K % 8 == 0: a chunk is all inside or all outside (zero-filled)
-                    const bool in = kk < k_lim;
-                    cp_async16(dst, in ? static_cast<const void*>(src) : static_cast<const void*>(a.x), in ? 16u : 0u);
-                } else {         // unaligned x: plain guarded loads, stored by the lane that reads them back
-                    uint32_t e[8];
+            for (int nt = 0; nt < kNTiles; ++nt) {
+                if (!x_ok[nt]) continue;
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) e[j] = kk + j < k_lim ? __bfloat16_as_ushort(src[j]) : 0u;
-                    sts128(dst, make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16)));
+                for (int c = 0; c < 4; ++c) {
+                    const uint32_t kk = (uint32_t)sub * kStepK + t * 32 + c * 8;
+                    const uint32_t dst = base + c * x_chunk + (g + 8 * nt) * 64 + t * 16;
+                    const __nv_bfloat16* src = xptr[nt] + (size_t)sub * kStepK + c * 8;
+                    if (a.x_vec && full_k) {
+                        cp_async16(dst, src, 16u);
+                    } else if (a.x_vec) {   // K % 8 == 0: a chunk is all inside or all outside (zero-filled)
+                        const bool in = kk < k_lim;
+                        cp_async16(dst, in ? static_cast<const void*>(src) : static_cast<const void*>(a.x), in ? 16u : 0u);
+                    } else {         // unaligned x: plain guarded loads, stored by the lane that reads them back
+                        uint32_t e[8];
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) e[q] = kk + q < k_lim ? __bfloat16_as_ushort(src[q]) : 0u;
+                        sts128(dst, make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16)));
+                    }
                 }
             }
         }
@@ -154,7 +176,7 @@ __global__ void __launch_bounds__(kWarps * 32, kWarps == 16 ? 2 : 3) gemv_kernel
     // Prologue.  Weights first: they never depend on the previous kernel in the stream.
 #pragma unroll
     for (int d = 0; d < kDepth - 1; ++d)
-        if (warp + d * kWarps < steps) issue_weights(warp + d * kWarps);
+        if (warp + d * kWarps < steps) issue_weights(warp + d * kWarps, d);
     if (a.lut) {
         for (int e = threadIdx.x; e < 256; e += kWarps * 32) cp_async16(lut_base + e * 16, a.lut + e, 16u);
     } else {
@@ -174,7 +196,7 @@ __global__ void __launch_bounds__(kWarps * 32, kWarps == 16 ? 2 : 3) gemv_kernel
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 #pragma unroll
     for (int d = 0; d < kDepth - 1; ++d) {
-        if (warp + d * kWarps < steps) issue_x(warp + d * kWarps);
+        if (warp + d * kWarps < steps) issue_x(warp + d * kWarps, d);
         cp_async_commit();                 // group d: x of step d (+ every earlier copy)
     }
     cp_async_wait<kDepth - 2>();           // table copies (part of the first group) have landed
@@ -186,44 +208,53 @@ __global__ void __launch_bounds__(kWarps * 32, kWarps == 16 ? 2 : 3) gemv_kernel
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[nt][i] = 0.0f;
 
+    uint32_t use_slot = 0, fill_slot = kDepth - 1;
     for (int step = warp; step < steps; step += kWarps) {
-        // the stage written now was read in the previous iteration: all lanes must be done with it
+        // the slot written now was read in the previous iteration: all lanes must be done with it
         __syncwarp();
         const int ahead = step + (kDepth - 1) * kWarps;
-        if (ahead < steps) { issue_weights(ahead); issue_x(ahead); }
+        if (ahead < steps) { issue_weights(ahead, fill_slot); issue_x(ahead, fill_slot); }
         cp_async_commit();
         cp_async_wait<kDepth - 1>();
         __syncwarp();                                        // scale bytes come from another lane's copy
-        const uint32_t base = ring + (uint32_t)(step / kWarps % kDepth) * stage;
-        const uint4 cl = lds128(base + off_codes + lane * 16);
-        const uint4 ch = lds128(base + off_codes + 512 + lane * 16);
-        uint32_t sl = lds16(base + off_scales + g * 8 + t * 2);
-        uint32_t sh = lds16(base + off_scales + (g + 8) * 8 + t * 2);
-        if constexpr (!kKL) {   // canonical: merge the format bits into bit 7 of each scale byte
-            const uint32_t fl = fmt_tab[g * ld_fmt + step] >> (2 * t);
-            const uint32_t fh = fmt_tab[(g + 8) * ld_fmt + step] >> (2 * t);
-            sl = (sl & 0x7f7fu) | ((fl & 1u) << 7) | ((fl & 2u) << 14);
-            sh = (sh & 0x7f7fu) | ((fh & 1u) << 7) | ((fh & 2u) << 14);
-        }
 #pragma unroll
-        for (int b = 0; b < 2; ++b) {                        // the 2 blocks of this lane's piece
-            const uint4 tl = lds128(lut_base + ((sl >> (8 * b)) & 0xffu) * 16);
-            const uint4 th = lds128(lut_base + ((sh >> (8 * b)) & 0xffu) * 16);
+        for (int j = 0; j < kU; ++j) {
+            const int sub = step * kU + j;
+            if (sub >= subs) break;
+            const uint32_t base = ring + use_slot * slot_bytes + j * stage;
+            const uint4 cl = lds128(base + off_codes + lane * 16);
+            const uint4 ch = lds128(base + off_codes + 512 + lane * 16);
+            uint32_t sl = lds16(base + off_scales + g * 8 + t * 2);
+            uint32_t sh = lds16(base + off_scales + (g + 8) * 8 + t * 2);
+            if constexpr (!kKL) {   // canonical: merge the format bits into bit 7 of each scale byte
+                const uint32_t fl = fmt_tab[g * ld_fmt + sub] >> (2 * t);
+                const uint32_t fh = fmt_tab[(g + 8) * ld_fmt + sub] >> (2 * t);
+                sl = (sl & 0x7f7fu) | ((fl & 1u) << 7) | ((fl & 2u) << 14);
+                sh = (sh & 0x7f7fu) | ((fh & 1u) << 7) | ((fh & 2u) << 14);
+            }
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {           // 8 elements = 2 MMAs
-                const int i = 2 * b + half;                  // word index inside the piece
-                uint32_t pl[4], ph[4];
-                decode_word<kKL>(i == 0 ? cl.x : i == 1 ? cl.y : i == 2 ? cl.z : cl.w, tl, pl);
-                decode_word<kKL>(i == 0 ? ch.x : i == 1 ? ch.y : i == 2 ? ch.z : ch.w, th, ph);
+            for (int b = 0; b < 2; ++b) {                        // the 2 blocks of this lane's piece
+                const uint4 tl = lds128(lut_base + ((sl >> (8 * b)) & 0xffu) * 16);
+                const uint4 th = lds128(lut_base + ((sh >> (8 * b)) & 0xffu) * 16);
 #pragma unroll
-                for (int nt = 0; nt < kNTiles; ++nt) {
-                    uint4 xv = make_uint4(0, 0, 0, 0);
-                    if (x_ok[nt]) xv = lds128(base + i * x_chunk + (g + 8 * nt) * 64 + t * 16);
-                    mma_bf16(acc[nt], pl[0], ph[0], pl[1], ph[1], xv.x, xv.y);
-                    mma_bf16(acc[nt], pl[2], ph[2], pl[3], ph[3], xv.z, xv.w);
+                for (int half = 0; half < 2; ++half) {           // 8 elements = 2 MMAs
+                    const int i = 2 * b + half;                  // word index inside the piece
+                    uint32_t pl[4], ph[4];
+                    decode_word<kKL>(i == 0 ? cl.x : i == 1 ? cl.y : i == 2 ? cl.z : cl.w, tl, pl);
+                    decode_word<kKL>(i == 0 ? ch.x : i == 1 ? ch.y : i == 2 ? ch.z : ch.w, th, ph);
+#pragma unroll
+                    for (int nt = 0; nt < kNTiles; ++nt) {
+                        // lanes of absent batch rows re-read row 0 (same address: a broadcast);
+                        // their accumulator columns are never stored
+                        const uint4 xv = lds128(base + i * x_chunk + xrow_off[nt]);
+                        mma_bf16(acc[nt], pl[0], ph[0], pl[1], ph[1], xv.x, xv.y);
+                        mma_bf16(acc[nt], pl[2], ph[2], pl[3], ph[3], xv.z, xv.w);
+                    }
                 }
             }
         }
+        use_slot = use_slot + 1 == kDepth ? 0 : use_slot + 1;
+        fill_slot = fill_slot + 1 == kDepth ? 0 : fill_slot + 1;
     }
     cp_async_wait<0>();
 
@@ -249,15 +280,15 @@ __global__ void __launch_bounds__(kWarps * 32, kWarps == 16 ? 2 : 3) gemv_kernel
     }
 }
 
-template <int kWarps, int kNTiles, bool kKL>
+template <int kWarps, int kNTiles, bool kKL, int kU>
 int launch(const GemvArgs& a, int flags, cudaStream_t st) {
     const int64_t ctas = (a.n + kRowsPerCta - 1) / kRowsPerCta;
     const size_t smem = 4096 + (size_t)kWarps * kRowsPerCta * 8 * kNTiles * 4 +
-                        (size_t)kWarps * kDepth * stage_bytes(a.m) + (kKL ? 0 : (size_t)kRowsPerCta * (a.kpad / 128));
+                        (size_t)kWarps * kDepth * kU * stage_bytes(a.m) + (kKL ? 0 : (size_t)kRowsPerCta * (a.kpad / 128));
     if (smem > 200 * 1024 || ctas > 0x7fffffffLL) return MIXFP4_E_SHAPE;
     static bool configured = false;          // one per instantiation
     if (!configured) {
-        MIXFP4_CUDA_CHECK(cudaFuncSetAttribute(gemv_kernel<kWarps, kNTiles, kKL>,
+        MIXFP4_CUDA_CHECK(cudaFuncSetAttribute(gemv_kernel<kWarps, kNTiles, kKL, kU>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         configured = true;
     }
@@ -271,15 +302,20 @@ int launch(const GemvArgs& a, int flags, cudaStream_t st) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (flags & MIXFP4_FLAG_OVERLAP_PREVIOUS) ? 1 : 0;
-    MIXFP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemv_kernel<kWarps, kNTiles, kKL>, a));
+    MIXFP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemv_kernel<kWarps, kNTiles, kKL, kU>, a));
     return MIXFP4_OK;
 }
 
 template <bool kKL>
 int dispatch(const GemvArgs& a, int flags, cudaStream_t st) {
-    const bool wide = a.kpad / kStepK >= 32 && a.m <= 4;
-    if (a.m <= 8) return wide ? launch<16, 1, kKL>(a, flags, st) : launch<8, 1, kKL>(a, flags, st);
-    return launch<8, 2, kKL>(a, flags, st);
+    const int64_t subs = a.kpad / kStepK;
+    int warps = 8, unroll = subs >= 32 ? 2 : 1;
+    if (8 * kDepth * 2 * (int64_t)stage_bytes(a.m) > 160 * 1024) unroll = 1;
+    if (const char* e = getenv("MIXFP4_GEMV_CFG")) sscanf(e, "%dx%d", &warps, &unroll);   // TEMP tuning knob
+    if (a.m > 8) return unroll == 2 ? launch<8, 2, kKL, 2>(a, flags, st) : launch<8, 2, kKL, 1>(a, flags, st);
+    if (warps == 16) return unroll == 2 ? launch<16, 1, kKL, 2>(a, flags, st) : launch<16, 1, kKL, 1>(a, flags, st);
+    if (warps == 4) return unroll == 2 ? launch<4, 1, kKL, 2>(a, flags, st) : launch<4, 1, kKL, 1>(a, flags, st);
+    return unroll == 2 ? launch<8, 1, kKL, 2>(a, flags, st) : launch<8, 1, kKL, 1>(a, flags, st);
 }
 
 }  // namespace
