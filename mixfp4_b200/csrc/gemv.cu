@@ -36,7 +36,10 @@ namespace {
 
 constexpr int kRowsPerCta = 16;
 constexpr int kStepK = 128;               // K elements one warp consumes per step
-constexpr int kDepth = 3;                 // ring stages per warp
+// The decode table is kept kLutRep times in shared memory, lane t of a quad reading copy t: lanes
+// of a quad then never collide on a bank, which removes most conflicts of the random lookups.
+constexpr int kLutRep = 4;
+constexpr int kLutBytes = 4096 * kLutRep;
 
 struct GemvArgs {
     const __nv_bfloat16* x;
@@ -90,33 +93,41 @@ __device__ __forceinline__ void sts128(uint32_t addr, const uint4& v) {
 
 // One ring stage of a warp: x [chunk 0..3][batch row][t] 16 B (m * 256 bytes), then the codes
 // [row half][lane] 16 B, then the scales [row 0..15] 8 B.
-__host__ __device__ inline uint32_t stage_bytes(int64_t m) { return (uint32_t)m * 256u + 1024u + 128u; }
+__host__ __device__ inline uint32_t stage_bytes(int64_t m, bool x_resident) {
+    return (x_resident ? 0u : (uint32_t)m * 256u) + 1024u + 128u;
+}
+// With x resident in shared memory (small M*K) a row of x takes kpad*2 + 16 bytes (the pad
+// staggers the banks of different batch rows).
+__host__ __device__ inline uint32_t xres_row_bytes(int64_t kpad) { return (uint32_t)kpad * 2u + 16u; }
 
-template <int kWarps, int kNTiles, bool kKL, int kU>
+template <int kWarps, int kNTiles, bool kKL, int kU, int kDepth, bool kXRes>
 __global__ void __launch_bounds__(kWarps * 32, kWarps == 16 ? 2 : 3) gemv_kernel(const GemvArgs a) {
     extern __shared__ __align__(16) uint8_t smem[];
-    // lut 4096 | red kWarps*16*8*kNTiles*4 | rings kWarps*kDepth*kU*stage | (canonical) fmt bytes 16*ld_fmt
-    constexpr int kRedBytes = kWarps * kRowsPerCta * 8 * kNTiles * 4;
-    float* red = reinterpret_cast<float*>(smem + 4096);
-    const uint32_t x_bytes = (uint32_t)a.m * 256u, stage = stage_bytes(a.m);
+    // lut kLutBytes | red 2*kWarps*16*8*kNTiles*4 | rings kWarps*kDepth*kU*stage | (canonical) fmt bytes 16*ld_fmt
+    constexpr int kCols = 8 * kNTiles;
+    constexpr int kRedBytes = 2 * kWarps * kRowsPerCta * kCols * 4;
+    float* red = reinterpret_cast<float*>(smem + kLutBytes);
+    const uint32_t x_bytes = kXRes ? 0u : (uint32_t)a.m * 256u, stage = stage_bytes(a.m, kXRes);
     const uint32_t off_codes = x_bytes, off_scales = x_bytes + 1024u, x_chunk = (uint32_t)a.m * 64u;
-    uint8_t* fmt_tab = smem + 4096 + kRedBytes + kWarps * kDepth * kU * stage;
+    uint8_t* fmt_tab = smem + kLutBytes + kRedBytes + kWarps * kDepth * kU * stage;
+    // resident x (if any) sits after the format bytes, 16-byte aligned
+    const uint32_t xres_off = ((uint32_t)kLutBytes + kRedBytes + kWarps * kDepth * kU * stage +
+                               (kKL ? 0u : (uint32_t)kRowsPerCta * (uint32_t)(a.kpad >> 7)) + 15u) & ~15u;
+    const uint32_t xres_rs = xres_row_bytes(a.kpad);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const uint32_t row0 = blockIdx.x * kRowsPerCta;
     const uint32_t ld_codes = (uint32_t)(a.kpad >> 1), ld_scales = (uint32_t)(a.kpad >> 4);
     const uint32_t ld_fmt = (uint32_t)(a.kpad >> 7);
     const int subs = static_cast<int>(a.kpad / kStepK);     // 128-element sub-steps along K
-    const int steps = (subs + kU - 1) / kU;
+    const int steps = (subs + kU - 1) / kU;                 // steps of a tile
+    const int spw = (steps + kWarps - 1) / kWarps;          // steps per warp and tile (some may be empty)
     const uint32_t last_row = (uint32_t)a.n - 1;
-    // rows past N re-read the last row; their sums are never stored
-    const uint32_t r0 = min(row0 + g, last_row), r1 = min(row0 + g + 8, last_row);
-    const uint8_t* cptr[2] = {a.codes + (size_t)r0 * ld_codes + t * 16, a.codes + (size_t)r1 * ld_codes + t * 16};
-    const uint8_t* sptr = a.scales + (size_t)(t == 0 ? r0 : r1) * ld_scales;   // used by lanes t < 2
+    const int ntiles = static_cast<int>((a.n + kRowsPerCta - 1) / kRowsPerCta);
     const uint32_t lut_base = (uint32_t)__cvta_generic_to_shared(smem);
-    const uint32_t ring = lut_base + 4096 + kRedBytes + warp * kDepth * kU * stage;
+    const uint32_t ring = lut_base + kLutBytes + kRedBytes + warp * kDepth * kU * stage;
     const uint32_t k_lim = (uint32_t)a.k;
+    const bool full_k = a.k == a.kpad;                      // no K tail: every x chunk is in range
     bool x_ok[kNTiles];
     const __nv_bfloat16* xptr[kNTiles];
     uint32_t xrow_off[kNTiles];
@@ -124,12 +135,24 @@ __global__ void __launch_bounds__(kWarps * 32, kWarps == 16 ? 2 : 3) gemv_kernel
     for (int nt = 0; nt < kNTiles; ++nt) {
         x_ok[nt] = g + 8 * nt < a.m;
         xptr[nt] = a.x + (size_t)(x_ok[nt] ? g + 8 * nt : 0) * a.ldx + t * 32;
-        xrow_off[nt] = (x_ok[nt] ? (uint32_t)(g + 8 * nt) * 64u : 0u) + t * 16;
+        if (kXRes) xrow_off[nt] = (x_ok[nt] ? (uint32_t)(g + 8 * nt) * xres_rs : 0u) + t * 64;
+        else xrow_off[nt] = (x_ok[nt] ? (uint32_t)(g + 8 * nt) * 64u : 0u) + t * 16;
     }
-    const bool full_k = a.k == a.kpad;                  // no K tail: every x chunk is in range
 
-    // A step is kU consecutive 128-element sub-steps handled back to back (shared waits and
-    // loop overhead); ring slot = kU sub-step stages.
+    // The CTA walks over row tiles blockIdx.x, blockIdx.x + gridDim.x, ...; every warp sees the
+    // flat sequence (tile, its j-th step of that tile) and prefetches kDepth-1 entries ahead of
+    // the arithmetic, across tile boundaries, so the weight stream never drains.
+    // Prefetch cursor:
+    int p_tile = blockIdx.x, p_j = 0;
+    const uint8_t* pc[2] = {a.codes, a.codes};
+    const uint8_t* ps = a.scales;
+    auto set_rows = [&]() {     // rows past N re-read the last row; their sums are never stored
+        const uint32_t row0 = (uint32_t)p_tile * kRowsPerCta;
+        const uint32_t r0 = min(row0 + g, last_row), r1 = min(row0 + g + 8, last_row);
+        pc[0] = a.codes + (size_t)r0 * ld_codes + t * 16;
+        pc[1] = a.codes + (size_t)r1 * ld_codes + t * 16;
+        ps = a.scales + (size_t)(t == 0 ? r0 : r1) * ld_scales;   // used by lanes t < 2
+    };
     const uint32_t slot_bytes = kU * stage;
     auto issue_weights = [&](int step, uint32_t slot) {
 #pragma unroll
@@ -139,8 +162,8 @@ __global__ void __launch_bounds__(kWarps * 32, kWarps == 16 ? 2 : 3) gemv_kernel
             const uint32_t base = ring + slot * slot_bytes + j * stage;
 #pragma unroll
             for (int h = 0; h < 2; ++h)
-                cp_async16_stream(base + off_codes + h * 512 + lane * 16, cptr[h] + (size_t)sub * 64);
-            if (t < 2) cp_async8(base + off_scales + (g + 8 * t) * 8, sptr + (size_t)sub * 8);
+                cp_async16_stream(base + off_codes + h * 512 + lane * 16, pc[h] + (size_t)sub * 64);
+            if (t < 2) cp_async8(base + off_scales + (g + 8 * t) * 8, ps + (size_t)sub * 8);
         }
     };
     auto issue_x = [&](int step, uint32_t slot) {
@@ -172,19 +195,34 @@ __global__ void __launch_bounds__(kWarps * 32, kWarps == 16 ? 2 : 3) gemv_kernel
             }
         }
     };
+    // Issue the entry under the prefetch cursor (if any) into `slot`, then advance the cursor.
+    auto prefetch = [&](uint32_t slot, bool weights, bool xs) {
+        if (p_tile < ntiles) {
+            const int step = warp + p_j * kWarps;
+            if (step < steps) {
+                if (weights) issue_weights(step, slot);
+                if (xs && !kXRes) issue_x(step, slot);
+            }
+        }
+    };
+    auto advance = [&]() {
+        if (++p_j == spw) { p_j = 0; p_tile += gridDim.x; if (p_tile < ntiles) set_rows(); }
+    };
 
     // Prologue.  Weights first: they never depend on the previous kernel in the stream.
+    set_rows();
 #pragma unroll
-    for (int d = 0; d < kDepth - 1; ++d)
-        if (warp + d * kWarps < steps) issue_weights(warp + d * kWarps, d);
-    if (a.lut) {
-        for (int e = threadIdx.x; e < 256; e += kWarps * 32) cp_async16(lut_base + e * 16, a.lut + e, 16u);
-    } else {
-        const float gs = *a.global_scale;
-        for (int e = threadIdx.x; e < 256; e += kWarps * 32)
-            reinterpret_cast<uint4*>(smem)[e] = make_lut_entry(e & 127, e >> 7, gs);
+    for (int d = 0; d < kDepth - 1; ++d) { prefetch(d, true, false); advance(); }
+    {
+        const float gs = a.lut ? 0.0f : *a.global_scale;
+        for (int e = threadIdx.x; e < 256; e += kWarps * 32) {
+            const uint4 v = a.lut ? __ldg(a.lut + e) : make_lut_entry(e & 127, e >> 7, gs);
+#pragma unroll
+            for (int r = 0; r < kLutRep; ++r) sts128(lut_base + e * (16 * kLutRep) + r * 16, v);
+        }
     }
-    if constexpr (!kKL) {
+    if constexpr (!kKL) {   // canonical layout: the host launches one tile per CTA
+        const uint32_t row0 = blockIdx.x * kRowsPerCta;
         for (uint32_t i = threadIdx.x; i < kRowsPerCta * ld_fmt; i += kWarps * 32) {
             const uint32_t r = min(row0 + i / ld_fmt, last_row);
             fmt_tab[i] = __ldg(a.fmt + (size_t)r * ld_fmt + i % ld_fmt);
@@ -194,101 +232,141 @@ __global__ void __launch_bounds__(kWarps * 32, kWarps == 16 ? 2 : 3) gemv_kernel
     // and let the next kernel in the stream start its own weight prefetch.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if constexpr (kXRes) {   // the whole x (m rows, zero-filled to kpad) once per CTA
+        const uint32_t chunks_per_row = (uint32_t)(a.kpad >> 3);
+        const uint32_t xres_base = lut_base + xres_off;
+        for (uint32_t i = threadIdx.x; i < (uint32_t)a.m * chunks_per_row; i += kWarps * 32) {
+            const uint32_t r = i / chunks_per_row, c = i - r * chunks_per_row;
+            const uint32_t dst = xres_base + r * xres_rs + c * 16;
+            const __nv_bfloat16* src = a.x + (size_t)r * a.ldx + c * 8;
+            if (a.x_vec) {
+                const bool in = c * 8 < k_lim;
+                cp_async16(dst, in ? static_cast<const void*>(src) : static_cast<const void*>(a.x), in ? 16u : 0u);
+            } else {
+                uint32_t e[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) e[q] = c * 8 + q < k_lim ? __bfloat16_as_ushort(src[q]) : 0u;
+                sts128(dst, make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16)));
+            }
+        }
+    }
+    p_tile = blockIdx.x; p_j = 0;
+    set_rows();
 #pragma unroll
     for (int d = 0; d < kDepth - 1; ++d) {
-        if (warp + d * kWarps < steps) issue_x(warp + d * kWarps, d);
-        cp_async_commit();                 // group d: x of step d (+ every earlier copy)
+        prefetch(d, false, true);
+        advance();
+        cp_async_commit();                 // group d: x of entry d (+ every earlier copy)
     }
     cp_async_wait<kDepth - 2>();           // table copies (part of the first group) have landed
     __syncthreads();
 
-    float acc[kNTiles][4];
+    float acc[kNTiles][2][4];           // two independent accumulation chains per output tile
 #pragma unroll
     for (int nt = 0; nt < kNTiles; ++nt)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) acc[nt][i] = 0.0f;
+        for (int i = 0; i < 4; ++i) acc[nt][0][i] = acc[nt][1][i] = 0.0f;
+    const uint32_t xres_base = lut_base + xres_off;
 
-    uint32_t use_slot = 0, fill_slot = kDepth - 1;
-    for (int step = warp; step < steps; step += kWarps) {
-        // the slot written now was read in the previous iteration: all lanes must be done with it
-        __syncwarp();
-        const int ahead = step + (kDepth - 1) * kWarps;
-        if (ahead < steps) { issue_weights(ahead, fill_slot); issue_x(ahead, fill_slot); }
-        cp_async_commit();
-        cp_async_wait<kDepth - 1>();
-        __syncwarp();                                        // scale bytes come from another lane's copy
+    uint32_t use_slot = 0, fill_slot = kDepth - 1, parity = 0;
+    for (int c_tile = blockIdx.x; c_tile < ntiles; c_tile += gridDim.x) {
+        for (int c_j = 0; c_j < spw; ++c_j) {
+            // the slot written now was read in the previous iteration: all lanes must be done with it
+            __syncwarp();
+            prefetch(fill_slot, true, true);
+            advance();
+            cp_async_commit();
+            cp_async_wait<kDepth - 1>();
+            __syncwarp();                                    // scale bytes come from another lane's copy
+            const int step = warp + c_j * kWarps;
+            if (step < steps) {
 #pragma unroll
-        for (int j = 0; j < kU; ++j) {
-            const int sub = step * kU + j;
-            if (sub >= subs) break;
-            const uint32_t base = ring + use_slot * slot_bytes + j * stage;
-            const uint4 cl = lds128(base + off_codes + lane * 16);
-            const uint4 ch = lds128(base + off_codes + 512 + lane * 16);
-            uint32_t sl = lds16(base + off_scales + g * 8 + t * 2);
-            uint32_t sh = lds16(base + off_scales + (g + 8) * 8 + t * 2);
-            if constexpr (!kKL) {   // canonical: merge the format bits into bit 7 of each scale byte
-                const uint32_t fl = fmt_tab[g * ld_fmt + sub] >> (2 * t);
-                const uint32_t fh = fmt_tab[(g + 8) * ld_fmt + sub] >> (2 * t);
-                sl = (sl & 0x7f7fu) | ((fl & 1u) << 7) | ((fl & 2u) << 14);
-                sh = (sh & 0x7f7fu) | ((fh & 1u) << 7) | ((fh & 2u) << 14);
-            }
+                for (int j = 0; j < kU; ++j) {
+                    const int sub = step * kU + j;
+                    if (sub >= subs) break;
+                    const uint32_t base = ring + use_slot * slot_bytes + j * stage;
+                    const uint4 cl = lds128(base + off_codes + lane * 16);
+                    const uint4 ch = lds128(base + off_codes + 512 + lane * 16);
+                    uint32_t sl = lds16(base + off_scales + g * 8 + t * 2);
+                    uint32_t sh = lds16(base + off_scales + (g + 8) * 8 + t * 2);
+                    if constexpr (!kKL) {   // canonical: merge the format bits into bit 7 of each scale byte
+                        const uint32_t fl = fmt_tab[g * ld_fmt + sub] >> (2 * t);
+                        const uint32_t fh = fmt_tab[(g + 8) * ld_fmt + sub] >> (2 * t);
+                        sl = (sl & 0x7f7fu) | ((fl & 1u) << 7) | ((fl & 2u) << 14);
+                        sh = (sh & 0x7f7fu) | ((fh & 1u) << 7) | ((fh & 2u) << 14);
+                    }
 #pragma unroll
-            for (int b = 0; b < 2; ++b) {                        // the 2 blocks of this lane's piece
-                const uint4 tl = lds128(lut_base + ((sl >> (8 * b)) & 0xffu) * 16);
-                const uint4 th = lds128(lut_base + ((sh >> (8 * b)) & 0xffu) * 16);
+                    for (int b = 0; b < 2; ++b) {                    // the 2 blocks of this lane's piece
+                        const uint4 tl = lds128(lut_base + ((sl >> (8 * b)) & 0xffu) * (16 * kLutRep) + t * 16);
+                        const uint4 th = lds128(lut_base + ((sh >> (8 * b)) & 0xffu) * (16 * kLutRep) + t * 16);
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {           // 8 elements = 2 MMAs
-                    const int i = 2 * b + half;                  // word index inside the piece
-                    uint32_t pl[4], ph[4];
-                    decode_word<kKL>(i == 0 ? cl.x : i == 1 ? cl.y : i == 2 ? cl.z : cl.w, tl, pl);
-                    decode_word<kKL>(i == 0 ? ch.x : i == 1 ? ch.y : i == 2 ? ch.z : ch.w, th, ph);
+                        for (int half = 0; half < 2; ++half) {       // 8 elements = 2 MMAs
+                            const int i = 2 * b + half;              // word index inside the piece
+                            uint32_t pl[4], ph[4];
+                            decode_word<kKL>(i == 0 ? cl.x : i == 1 ? cl.y : i == 2 ? cl.z : cl.w, tl, pl);
+                            decode_word<kKL>(i == 0 ? ch.x : i == 1 ? ch.y : i == 2 ? ch.z : ch.w, th, ph);
 #pragma unroll
-                    for (int nt = 0; nt < kNTiles; ++nt) {
-                        // lanes of absent batch rows re-read row 0 (same address: a broadcast);
-                        // their accumulator columns are never stored
-                        const uint4 xv = lds128(base + i * x_chunk + xrow_off[nt]);
-                        mma_bf16(acc[nt], pl[0], ph[0], pl[1], ph[1], xv.x, xv.y);
-                        mma_bf16(acc[nt], pl[2], ph[2], pl[3], ph[3], xv.z, xv.w);
+                            for (int nt = 0; nt < kNTiles; ++nt) {
+                                // lanes of absent batch rows re-read row 0 (same address: a broadcast);
+                                // their accumulator columns are never stored
+                                const uint4 xv = kXRes ? lds128(xres_base + xrow_off[nt] + (uint32_t)sub * 256u + i * 16)
+                                                       : lds128(base + i * x_chunk + xrow_off[nt]);
+                                mma_bf16(acc[nt][0], pl[0], ph[0], pl[1], ph[1], xv.x, xv.y);
+                                mma_bf16(acc[nt][1], pl[2], ph[2], pl[3], ph[3], xv.z, xv.w);
+                            }
+                        }
                     }
                 }
             }
+            use_slot = use_slot + 1 == kDepth ? 0 : use_slot + 1;
+            fill_slot = fill_slot + 1 == kDepth ? 0 : fill_slot + 1;
         }
-        use_slot = use_slot + 1 == kDepth ? 0 : use_slot + 1;
-        fill_slot = fill_slot + 1 == kDepth ? 0 : fill_slot + 1;
+
+        // Tile done: add the warps' partial sums in a fixed order.  The buffer alternates between
+        // tiles, so one barrier per tile is enough.
+        // accumulator fragment: c0,c1 = (row g, batch 2t, 2t+1); c2,c3 = (row g+8, same batches)
+        float* rbuf = red + parity * (kWarps * kRowsPerCta * kCols);
+#pragma unroll
+        for (int nt = 0; nt < kNTiles; ++nt) {
+            float* rw = rbuf + warp * kRowsPerCta * kCols;
+            rw[g * kCols + 8 * nt + 2 * t] = acc[nt][0][0] + acc[nt][1][0];
+            rw[g * kCols + 8 * nt + 2 * t + 1] = acc[nt][0][1] + acc[nt][1][1];
+            rw[(g + 8) * kCols + 8 * nt + 2 * t] = acc[nt][0][2] + acc[nt][1][2];
+            rw[(g + 8) * kCols + 8 * nt + 2 * t + 1] = acc[nt][0][3] + acc[nt][1][3];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[nt][0][i] = acc[nt][1][i] = 0.0f;
+        }
+        __syncthreads();
+        const uint32_t row0 = (uint32_t)c_tile * kRowsPerCta;
+        for (int idx = threadIdx.x; idx < kRowsPerCta * kCols; idx += kWarps * 32) {
+            const int r = idx % kRowsPerCta, b = idx / kRowsPerCta;
+            if (b >= a.m || row0 + r >= a.n) continue;
+            float sum = rbuf[r * kCols + b];
+#pragma unroll
+            for (int w = 1; w < kWarps; ++w) sum += rbuf[(w * kRowsPerCta + r) * kCols + b];
+            if (a.out_dtype == MIXFP4_F32) static_cast<float*>(a.y)[(int64_t)b * a.ldy + row0 + r] = sum;
+            else static_cast<__nv_bfloat16*>(a.y)[(int64_t)b * a.ldy + row0 + r] = __float2bfloat16_rn(sum);
+        }
+        parity ^= 1u;
     }
     cp_async_wait<0>();
-
-    // accumulator fragment: c0,c1 = (row g, batch 2t, 2t+1); c2,c3 = (row g+8, same batches)
-    constexpr int kCols = 8 * kNTiles;
-#pragma unroll
-    for (int nt = 0; nt < kNTiles; ++nt) {
-        float* rw = red + warp * kRowsPerCta * kCols;
-        rw[g * kCols + 8 * nt + 2 * t] = acc[nt][0];
-        rw[g * kCols + 8 * nt + 2 * t + 1] = acc[nt][1];
-        rw[(g + 8) * kCols + 8 * nt + 2 * t] = acc[nt][2];
-        rw[(g + 8) * kCols + 8 * nt + 2 * t + 1] = acc[nt][3];
-    }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < kRowsPerCta * kCols; idx += kWarps * 32) {
-        const int r = idx % kRowsPerCta, b = idx / kRowsPerCta;
-        if (b >= a.m || row0 + r >= a.n) continue;
-        float sum = red[r * kCols + b];
-#pragma unroll
-        for (int w = 1; w < kWarps; ++w) sum += red[(w * kRowsPerCta + r) * kCols + b];
-        if (a.out_dtype == MIXFP4_F32) static_cast<float*>(a.y)[(int64_t)b * a.ldy + row0 + r] = sum;
-        else static_cast<__nv_bfloat16*>(a.y)[(int64_t)b * a.ldy + row0 + r] = __float2bfloat16_rn(sum);
-    }
 }
 
-template <int kWarps, int kNTiles, bool kKL, int kU>
-int launch(const GemvArgs& a, int flags, cudaStream_t st) {
-    const int64_t ctas = (a.n + kRowsPerCta - 1) / kRowsPerCta;
-    const size_t smem = 4096 + (size_t)kWarps * kRowsPerCta * 8 * kNTiles * 4 +
-                        (size_t)kWarps * kDepth * kU * stage_bytes(a.m) + (kKL ? 0 : (size_t)kRowsPerCta * (a.kpad / 128));
+template <int kWarps, int kNTiles, bool kKL, int kU, int kDepth, bool kXRes>
+int launch(const GemvArgs& a, int flags, int ctas_per_sm, cudaStream_t st) {
+    const int64_t tiles = (a.n + kRowsPerCta - 1) / kRowsPerCta;
+    // kernel layout: persistent CTAs stream over several row tiles each; the canonical layout
+    // keeps per-CTA format bytes in shared memory, so one tile per CTA
+    int64_t ctas = tiles;
+    if (kKL && ctas > (int64_t)ctas_per_sm * 148) ctas = (int64_t)ctas_per_sm * 148;
+    const size_t smem = kLutBytes + 2 * (size_t)kWarps * kRowsPerCta * 8 * kNTiles * 4 +
+                        (size_t)kWarps * kDepth * kU * stage_bytes(a.m, kXRes) +
+                        (kKL ? 0 : (size_t)kRowsPerCta * (a.kpad / 128)) + 16 +
+                        (kXRes ? (size_t)a.m * xres_row_bytes(a.kpad) : 0);
     if (smem > 200 * 1024 || ctas > 0x7fffffffLL) return MIXFP4_E_SHAPE;
     static bool configured = false;          // one per instantiation
     if (!configured) {
-        MIXFP4_CUDA_CHECK(cudaFuncSetAttribute(gemv_kernel<kWarps, kNTiles, kKL, kU>,
+        MIXFP4_CUDA_CHECK(cudaFuncSetAttribute(gemv_kernel<kWarps, kNTiles, kKL, kU, kDepth, kXRes>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         configured = true;
     }
@@ -302,20 +380,26 @@ int launch(const GemvArgs& a, int flags, cudaStream_t st) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (flags & MIXFP4_FLAG_OVERLAP_PREVIOUS) ? 1 : 0;
-    MIXFP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemv_kernel<kWarps, kNTiles, kKL, kU>, a));
+    MIXFP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemv_kernel<kWarps, kNTiles, kKL, kU, kDepth, kXRes>, a));
     return MIXFP4_OK;
 }
 
 template <bool kKL>
 int dispatch(const GemvArgs& a, int flags, cudaStream_t st) {
-    const int64_t subs = a.kpad / kStepK;
-    int warps = 8, unroll = subs >= 32 ? 2 : 1;
-    if (8 * kDepth * 2 * (int64_t)stage_bytes(a.m) > 160 * 1024) unroll = 1;
-    if (const char* e = getenv("MIXFP4_GEMV_CFG")) sscanf(e, "%dx%d", &warps, &unroll);   // TEMP tuning knob
-    if (a.m > 8) return unroll == 2 ? launch<8, 2, kKL, 2>(a, flags, st) : launch<8, 2, kKL, 1>(a, flags, st);
-    if (warps == 16) return unroll == 2 ? launch<16, 1, kKL, 2>(a, flags, st) : launch<16, 1, kKL, 1>(a, flags, st);
-    if (warps == 4) return unroll == 2 ? launch<4, 1, kKL, 2>(a, flags, st) : launch<4, 1, kKL, 1>(a, flags, st);
-    return unroll == 2 ? launch<8, 1, kKL, 2>(a, flags, st) : launch<8, 1, kKL, 1>(a, flags, st);
+    // x stays resident in shared memory when it is small (decode at M = 1..4 for Llama shapes)
+    const bool xres = (int64_t)a.m * xres_row_bytes(a.kpad) <= 32 * 1024;
+    int cfgid = 0;
+    if (const char* e = getenv("MIXFP4_GEMV_CFG")) cfgid = atoi(e);   // TEMP tuning knob
+    if (a.m > 8) return launch<8, 2, kKL, 1, 3, false>(a, flags, 2, st);
+    if (!xres) return launch<8, 1, kKL, 1, 3, false>(a, flags, 2, st);
+    switch (cfgid) {
+        case 1: return launch<8, 1, kKL, 2, 3, true>(a, flags, 3, st);
+        case 2: return launch<16, 1, kKL, 1, 3, true>(a, flags, 2, st);
+        case 3: return launch<8, 1, kKL, 1, 4, true>(a, flags, 2, st);
+        case 4: return launch<8, 1, kKL, 2, 3, true>(a, flags, 2, st);
+        case 5: return launch<16, 1, kKL, 1, 4, true>(a, flags, 2, st);
+        default: return launch<8, 1, kKL, 1, 4, true>(a, flags, 3, st);
+    }
 }
 
 }  // namespace
