@@ -3,30 +3,29 @@
 // (project_quant/modeling.py:629 + nn.Linear.forward).  HBM-bound by design: the packed
 // weight (0.5703 B/element) is read exactly once, x stays in L1/L2.
 //
-// Work split.  A CTA owns 16 consecutive weight rows; its warps split K in interleaved
-// 128-element steps and their partial sums are added in a fixed order through shared
-// memory (deterministic).  Inside a warp a 16 x 128 step is laid over the
-// mma.sync.m16n8k16 A-fragment: lane (g, t) = (lane/4, lane%4) owns rows g and g+8 and
-// the 32 consecutive K elements starting at 32*t.  The k index of an MMA is only a
-// summation label, so the 16 k-slots of every MMA are filled with whatever 4 consecutive
-// elements each lane decodes next; the B fragment takes the same 4 elements of x (batch
-// row g).
+// Work split.  A row tile is 16 consecutive weight rows; the warps of a CTA split its K range
+// in interleaved 128-element steps and their partial sums are added in a fixed order through
+// shared memory (deterministic).  With the kernel layout the CTAs are persistent (two or three
+// per SM) and walk over row tiles blockIdx.x, blockIdx.x + gridDim.x, ...  Inside a warp a
+// 16 x 128 step is laid over the mma.sync.m16n8k16 A-fragment: lane (g, t) = (lane/4, lane%4)
+// owns rows g and g+8 and the 32 consecutive K elements starting at 32*t.  The k index of an
+// MMA is only a summation label, so the 16 k-slots of every MMA are filled with whatever 4
+// consecutive elements each lane decodes next; the B fragment takes the same 4 elements of x
+// (batch row g).  Two accumulator sets alternate to shorten the MMA dependency chain.
 //
-// Data movement.  Every warp runs its own ring of cp.async stages: per step a lane
-// copies its 2 x 16 B of codes, (two lanes of each quad) the 8 scale bytes of a row, and
-// its 64 B of x, a few steps ahead of the arithmetic, so neither the HBM latency of the
-// weights nor the L2 latency of x is exposed.  With MIXFP4_FLAG_OVERLAP_PREVIOUS the kernel
-// is launched as a programmatic dependent: weight copies start while the previous kernel
-// drains, x is touched only after griddepcontrol.wait.
+// Data movement.  Every warp runs its own ring of cp.async stages: per step a lane copies its
+// 2 x 16 B of codes and (two lanes of each quad) the 8 scale bytes of a row, a few steps ahead
+// of the arithmetic and across tile boundaries, so the weight stream never drains.  x is
+// copied into shared memory once per CTA when M*K is small (decode), else staged per step like
+// the weights.  With MIXFP4_FLAG_OVERLAP_PREVIOUS the kernel is launched as a programmatic
+// dependent: weight copies start while the previous kernel drains, x is touched only after
+// griddepcontrol.wait.
 //
 // Decode.  A 256-entry table (from mixfp4_decode_table, or built here) maps
 // (format bit, E4M3 scale byte) to the block's eight magnitudes
 // bf16((level * scale) * global) -- exactly the reference's dequantized weight.  Eight
 // 4-bit codes (one 32-bit word) become four bf16x2 registers with byte permutes
 // (decode.cuh).  The accumulation is the tensor core's fp32.
-
-#include <stdio.h>
-#include <stdlib.h>
 
 #include "common.cuh"
 #include "decode.cuh"
@@ -388,18 +387,12 @@ template <bool kKL>
 int dispatch(const GemvArgs& a, int flags, cudaStream_t st) {
     // x stays resident in shared memory when it is small (decode at M = 1..4 for Llama shapes)
     const bool xres = (int64_t)a.m * xres_row_bytes(a.kpad) <= 32 * 1024;
-    int cfgid = 0;
-    if (const char* e = getenv("MIXFP4_GEMV_CFG")) cfgid = atoi(e);   // TEMP tuning knob
+    const int64_t tiles = (a.n + kRowsPerCta - 1) / kRowsPerCta;
     if (a.m > 8) return launch<8, 2, kKL, 1, 3, false>(a, flags, 2, st);
     if (!xres) return launch<8, 1, kKL, 1, 3, false>(a, flags, 2, st);
-    switch (cfgid) {
-        case 1: return launch<8, 1, kKL, 2, 3, true>(a, flags, 3, st);
-        case 2: return launch<16, 1, kKL, 1, 3, true>(a, flags, 2, st);
-        case 3: return launch<8, 1, kKL, 1, 4, true>(a, flags, 2, st);
-        case 4: return launch<8, 1, kKL, 2, 3, true>(a, flags, 2, st);
-        case 5: return launch<16, 1, kKL, 1, 4, true>(a, flags, 2, st);
-        default: return launch<8, 1, kKL, 1, 4, true>(a, flags, 3, st);
-    }
+    // few row tiles: more warps per tile keep the SMs busy; many: three 8-warp CTAs per SM
+    if (tiles < 2 * 148) return launch<16, 1, kKL, 1, 3, true>(a, flags, 2, st);
+    return launch<8, 1, kKL, 1, 4, true>(a, flags, 3, st);
 }
 
 }  // namespace
