@@ -276,9 +276,15 @@ def run_ours(args):
             "cpu_baseline": cpu_baseline(m, budget_s=12.0) if world == 1 and not args.no_cpu else None,
             "extra": extra,
         }
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # Leave without tearing NCCL down: destroying a process group while a CUDA graph that
+        # captured its collectives is alive can block forever.  All ranks are past their last
+        # collective (the MAX all-reduce above), so a hard exit is safe.
+        torch.cuda.synchronize(dev)
+        dist.barrier()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 def secondary_numbers(dev) -> dict:

@@ -518,10 +518,6 @@ extern "C" int mixfp4_gemm(const void* x, int64_t m, int64_t ldx, const uint8_t*
             if (t < best) { best = t; mt = mts[i]; bn = bns[i]; }
         }
     }
-    if (const char* e = getenv("MIXFP4_GEMM_TILE")) {   // TEMP tuning knob: "<mt>x<bn>"
-        int emt = 0, ebn = 0;
-        if (sscanf(e, "%dx%d", &emt, &ebn) == 2 && (emt == 1 || emt == 2) && (ebn == 128 || ebn == 256)) { mt = emt; bn = ebn; }
-    }
     const bool kl = layout == MIXFP4_LAYOUT_KERNEL;
     if (mt == 1 && bn == 128) return kl ? launch_gemm<1, 128, true>(xa, lda, a, st) : launch_gemm<1, 128, false>(xa, lda, a, st);
     if (mt == 1 && bn == 256) return kl ? launch_gemm<1, 256, true>(xa, lda, a, st) : launch_gemm<1, 256, false>(xa, lda, a, st);

@@ -37,7 +37,7 @@ constexpr int kRowsPerCta = 16;
 constexpr int kStepK = 128;               // K elements one warp consumes per step
 // The decode table is kept kLutRep times in shared memory, lane t of a quad reading copy t: lanes
 // of a quad then never collide on a bank, which removes most conflicts of the random lookups.
-constexpr int kLutRep = 4;
+constexpr int kLutRep = 1;
 constexpr int kLutBytes = 4096 * kLutRep;
 
 struct GemvArgs {
@@ -99,8 +99,8 @@ __host__ __device__ inline uint32_t stage_bytes(int64_t m, bool x_resident) {
 // staggers the banks of different batch rows).
 __host__ __device__ inline uint32_t xres_row_bytes(int64_t kpad) { return (uint32_t)kpad * 2u + 16u; }
 
-template <int kWarps, int kNTiles, bool kKL, int kU, int kDepth, bool kXRes>
-__global__ void __launch_bounds__(kWarps * 32, kWarps == 16 ? 2 : 3) gemv_kernel(const GemvArgs a) {
+template <int kWarps, int kNTiles, bool kKL, int kU, int kDepth, bool kXRes, int kMinCtas>
+__global__ void __launch_bounds__(kWarps * 32, kMinCtas) gemv_kernel(const GemvArgs a) {
     extern __shared__ __align__(16) uint8_t smem[];
     // lut kLutBytes | red 2*kWarps*16*8*kNTiles*4 | rings kWarps*kDepth*kU*stage | (canonical) fmt bytes 16*ld_fmt
     constexpr int kCols = 8 * kNTiles;
@@ -351,8 +351,9 @@ __global__ void __launch_bounds__(kWarps * 32, kWarps == 16 ? 2 : 3) gemv_kernel
     cp_async_wait<0>();
 }
 
-template <int kWarps, int kNTiles, bool kKL, int kU, int kDepth, bool kXRes>
-int launch(const GemvArgs& a, int flags, int ctas_per_sm, cudaStream_t st) {
+template <int kWarps, int kNTiles, bool kKL, int kU, int kDepth, bool kXRes, int kMinCtas>
+int launch(const GemvArgs& a, int flags, cudaStream_t st) {
+    constexpr int ctas_per_sm = kMinCtas;
     const int64_t tiles = (a.n + kRowsPerCta - 1) / kRowsPerCta;
     // kernel layout: persistent CTAs stream over several row tiles each; the canonical layout
     // keeps per-CTA format bytes in shared memory, so one tile per CTA
@@ -365,7 +366,7 @@ int launch(const GemvArgs& a, int flags, int ctas_per_sm, cudaStream_t st) {
     if (smem > 200 * 1024 || ctas > 0x7fffffffLL) return MIXFP4_E_SHAPE;
     static bool configured = false;          // one per instantiation
     if (!configured) {
-        MIXFP4_CUDA_CHECK(cudaFuncSetAttribute(gemv_kernel<kWarps, kNTiles, kKL, kU, kDepth, kXRes>,
+        MIXFP4_CUDA_CHECK(cudaFuncSetAttribute(gemv_kernel<kWarps, kNTiles, kKL, kU, kDepth, kXRes, kMinCtas>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         configured = true;
     }
@@ -379,7 +380,7 @@ int launch(const GemvArgs& a, int flags, int ctas_per_sm, cudaStream_t st) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (flags & MIXFP4_FLAG_OVERLAP_PREVIOUS) ? 1 : 0;
-    MIXFP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemv_kernel<kWarps, kNTiles, kKL, kU, kDepth, kXRes>, a));
+    MIXFP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemv_kernel<kWarps, kNTiles, kKL, kU, kDepth, kXRes, kMinCtas>, a));
     return MIXFP4_OK;
 }
 
@@ -388,11 +389,11 @@ int dispatch(const GemvArgs& a, int flags, cudaStream_t st) {
     // x stays resident in shared memory when it is small (decode at M = 1..4 for Llama shapes)
     const bool xres = (int64_t)a.m * xres_row_bytes(a.kpad) <= 32 * 1024;
     const int64_t tiles = (a.n + kRowsPerCta - 1) / kRowsPerCta;
-    if (a.m > 8) return launch<8, 2, kKL, 1, 3, false>(a, flags, 2, st);
-    if (!xres) return launch<8, 1, kKL, 1, 3, false>(a, flags, 2, st);
+    if (a.m > 8) return launch<8, 2, kKL, 1, 3, false, 2>(a, flags, st);
+    if (!xres) return launch<8, 1, kKL, 1, 3, false, 2>(a, flags, st);
     // few row tiles: more warps per tile keep the SMs busy; many: three 8-warp CTAs per SM
-    if (tiles < 2 * 148) return launch<16, 1, kKL, 1, 3, true>(a, flags, 2, st);
-    return launch<8, 1, kKL, 1, 4, true>(a, flags, 3, st);
+    if (tiles < 2 * 148) return launch<16, 1, kKL, 1, 3, true, 2>(a, flags, st);
+    return launch<8, 1, kKL, 1, 4, true, 3>(a, flags, st);
 }
 
 }  // namespace
