@@ -107,6 +107,12 @@ MIXFP4_API int mixfp4_quantize(const void* x, int dtype, int64_t rows, int64_t k
                     float* e2_err, float* e0_err, float* e2_scale, float* e0_scale,
                     void* dequant, int64_t ld_dequant, void* stream);
 
+/* Diagnostic: the quantizer divides by block scales with a reciprocal-and-residual sequence
+ * instead of a full IEEE division.  This runs the exhaustive proof that the two agree (all 2^23
+ * dividend significands x the 8 significands an E4M3 scale or the constants 6 and 7 can have)
+ * and leaves the number of disagreements (expected 0) in *mismatches (device memory). */
+MIXFP4_API int mixfp4_selftest_division(unsigned long long* mismatches, void* stream);
+
 /* Packed -> dense weight in out_dtype (the tensor the reference stores back into
  * nn.Linear.weight, project_quant/modeling.py:629). */
 MIXFP4_API int mixfp4_dequant(const uint8_t* codes, const uint8_t* scales, const uint8_t* fmt,

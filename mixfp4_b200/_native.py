@@ -50,6 +50,8 @@ def _declare(h: ctypes.CDLL) -> None:
     h.mixfp4_amax.argtypes = [p, i32, i64, i64, i64, p, p]
     h.mixfp4_quantize.restype = i32
     h.mixfp4_quantize.argtypes = [p, i32, i64, i64, i64, i32, p, p, p, p, p, p, p, p, p, p, i64, p]
+    h.mixfp4_selftest_division.restype = i32
+    h.mixfp4_selftest_division.argtypes = [p, p]
     h.mixfp4_dequant.restype = i32
     h.mixfp4_dequant.argtypes = [p, p, p, p, i64, i64, i32, p, i32, i64, p]
     h.mixfp4_repack.restype = i32
@@ -73,7 +75,7 @@ def _declare(h: ctypes.CDLL) -> None:
 # every symbol include/mixfp4_b200.h declares
 EXPORTED = (
     "mixfp4_abi_version", "mixfp4_status_string", "mixfp4_last_cuda_error", "mixfp4_padded_k",
-    "mixfp4_amax", "mixfp4_quantize", "mixfp4_dequant", "mixfp4_repack", "mixfp4_decode_table", "mixfp4_fwht",
+    "mixfp4_amax", "mixfp4_quantize", "mixfp4_selftest_division", "mixfp4_dequant", "mixfp4_repack", "mixfp4_decode_table", "mixfp4_fwht",
     "mixfp4_gemv",
     "mixfp4_gemm_workspace_bytes", "mixfp4_gemm", "mixfp4_gemm_h128_static_max_bytes", "mixfp4_gemm_h128_static",
 )

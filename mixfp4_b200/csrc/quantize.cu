@@ -88,41 +88,69 @@ struct QuantArgs {
     int64_t ld_dequant;
 };
 
-// E2M1 rounding of |n| exactly as codebook.py:12-25 computes it.
-__device__ __forceinline__ float e2m1_round(float mag) {
-    // exponent floor(log2 mag) clamped at 0 -> scale by 2/2^e, add 0.5 (fp32 rounding of
-    // that sum is part of the contract), floor, scale back, saturate at 6
-    const float up = mag < 2.0f ? 2.0f : (mag < 4.0f ? 1.0f : 0.5f);
-    const float down = mag < 2.0f ? 0.5f : (mag < 4.0f ? 1.0f : 2.0f);
-    const float q = __fmul_rn(floorf(__fadd_rn(__fmul_rn(mag, up), 0.5f)), down);
-    return fminf(q, 6.0f);
+// a / b from a correctly rounded reciprocal r = RN(1/b): one multiply and two FMAs (the
+// classical residual correction).  It returns the IEEE quotient for every a whenever it does
+// so for every significand of a, because the three steps scale exactly with powers of two as
+// long as the residual (about 2^-24 |a|) stays a normal number.  The quantizer uses it only
+// where that has been checked: for the eight significands an E4M3 scale (and the constants 6
+// and 7) can have by mixfp4_selftest_division, for the tensor scale by a per-CTA check over
+// all significands of the 16-bit input type.  Quotients below 2^-102, where the residual
+// would be subnormal, can be off in the last bit; with a 16-bit input and a tensor scale
+// below 2^10 they are still nonzero with the right sign, and anything that small is clamped
+// away by the 2^-9 scale floor and rounds to code 0, so no output bit depends on it.
+__device__ __forceinline__ float div_rcp(float a, float b, float r) {
+    const float q = __fmul_rn(a, r);
+    const float rem = __fmaf_rn(-q, b, a);
+    return __fmaf_rn(rem, r, q);
+}
+template <bool kFast>
+__device__ __forceinline__ float div_exact(float a, float b, float r) {
+    if constexpr (kFast) return div_rcp(a, b, r);
+    else return __fdiv_rn(a, b);
 }
 
-__device__ __forceinline__ uint32_t e2m1_index(float q) {
-    return q >= 1.0f ? (__float_as_uint(q) >> 22) - 252u : static_cast<uint32_t>(q + q);
+// E2M1 rounding of |n| exactly as codebook.py:12-25 computes it: exponent floor(log2 |n|)
+// clamped at 0, floor(mantissa * 2 + 0.5), saturate at 6.  For |n| >= 1 that is round-half-up
+// to one mantissa bit, done on the bit pattern (the level index is then the float's exponent
+// and top mantissa bit: index = (bits >> 22) - 252); below 1 the grid is {0, 0.5, 1} with
+// thresholds 0.75 and -- because the reference adds 0.5 in fp32 -- the float just below 0.25.
+__device__ __forceinline__ void e2m1_quantize(float mag, float& q, uint32_t& idx) {
+    const uint32_t b = __float_as_uint(mag);
+    const uint32_t rb = (b + 0x00200000u) & 0xffc00000u;               // |n| >= 1
+    const uint32_t lo_idx = (b >= 0x3f400000u ? 1u : 0u) + (b >= 0x3e7fffffu ? 1u : 0u);   // |n| < 1
+    const bool big = b >= 0x3f800000u;
+    q = big ? fminf(__uint_as_float(rb), 6.0f) : 0.5f * static_cast<float>(lo_idx);
+    idx = big ? min((rb >> 22) - 252u, 7u) : lo_idx;
 }
 
-// E0M3 rounding of |n|: round-half-even then saturate at 7 (codebook.py:41-43).
-__device__ __forceinline__ float e0m3_round(float mag) { return fminf(rintf(mag), 7.0f); }
+// E0M3 rounding of |n|: round-half-even then saturate at 7 (codebook.py:41-43); |n| < 2^22.
+__device__ __forceinline__ void e0m3_quantize(float mag, float& q, uint32_t& idx) {
+    const float t = __fadd_rn(mag, 8388608.0f);           // the sum's low mantissa bits are RNE(mag)
+    q = fminf(__fsub_rn(t, 8388608.0f), 7.0f);
+    idx = min(__float_as_uint(t) & 0x3fffffu, 7u);
+}
 
-template <bool kE0>
+template <bool kE0, bool kFast>
 __device__ __forceinline__ void candidate(const float (&ax)[kGroup], const float (&s)[kGroup], float amax_s,
                                           float gs, uint32_t& lo, uint32_t& hi, uint32_t& scale_byte,
                                           float& scale_val, float& err, float (&dmag)[kGroup]) {
-    float ideal = __fdiv_rn(amax_s, kE0 ? 7.0f : 6.0f);
+    float ideal = div_exact<kFast>(amax_s, kE0 ? 7.0f : 6.0f, kE0 ? (1.0f / 7.0f) : (1.0f / 6.0f));
     ideal = fminf(fmaxf(ideal, 0.001953125f), 448.0f);
     scale_byte = __nv_cvt_float_to_fp8(ideal, __NV_SATFINITE, __NV_E4M3);
     const float sc = e4m3_to_float(scale_byte);
+    const float rsc = __frcp_rn(sc);
     scale_val = sc;
     float sq[kGroup];
     lo = 0;
     hi = 0;
 #pragma unroll
     for (int i = 0; i < kGroup; ++i) {
-        const float n = __fdiv_rn(s[i], sc);
+        const float n = div_exact<kFast>(s[i], sc, rsc);
         const float mag = fabsf(n);
-        const float q = kE0 ? e0m3_round(mag) : e2m1_round(mag);
-        const uint32_t idx = kE0 ? static_cast<uint32_t>(q) : e2m1_index(q);
+        float q;
+        uint32_t idx;
+        if constexpr (kE0) e0m3_quantize(mag, q, idx);
+        else e2m1_quantize(mag, q, idx);
         const uint32_t nib = idx | (n < 0.0f ? 8u : 0u);
         if (i < 8) lo |= nib << (4 * i);
         else hi |= nib << (4 * (i - 8));
@@ -138,19 +166,49 @@ __device__ __forceinline__ void candidate(const float (&ax)[kGroup], const float
     err = acc;
 }
 
+// Exhaustive check of div_rcp against IEEE division: all 2^23 significands of the dividend
+// for each of the 8 significands a divisor can have (E4M3 scales; 6 = 1.5 * 4, 7 = 1.75 * 4).
+__global__ void selftest_division_kernel(unsigned long long* mismatches) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;          // 2^23 dividends
+    const float a = __uint_as_float(0x3f800000u | i);
+    unsigned long long bad = 0;
+#pragma unroll
+    for (int d = 0; d < 8; ++d) {
+        const float b = 1.0f + 0.125f * d;
+        const float r = __frcp_rn(b);
+        bad += __float_as_uint(div_rcp(a, b, r)) != __float_as_uint(__fdiv_rn(a, b));
+        bad += __float_as_uint(div_rcp(a * 0.001f, b * 6.0f, __frcp_rn(b * 6.0f))) != __float_as_uint(__fdiv_rn(a * 0.001f, b * 6.0f));
+    }
+    if (bad) atomicAdd(mismatches, bad);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads) quantize_kernel(const QuantArgs a) {
     const int lane = threadIdx.x & 31;
     const int64_t warp = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
     const int64_t row = warp / a.chunks;
+    const float amax = *a.amax;
+    const float gs = amax > 0.0f ? __fdiv_rn(amax, 2688.0f) : 1.0f;
+    const float rgs = __frcp_rn(gs);
+    // The reciprocal form of x / gs is used only if it gives the IEEE quotient for every
+    // significand the 16-bit input type has (checked here by the whole CTA, 128 or 1024
+    // divisions); fp32 inputs and extreme tensor scales take the IEEE path.
+    bool fast = sizeof(T) == 2 && gs > 8.7e-19f && gs < 1024.0f;
+    {
+        constexpr int kSig = sizeof(T) == 2 ? (Elem<T>::kDtype == MIXFP4_BF16 ? 128 : 1024) : 0;
+        bool ok = true;
+        for (int i = threadIdx.x; i < kSig; i += kThreads) {
+            const float v = 1.0f + static_cast<float>(i) * (1.0f / kSig);
+            ok = ok && __float_as_uint(div_rcp(v, gs, rgs)) == __float_as_uint(__fdiv_rn(v, gs));
+        }
+        fast = __syncthreads_and(ok) && fast;
+    }
     if (row >= a.rows) return;                     // whole warp leaves together
     const int64_t chunk = warp - row * a.chunks;
     const int64_t blk = chunk * 32 + lane;         // block index inside the row
     const bool stored = blk < a.blocks_pad;
     const bool real = blk < a.groups;
 
-    const float amax = *a.amax;
-    const float gs = amax > 0.0f ? __fdiv_rn(amax, 2688.0f) : 1.0f;
     if (warp == 0 && lane == 0) *a.global_scale = gs;
 
     uint32_t lo = 0, hi = 0, scale_byte = 0x01;    // what an all-zero block quantizes to
@@ -175,18 +233,28 @@ __global__ void __launch_bounds__(kThreads) quantize_kernel(const QuantArgs a) {
 
         float s[kGroup], ax[kGroup];
         float amax_s = 0.0f;
-#pragma unroll
-        for (int i = 0; i < kGroup; ++i) {
-            s[i] = __fdiv_rn(x[i], gs);
-            ax[i] = fabsf(x[i]);
-            amax_s = fmaxf(amax_s, fabsf(s[i]));
-        }
-
         uint32_t lo2, hi2, b2, lo0, hi0, b0;
         float sc2, sc0, err2, err0;
         float d2[kGroup], d0[kGroup];
-        candidate<false>(ax, s, amax_s, gs, lo2, hi2, b2, sc2, err2, d2);
-        candidate<true>(ax, s, amax_s, gs, lo0, hi0, b0, sc0, err0, d0);
+        if (fast) {
+#pragma unroll
+            for (int i = 0; i < kGroup; ++i) {
+                s[i] = div_exact<true>(x[i], gs, rgs);
+                ax[i] = fabsf(x[i]);
+                amax_s = fmaxf(amax_s, fabsf(s[i]));
+            }
+            candidate<false, true>(ax, s, amax_s, gs, lo2, hi2, b2, sc2, err2, d2);
+            candidate<true, true>(ax, s, amax_s, gs, lo0, hi0, b0, sc0, err0, d0);
+        } else {
+#pragma unroll
+            for (int i = 0; i < kGroup; ++i) {
+                s[i] = __fdiv_rn(x[i], gs);
+                ax[i] = fabsf(x[i]);
+                amax_s = fmaxf(amax_s, fabsf(s[i]));
+            }
+            candidate<false, false>(ax, s, amax_s, gs, lo2, hi2, b2, sc2, err2, d2);
+            candidate<true, false>(ax, s, amax_s, gs, lo0, hi0, b0, sc0, err0, d0);
+        }
         use_e0 = a.mode == MIXFP4_MODE_ORACLE16 ? (err0 < err2) : (a.mode == MIXFP4_MODE_ALL_E0M3);
         lo = use_e0 ? lo0 : lo2;
         hi = use_e0 ? hi0 : hi2;
@@ -449,4 +517,12 @@ extern "C" int mixfp4_decode_table(const float* global_scale, void* lut, void* s
     if (!aligned(lut, 16)) return MIXFP4_E_ALIGN;
     decode_table_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(global_scale, static_cast<uint4*>(lut));
     return check_launch("decode_table_kernel");
+}
+
+extern "C" int mixfp4_selftest_division(unsigned long long* mismatches, void* stream) {
+    if (!mismatches) return MIXFP4_E_NULL;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    MIXFP4_CUDA_CHECK(cudaMemsetAsync(mismatches, 0, sizeof(unsigned long long), st));
+    selftest_division_kernel<<<(1u << 23) / 256, 256, 0, st>>>(mismatches);
+    return check_launch("selftest_division_kernel");
 }

@@ -157,3 +157,13 @@ def test_largest_8b_layer_against_oracle():
     err1 = (dq.float() - wd.float()).square().sum().item()
     err2 = (again.float() - wd.float()).square().sum().item()
     assert err2 <= err1 * 1.05       # re-quantizing a quantized tensor does not drift
+
+
+def test_reciprocal_division_is_ieee_exact():
+    """Exhaustive on-device proof behind the quantizer's fast division (see
+    mixfp4_selftest_division): zero disagreements with IEEE division."""
+    from mixfp4_b200 import _native as nat
+    out = torch.ones(1, dtype=torch.int64, device="cuda")
+    rc = nat.lib().mixfp4_selftest_division(out.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    assert int(out.item()) == 0
