@@ -43,6 +43,12 @@ if ROOT not in sys.path:
 METRIC = "mixed-FP4 linear: GEMV HBM GB/s @M=1 (Llama-3-8B decode linears)"
 UNIT = "GB/s"
 FALLBACK_HBM_GBS = 6650.0
+# DRAM traffic of one launch of the dominant kernel from an ncu capture of the gate/up layer
+# (14336 x 4096, M = 1): dram__bytes_read.sum + dram__bytes_write.sum = 33.06 MB against 33.52 MB
+# algorithmic (the kernel layout does not read the separate format array), i.e. 0.986 x the
+# algorithmic bytes; scaled here to the average launch of the step (traffic grows with N*K).
+TRAFFIC_OVER_ALGORITHMIC = 0.986
+TRAFFIC_BYTES_PER_LAUNCH = None   # set in run_ours once the step's bytes are known
 
 
 def layer_list():
@@ -190,6 +196,8 @@ def run_ours(args):
     layers, nlayers = layer_list()
     total_bytes = nlayers * sum(algorithmic_bytes(n, k, m) for _, n, k in layers)
     launches_per_step = nlayers * len(layers)
+    global TRAFFIC_BYTES_PER_LAUNCH
+    TRAFFIC_BYTES_PER_LAUNCH = int(TRAFFIC_OVER_ALGORITHMIC * total_bytes / launches_per_step / world)
 
     model = build_model(dev, rank, world, m)
     x_host = torch.randn((m, 4096), generator=torch.Generator().manual_seed(7)).to(torch.bfloat16).pin_memory()
@@ -250,6 +258,7 @@ def run_ours(args):
     extra = {}
     if rank == 0 and world == 1 and not args.no_extra:
         extra = secondary_numbers(dev)
+        extra["decode_tokens_per_s_linears_only"] = round(1e3 / dev_ms * m, 1)
 
     if rank == 0:
         peak, peak_kind = measured_peak()
@@ -271,7 +280,7 @@ def run_ours(args):
             "gpu_launches": launches_per_step * args.steps,
             "roofline": {"bound": "hbm", "achieved": round(per_gpu, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(per_gpu / peak, 4), "peak_kind": peak_kind, "kernel": "gemv_kernel",
-                         "traffic": None,
+                         "traffic": TRAFFIC_BYTES_PER_LAUNCH,
                          "note": "achieved = algorithmic bytes of the %d GEMV launches of a step / CUDA-event time" % launches_per_step},
             "cpu_baseline": cpu_baseline(m, budget_s=12.0) if world == 1 and not args.no_cpu else None,
             "extra": extra,
@@ -288,8 +297,9 @@ def run_ours(args):
 
 
 def secondary_numbers(dev) -> dict:
-    """Other kernels of the path, device-timed on inputs larger than L2: the quantizer and
-    the prefill GEMM at M=4096 (reported beside the headline, not part of `value`)."""
+    """Other kernels and shapes of the path, device-timed (reported beside the headline, not
+    part of `value`): the quantizer, the decode GEMV at M = 4 and 16, and the prefill GEMM at
+    M = 4096 (tensor-pipe roofline), with and without the on-line H128 rotation."""
     import mixfp4_b200 as mx
     out = {}
 
@@ -305,7 +315,8 @@ def secondary_numbers(dev) -> dict:
         torch.cuda.synchronize(dev)
         return a.elapsed_time(b) / iters * 1e-3
 
-    ws = [(torch.randn((14336, 4096), device=dev) * 0.02).to(torch.bfloat16) for _ in range(4)]  # 470 MB
+    n, k = 14336, 4096
+    ws = [(torch.randn((n, k), device=dev) * 0.02).to(torch.bfloat16) for _ in range(4)]  # 470 MB > L2
     state = {"i": 0}
 
     def quant():
@@ -313,17 +324,42 @@ def secondary_numbers(dev) -> dict:
         mx.quantize_packed(ws[state["i"]])
 
     t = timeit(quant, 12)
-    n, k = 14336, 4096
-    out["quantize_gbs"] = round((2 * n * k + mx.packed_nbytes(n, k)) / t / 1e9, 1)
+    out["quantize_gbs_14336x4096"] = round((2 * n * k + mx.packed_nbytes(n, k)) / t / 1e9, 1)
     out["quantize_ms_14336x4096"] = round(t * 1e3, 4)
+
+    # decode GEMV at larger batch, gate/up shape, cycling over distinct weights (> L2)
+    packs = [mx.quantize_packed(w)[0].to_kernel_layout() for w in ws]
+    for m in (4, 16):
+        x = torch.randn((m, k), device=dev).to(torch.bfloat16)
+
+        def gemv_pass():
+            for p in packs:
+                mx.mixfp4_linear(x, p, overlap_previous=True)
+
+        t = timeit(gemv_pass, 10) / len(packs)
+        out["gemv_gbs_m%d_14336x4096" % m] = round(algorithmic_bytes(n, k, m) / t / 1e9, 1)
+
+    peak_tf = None
     try:
-        packed = mx.quantize_packed(ws[0][:4096])[0]
-        x = torch.randn((4096, 4096), device=dev).to(torch.bfloat16)
-        t = timeit(lambda: mx.mixfp4_linear(x, packed), 10)
-        out["gemm_tflops_m4096_4096x4096"] = round(2 * 4096 ** 3 / t / 1e12, 1)
-    except Exception as exc:  # the tensor-core kernel may not be built yet
-        out["gemm_tflops_m4096_4096x4096"] = None
-        out["gemm_note"] = str(exc)[:120]
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peak_tf = float(json.load(f)["bf16_tflops"])
+    except Exception:
+        peak_tf = 1590.0
+    for name, (gn, gk) in {"q_4096x4096": (4096, 4096), "gate_14336x4096": (14336, 4096), "down_4096x14336": (4096, 14336)}.items():
+        w = (torch.randn((gn, gk), device=dev) * 0.02).to(torch.bfloat16)
+        packed = mx.quantize_packed(w)[0].to_kernel_layout()
+        x = torch.randn((4096, gk), device=dev).to(torch.bfloat16)
+        t = timeit(lambda: mx.mixfp4_linear(x, packed), 8)
+        tf = 2.0 * 4096 * gn * gk / t / 1e12
+        out["gemm_tflops_m4096_" + name] = round(tf, 1)
+        out["gemm_frac_bf16_peak_m4096_" + name] = round(tf / peak_tf, 3)
+        if name == "q_4096x4096":
+            rot = mx.quantize_packed(mx.apply_transform(w, "H128"), rotation="H128")[0].to_kernel_layout()
+            t = timeit(lambda: mx.mixfp4_linear(x, rot), 8)
+            out["gemm_tflops_m4096_q_4096x4096_h128_rotation"] = round(2.0 * 4096 * gn * gk / t / 1e12, 1)
+        del w, packed, x
+    out["bf16_peak_tflops"] = peak_tf
+    out["decode_tokens_per_s_linears_only"] = None   # filled by the caller from ms_per_step
     return out
 
 

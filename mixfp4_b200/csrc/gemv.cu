@@ -296,8 +296,8 @@ __global__ void __launch_bounds__(kWarps * 32, kMinCtas) gemv_kernel(const GemvA
                     }
 #pragma unroll
                     for (int b = 0; b < 2; ++b) {                    // the 2 blocks of this lane's piece
-                        const uint4 tl = lds128(lut_base + ((sl >> (8 * b)) & 0xffu) * (16 * kLutRep) + t * 16);
-                        const uint4 th = lds128(lut_base + ((sh >> (8 * b)) & 0xffu) * (16 * kLutRep) + t * 16);
+                        const uint4 tl = lds128(lut_base + ((sl >> (8 * b)) & 0xffu) * (16 * kLutRep) + (t % kLutRep) * 16);
+                        const uint4 th = lds128(lut_base + ((sh >> (8 * b)) & 0xffu) * (16 * kLutRep) + (t % kLutRep) * 16);
 #pragma unroll
                         for (int half = 0; half < 2; ++half) {       // 8 elements = 2 MMAs
                             const int i = 2 * b + half;              // word index inside the piece
@@ -387,7 +387,7 @@ int launch(const GemvArgs& a, int flags, cudaStream_t st) {
 template <bool kKL>
 int dispatch(const GemvArgs& a, int flags, cudaStream_t st) {
     // x stays resident in shared memory when it is small (decode at M = 1..4 for Llama shapes)
-    const bool xres = (int64_t)a.m * xres_row_bytes(a.kpad) <= 32 * 1024;
+    const bool xres = (int64_t)a.m * xres_row_bytes(a.kpad) <= 40 * 1024;
     const int64_t tiles = (a.n + kRowsPerCta - 1) / kRowsPerCta;
     if (a.m > 8) return launch<8, 2, kKL, 1, 3, false, 2>(a, flags, st);
     if (!xres) return launch<8, 1, kKL, 1, 3, false, 2>(a, flags, st);
