@@ -13,13 +13,17 @@
 //               stage and commits the stage's "empty" barrier; after the last K step it
 //               commits the accumulator barrier.
 //   warps 2-9   weight transcoders, then epilogue.  Each thread owns half a row of the
-//               128 x 64 weight tile: it loads 16 B of codes, 2 scale bytes and the format
-//               byte straight from global memory one K step ahead, decodes them with the
-//               shared (format, scale) -> bf16 table into exactly the reference's
-//               dequantized bf16 values and writes them into the K-major 128B-swizzled
-//               operand layout tcgen05 reads (conflict-free 16-byte stores), fences the
-//               async proxy and arrives on the stage's "full" barrier.  At the end the
-//               same warps read the accumulator with tcgen05.ld and store y.
+//               128 x 64 weight tile: it reads 16 B of codes from the shared-memory code
+//               ring one K step ahead, takes its scale bytes (8 B per row and two K steps)
+//               straight from global memory, decodes with the shared (format, scale) ->
+//               bf16 table into exactly the reference's dequantized bf16 values and writes
+//               them into the K-major 128B-swizzled operand layout tcgen05 reads
+//               (conflict-free 16-byte stores), fences the async proxy and arrives on the
+//               stage's "full" barrier.  At the end the same warps read the accumulator
+//               with tcgen05.ld and store y.
+//   warp 10     TMA producer of the packed codes: a box of 32 bytes x tile rows per K step
+//               into its own ring (a per-thread global load of a row's 32 bytes touches 32
+//               lines per warp and made the load/store pipe the limiter).
 // Every mbarrier wait is bounded (wall-clock limit); on expiry the kernel records a code
 // in the caller's status word, stops issuing work, waits for its own TMA loads, frees
 // TMEM and returns.
@@ -41,7 +45,7 @@ namespace {
 
 constexpr int BK = 64;                     // K elements per pipeline stage (one 128-byte swizzle row)
 constexpr int kDecodeWarps = 8;
-constexpr int kThreads = (2 + kDecodeWarps) * 32;
+constexpr int kThreads = (3 + kDecodeWarps) * 32;   // x producer, MMA issuer, transcoders, code producer
 constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s: far beyond any legitimate wait
 
 // Tile configuration: kMT sub-tiles of 128 rows of x (each its own TMEM accumulator, all
@@ -57,8 +61,12 @@ struct Cfg {
     static constexpr uint32_t kOffA = 0;
     static constexpr uint32_t kOffB = kStages * kABytes;
     static constexpr uint32_t kOffLut = kOffB + kStages * kBBytes;
-    static constexpr uint32_t kOffBar = kOffLut + 4096;         // full_a[S] full_b[S] empty[S] accum
-    static constexpr uint32_t kOffMisc = kOffBar + (3 * kStages + 1) * 8;   // tmem base, abort flag
+    // ring of packed code tiles (kBN rows x 32 bytes per K step), filled by TMA
+    static constexpr uint32_t kWBytes = BN * (BK / 2);
+    static constexpr int kWStages = 24576 / kWBytes;            // 3 (256 rows) or 6 (128 rows)
+    static constexpr uint32_t kOffW = kOffLut + 4096;
+    static constexpr uint32_t kOffBar = kOffW + kWStages * kWBytes;   // full_a[S] full_b[S] empty[S] accum full_w[WS] empty_w[WS]
+    static constexpr uint32_t kOffMisc = kOffBar + (3 * kStages + 1 + 2 * kWStages) * 8;   // tmem base, abort flag
     static constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;   // + alignment slack
     // tcgen05 instruction descriptor, kind::f16: D fp32 (bits 4-5 = 1), A and B bf16 (bits 7-9
     // and 10-12 = 1), both K-major (bits 15, 16 = 0), N >> 3 at bits 17-22, M >> 4 at bits 24-28.
@@ -206,9 +214,10 @@ __device__ __forceinline__ uint4 lds128_lut(uint32_t addr) {
 // ------------------------------------------------------------------------------ kernel
 template <int kMT, int kBN, bool kKL>
 __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
+                                                           const __grid_constant__ CUtensorMap tmap_w,
                                                            const GemmArgs a) {
     using C = Cfg<kMT, kBN>;
-    constexpr int kStages = C::kStages;
+    constexpr int kStages = C::kStages, kWStages = C::kWStages;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -222,6 +231,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     auto full_b = [&](int s) { return base + C::kOffBar + 8u * (kStages + s); };
     auto empty = [&](int s) { return base + C::kOffBar + 8u * (2 * kStages + s); };
     const uint32_t accum_bar = base + C::kOffBar + 8u * (3 * kStages);
+    auto full_w = [&](int s) { return base + C::kOffBar + 8u * (3 * kStages + 1 + s); };
+    auto empty_w = [&](int s) { return base + C::kOffBar + 8u * (3 * kStages + 1 + kWStages + s); };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + C::kOffMisc);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + C::kOffMisc + 4);
     const WaitCtx ctx{abort_flag, a.status};
@@ -233,12 +244,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
             mbar_init(empty(s), 1);
         }
         mbar_init(accum_bar, 1);
+        for (int s = 0; s < kWStages; ++s) {
+            mbar_init(full_w(s), 1);
+            mbar_init(empty_w(s), kDecodeWarps);
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_proxy();
     }
     if (warp == 1) tmem_alloc(base + C::kOffMisc, C::kTmemCols);
-    if (warp >= 2) {   // the (format, scale) -> magnitudes table: 256 entries, 256 transcoder threads
+    if (warp >= 2 && warp < 2 + kDecodeWarps) {   // the (format, scale) -> magnitudes table: 256 entries, 256 transcoder threads
         const int e = threadIdx.x - 64;
         reinterpret_cast<uint4*>(gen + C::kOffLut)[e] =
             a.lut ? __ldg(a.lut + e) : make_lut_entry(e & 127, e >> 7, *a.global_scale);
@@ -287,6 +302,21 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
             }
             if (ok) umma_commit(accum_bar);
         }
+    } else if (warp == 2 + kDecodeWarps) {
+        // ------------------------------------------------- TMA producer of the code tiles
+        if (lane == 0) {
+            int issued = 0;
+            for (int kt = 0; kt < num_kt; ++kt) {
+                const int s = kt % kWStages;
+                const uint32_t ph = (kt / kWStages) & 1;
+                if (!mbar_wait(empty_w(s), ph ^ 1, ctx, 7)) break;
+                mbar_arrive_expect_tx(full_w(s), C::kWBytes);
+                tma_load_2d(base + C::kOffW + s * C::kWBytes, &tmap_w, full_w(s), kt * (BK / 2), (int)n0);
+                issued = kt + 1;
+            }
+            for (int kt = max(0, issued - kWStages); kt < issued; ++kt)
+                if (!mbar_wait(full_w(kt % kWStages), (kt / kWStages) & 1, ctx, 8)) break;
+        }
     } else {
         // -------------------------------------------------- weight transcoders / epilogue
         constexpr int kWords = C::kWords, kBlocks = kWords / 2;
@@ -294,41 +324,55 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         const int row = dt % kBN, part = dt / kBN;      // tile row, which part of the K step
         const uint32_t last_row = (uint32_t)a.n - 1;
         const uint32_t grow = min(n0 + row, last_row);  // rows past N re-read the last row; never stored
-        const uint8_t* cptr = a.codes + (size_t)grow * (a.kpad / 2) + part * (kWords * 4);
-        const uint8_t* sptr = a.scales + (size_t)grow * (a.kpad / 16) + part * kBlocks;
+        const uint8_t* srow = a.scales + (size_t)grow * (a.kpad / 16);
         const uint8_t* fptr = kKL ? a.scales : a.fmt + (size_t)grow * (a.kpad / 128);   // unused for the kernel layout
         const uint32_t lut_base = base + C::kOffLut;
         // destination of this thread's 16-byte chunks: row r, logical chunk c -> c ^ (r & 7)
         const uint32_t row_off = (row >> 3) * 1024u + (row & 7) * 128u;
         const uint32_t sw = row & 7;
 
-        auto load_codes = [&](uint32_t (&w)[kWords], int kt) {
-#pragma unroll
-            for (int j = 0; j < kWords / 4; ++j) {
-                const uint4 v = __ldg(reinterpret_cast<const uint4*>(cptr + (size_t)kt * 32) + j);
-                w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+        // The code tile of a K step is in shared memory (32 bytes per row, rows past N zero-filled
+        // by TMA).  With one thread per row the two 16-byte halves are read in an order that
+        // depends on the row so that eight neighbouring lanes cover all 32 banks.
+        auto load_codes = [&](uint32_t (&w)[kWords], int kt) -> bool {
+            const int ws = kt % kWStages;
+            if (!__all_sync(0xffffffffu, mbar_wait(full_w(ws), (kt / kWStages) & 1, ctx, 9))) return false;
+            const uint32_t src = base + C::kOffW + ws * C::kWBytes + row * 32;
+            if constexpr (kWords == 8) {
+                const uint32_t c0 = (lane >> 2) & 1;
+                const uint4 va = lds128_lut(src + c0 * 16), vb = lds128_lut(src + (c0 ^ 1) * 16);
+                const uint4 lo = c0 ? vb : va, hi = c0 ? va : vb;
+                w[0] = lo.x; w[1] = lo.y; w[2] = lo.z; w[3] = lo.w;
+                w[4] = hi.x; w[5] = hi.y; w[6] = hi.z; w[7] = hi.w;
+            } else {
+                const uint4 v = lds128_lut(src + part * 16);
+                w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
             }
+            __syncwarp();                               // every lane has read: the stage may be refilled
+            if (lane == 0) mbar_arrive(empty_w(ws));
+            return true;
         };
-        auto load_scales = [&](int kt) -> uint32_t {
-            if constexpr (kBlocks == 2) return __ldg(reinterpret_cast<const unsigned short*>(sptr + (size_t)kt * 4));
-            else return __ldg(reinterpret_cast<const unsigned int*>(sptr + (size_t)kt * 4));
+        // Scales: 8 bytes of a row cover two K steps.
+        auto load_scale_pair = [&](int pair) -> uint2 {
+            return __ldg(reinterpret_cast<const uint2*>(srow) + pair);
         };
 
         uint32_t codes[kWords], ncodes[kWords];
-        load_codes(codes, 0);
-        uint32_t scs = load_scales(0);
+        bool ok = load_codes(codes, 0);
+        uint2 sc2 = load_scale_pair(0), nsc2 = sc2;
         uint32_t fb = kKL ? 0u : __ldg(fptr);
-        bool ok = true;
-        for (int kt = 0; kt < num_kt; ++kt) {
+        for (int kt = 0; kt < num_kt && ok; ++kt) {
             const int s = kt % kStages;
             const uint32_t ph = (kt / kStages) & 1;
-            uint32_t nscs = scs, nfb = fb;
+            uint32_t nfb = fb;
             if (kt + 1 < num_kt) {                      // next K step's packed data, one step ahead
-                load_codes(ncodes, kt + 1);
-                nscs = load_scales(kt + 1);
+                ok = load_codes(ncodes, kt + 1);
+                if (!ok) break;
+                if ((kt & 1) == 0 && kt + 2 < num_kt) nsc2 = load_scale_pair((kt >> 1) + 1);
                 if constexpr (!kKL) nfb = __ldg(fptr + ((kt + 1) >> 1));
             }
-            ok = mbar_wait(empty(s), ph ^ 1, ctx, 5);
+            const uint32_t scs = ((kt & 1) ? sc2.y : sc2.x) >> (8 * part * kBlocks);
+            ok = __all_sync(0xffffffffu, mbar_wait(empty(s), ph ^ 1, ctx, 5));   // warp-uniform: lanes stay together
             if (!ok) break;
             const uint32_t dst = base + C::kOffB + s * C::kBBytes + row_off;
             const uint32_t fbits = fb >> ((kt & 1) * 4 + part * kBlocks);     // this thread's blocks
@@ -351,7 +395,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
             if (lane == 0) mbar_arrive(full_b(s));
 #pragma unroll
             for (int i = 0; i < kWords; ++i) codes[i] = ncodes[i];
-            scs = nscs; fb = nfb;
+            if (kt & 1) sc2 = nsc2;
+            fb = nfb;
         }
 
         // epilogue: TMEM lane quarter = warp % 4 (hardware rule), column half by warp group
@@ -445,6 +490,15 @@ int launch_gemm(const void* xa, int64_t lda, const GemmArgs& a, cudaStream_t st)
                                estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cr != CUDA_SUCCESS) return record_error_text("cuTensorMapEncodeTiled failed");
+    // the packed codes as a byte matrix [n, kpad/2]; a box is one K step (32 bytes) of BN rows
+    CUtensorMap tmap_w;
+    const cuuint64_t wdims[2] = {(cuuint64_t)(a.kpad / 2), (cuuint64_t)a.n};
+    const cuuint64_t wstrides[1] = {(cuuint64_t)(a.kpad / 2)};
+    const cuuint32_t wbox[2] = {BK / 2, (cuuint32_t)C::BN};
+    const CUresult cw = encode(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(a.codes), wdims, wstrides,
+                               wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cw != CUDA_SUCCESS) return record_error_text("cuTensorMapEncodeTiled failed for the code matrix");
     static bool configured = false;          // one per instantiation
     if (!configured) {
         MIXFP4_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel<kMT, kBN, kKL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -453,7 +507,7 @@ int launch_gemm(const void* xa, int64_t lda, const GemmArgs& a, cudaStream_t st)
     }
     const dim3 grid((unsigned)((a.n + C::BN - 1) / C::BN), (unsigned)((a.m + C::BM - 1) / C::BM));
     if (grid.y > 65535) return MIXFP4_E_SHAPE;
-    gemm_kernel<kMT, kBN, kKL><<<grid, kThreads, C::kSmemBytes, st>>>(tmap, a);
+    gemm_kernel<kMT, kBN, kKL><<<grid, kThreads, C::kSmemBytes, st>>>(tmap, tmap_w, a);
     return check_launch("gemm_kernel");
 }
 
@@ -478,7 +532,7 @@ extern "C" int mixfp4_gemm(const void* x, int64_t m, int64_t ldx, const uint8_t*
     if (m > 0x7fffffffLL || n > 0x7fffffffLL || k > 0x7fffffffLL) return MIXFP4_E_SHAPE;
     if (out_dtype != MIXFP4_F32 && out_dtype != MIXFP4_BF16) return MIXFP4_E_DTYPE;
     if (rotation_block != 0 && rotation_block != 128) return MIXFP4_E_MODE;
-    if (!aligned(codes, 16) || !aligned(scales, 2) || (lut && !aligned(lut, 16))) return MIXFP4_E_ALIGN;
+    if (!aligned(codes, 16) || !aligned(scales, 8) || (lut && !aligned(lut, 16))) return MIXFP4_E_ALIGN;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 
     // The TMA descriptor needs a 16-byte aligned base and row pitch; the rotation needs a
