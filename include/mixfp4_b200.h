@@ -152,6 +152,25 @@ MIXFP4_API int mixfp4_gemv(const void* x, int64_t m, int64_t ldx,
                 const float* global_scale, int64_t n, int64_t k, int layout, const void* lut,
                 void* y, int out_dtype, int64_t ldy, int flags, void* stream);
 
+/* Several weights that take the same x in one launch (q/k/v, gate/up of a decoder layer; no
+ * single counterpart in the reference, which calls nn.Linear.forward once per projection,
+ * modeling.py:629): y_i[M,n_i] = x[M,K] * W_i[n_i,K]^T for i < count, 1 <= count <= 3,
+ * 1 <= M <= 8, all weights in MIXFP4_LAYOUT_KERNEL with the same K.  Saves the per-launch
+ * ramp of the small projections.  Returns MIXFP4_E_SHAPE when x (M * (2 * padded K + 16)
+ * bytes) or the tables do not fit in shared memory: call mixfp4_gemv per weight then. */
+typedef struct mixfp4_gemv_segment {
+    const uint8_t* codes;          /* kernel layout [n, kpad/2] */
+    const uint8_t* scales;         /* kernel layout [n, kpad/16] */
+    const float* global_scale;     /* device f32[1] */
+    const void* lut;               /* optional table from mixfp4_decode_table, else NULL */
+    void* y;                       /* [M, n] in out_dtype */
+    int64_t ldy;
+    int64_t n;
+} mixfp4_gemv_segment;
+MIXFP4_API int mixfp4_gemv_grouped(const void* x, int64_t m, int64_t ldx, int64_t k,
+                        const mixfp4_gemv_segment* segments, int count,
+                        int out_dtype, int flags, void* stream);
+
 /* Prefill-shape dequant-linear on the tcgen05 tensor cores (any M >= 1, meant for
  * M >= 128).  rotation_block: 0, or 128 to apply the block-Hadamard H128 to x on the
  * fly (the reference's forward-pre-hook, modeling.py:662-668) -- the rotated operand is

@@ -15,6 +15,7 @@ import torch
 from . import build as _build
 
 OK = 0
+E_SHAPE = -2
 BF16, F16, F32 = 0, 1, 2
 MODE_ORACLE16, MODE_ALL_E2M1, MODE_ALL_E0M3 = 0, 1, 2
 LAYOUT_CANONICAL, LAYOUT_KERNEL = 0, 1
@@ -34,6 +35,12 @@ class MixFP4Error(RuntimeError):
         if detail:
             text += ": " + detail
         super().__init__(text)
+
+
+class GemvSegment(ctypes.Structure):
+    """struct mixfp4_gemv_segment of include/mixfp4_b200.h."""
+    _fields_ = [("codes", ctypes.c_void_p), ("scales", ctypes.c_void_p), ("global_scale", ctypes.c_void_p),
+                ("lut", ctypes.c_void_p), ("y", ctypes.c_void_p), ("ldy", ctypes.c_int64), ("n", ctypes.c_int64)]
 
 
 def _declare(h: ctypes.CDLL) -> None:
@@ -62,6 +69,8 @@ def _declare(h: ctypes.CDLL) -> None:
     h.mixfp4_fwht.argtypes = [p, p, i32, i64, i64, i64, i64, i32, p, i32, p]
     h.mixfp4_gemv.restype = i32
     h.mixfp4_gemv.argtypes = [p, i64, i64, p, p, p, p, i64, i64, i32, p, p, i32, i64, i32, p]
+    h.mixfp4_gemv_grouped.restype = i32
+    h.mixfp4_gemv_grouped.argtypes = [p, i64, i64, i64, ctypes.POINTER(GemvSegment), i32, i32, i32, p]
     h.mixfp4_gemm_workspace_bytes.restype = i64
     h.mixfp4_gemm_workspace_bytes.argtypes = [i64, i64, i64]
     h.mixfp4_gemm.restype = i32
@@ -76,7 +85,7 @@ def _declare(h: ctypes.CDLL) -> None:
 EXPORTED = (
     "mixfp4_abi_version", "mixfp4_status_string", "mixfp4_last_cuda_error", "mixfp4_padded_k",
     "mixfp4_amax", "mixfp4_quantize", "mixfp4_selftest_division", "mixfp4_dequant", "mixfp4_repack", "mixfp4_decode_table", "mixfp4_fwht",
-    "mixfp4_gemv",
+    "mixfp4_gemv", "mixfp4_gemv_grouped",
     "mixfp4_gemm_workspace_bytes", "mixfp4_gemm", "mixfp4_gemm_h128_static_max_bytes", "mixfp4_gemm_h128_static",
 )
 

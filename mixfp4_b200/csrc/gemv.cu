@@ -81,6 +81,15 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
 }
+// Predicated load: lanes with pred == false keep the previous contents of v.
+__device__ __forceinline__ void lds128_if(uint4& v, uint32_t addr, bool pred) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "@p ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n\t}"
+        : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)
+        : "r"(addr), "r"((uint32_t)pred));
+}
 __device__ __forceinline__ uint32_t lds16(uint32_t addr) {
     uint16_t v;
     asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
@@ -384,6 +393,246 @@ int launch(const GemvArgs& a, int flags, cudaStream_t st) {
     return MIXFP4_OK;
 }
 
+// ------------------------------------------------------------------------------------------
+// One CTA per SM, several warp groups (kernel layout, x resident, M <= 8).
+//
+// The shared-memory data path, not the arithmetic, limits the kernel above: of about 100
+// shared-memory wavefronts per warp and 128-element step, 43 are the four random table
+// look-ups (lanes of a quarter-warp collide on banks) and 16 are x loads that lanes of
+// unused batch columns do not need.  Here the CTA owns the SM: one decode table holds every
+// entry eight times, copy j in bank group j (entry e, copy j at e*128 + j*16), and a lane
+// reads copy (lane & 7), so a quarter-warp never collides; x is loaded only by the lanes
+// whose MMA column is a real batch row.  kGroups groups of kGW warps each work on their own
+// row tile (tile = blockIdx.x + gridDim.x * (group + kGroups * i)), split K between the
+// group's warps as above and synchronise with a named barrier per group.
+// Up to kMaxSegments weights that share x (q/k/v, gate/up) run as one launch: their row tiles
+// are numbered through, every segment has its own table in shared memory.
+constexpr uint32_t kLut8Bytes = 256u * 16u * 8u;     // 32 KB
+constexpr int kMaxSegments = 3;
+
+struct GemvSegment {
+    const uint8_t* codes;
+    const uint8_t* scales;
+    const float* global_scale;
+    const uint4* lut;                      // optional prebuilt decode table
+    void* y;
+    int64_t ldy;
+    int n;
+    int tile_end;                          // first tile index after this segment's tiles
+};
+struct GemvSmArgs {
+    const __nv_bfloat16* x;
+    int64_t ldx, k, kpad;
+    int m, nseg, ntiles, out_dtype;
+    bool x_vec;
+    GemvSegment seg[kMaxSegments];
+};
+constexpr uint32_t kStageSm = 1024u + 128u;          // codes [row half][lane] 16 B, scales [row] 8 B
+
+__host__ __device__ inline uint32_t red_bytes_sm(int groups, int gw, int64_t m) {
+    return (uint32_t)(groups * 2 * gw * kRowsPerCta * (int)m * 4);
+}
+
+template <int kGroups, int kGW, int kDepth>
+__global__ void __launch_bounds__(kGroups * kGW * 32, 1) gemv_sm_kernel(const GemvSmArgs a) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    constexpr int kThreadsSm = kGroups * kGW * 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int grp = warp / kGW, gw = warp % kGW;
+    const int g = lane >> 2, t = lane & 3;
+    const int m = a.m;
+    const uint32_t xres_rs = xres_row_bytes(a.kpad);
+    const uint32_t x_bytes = ((uint32_t)m * xres_rs + 15u) & ~15u;
+    const uint32_t lut_base = (uint32_t)__cvta_generic_to_shared(smem);
+    const uint32_t x_base = lut_base + a.nseg * kLut8Bytes;
+    float* red = reinterpret_cast<float*>(smem + a.nseg * kLut8Bytes + x_bytes) + grp * (2 * kGW * kRowsPerCta * m);
+    const uint32_t ring = x_base + x_bytes + red_bytes_sm(kGroups, kGW, m) + warp * kDepth * kStageSm;
+
+    const uint32_t ld_codes = (uint32_t)(a.kpad >> 1), ld_scales = (uint32_t)(a.kpad >> 4);
+    const int subs = static_cast<int>(a.kpad / kStepK);
+    const int spw = (subs + kGW - 1) / kGW;                  // steps per warp and tile
+    const int ntiles = a.ntiles;
+    const int tile0 = blockIdx.x + gridDim.x * grp, tile_stride = gridDim.x * kGroups;
+    const uint32_t k_lim = (uint32_t)a.k;
+    const bool x_ok = g < m;                                 // this lane's MMA column is a batch row
+    const uint32_t xrow_off = (x_ok ? (uint32_t)g * xres_rs : 0u) + t * 64;
+    const uint32_t lut_lane = lut_base + (lane & 7) * 16;
+
+    int p_tile = tile0, p_j = 0;
+    const uint8_t* pc[2] = {a.seg[0].codes, a.seg[0].codes};
+    const uint8_t* ps = a.seg[0].scales;
+    auto set_rows = [&]() {     // rows past N re-read the last row; their sums are never stored
+        const int s = (p_tile >= a.seg[0].tile_end) + (p_tile >= a.seg[1].tile_end);
+        const int first = s == 0 ? 0 : s == 1 ? a.seg[0].tile_end : a.seg[1].tile_end;
+        const uint8_t* codes = s == 0 ? a.seg[0].codes : s == 1 ? a.seg[1].codes : a.seg[2].codes;
+        const uint8_t* scales = s == 0 ? a.seg[0].scales : s == 1 ? a.seg[1].scales : a.seg[2].scales;
+        const uint32_t last_row = (uint32_t)(s == 0 ? a.seg[0].n : s == 1 ? a.seg[1].n : a.seg[2].n) - 1;
+        const uint32_t row0 = (uint32_t)(p_tile - first) * kRowsPerCta;
+        const uint32_t r0 = min(row0 + g, last_row), r1 = min(row0 + g + 8, last_row);
+        pc[0] = codes + (size_t)r0 * ld_codes + t * 16;
+        pc[1] = codes + (size_t)r1 * ld_codes + t * 16;
+        ps = scales + (size_t)(t == 0 ? r0 : r1) * ld_scales;   // used by lanes t < 2
+    };
+    auto prefetch = [&](uint32_t slot_off) {
+        if (p_tile < ntiles) {
+            const int sub = gw + p_j * kGW;
+            if (sub < subs) {
+                const uint32_t base = ring + slot_off;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) cp_async16_stream(base + h * 512 + lane * 16, pc[h] + (size_t)sub * 64);
+                if (t < 2) cp_async8(base + 1024 + (g + 8 * t) * 8, ps + (size_t)sub * 8);
+            }
+        }
+        if (++p_j == spw) { p_j = 0; p_tile += tile_stride; if (p_tile < ntiles) set_rows(); }
+    };
+
+    // Prologue.  Weights first: they never depend on the previous kernel in the stream.
+    if (p_tile < ntiles) set_rows();
+#pragma unroll
+    for (int d = 0; d < kDepth - 1; ++d) { prefetch(d * kStageSm); cp_async_commit(); }
+#pragma unroll
+    for (int s = 0; s < kMaxSegments; ++s) {
+        if (s >= a.nseg) break;
+        const uint4* lut = a.seg[s].lut;
+        const float gs = lut ? 0.0f : *a.seg[s].global_scale;
+        for (int i = threadIdx.x; i < 256 * 8; i += kThreadsSm) {   // (entry, copy): 512 contiguous bytes per warp
+            const int e = i >> 3;
+            const uint4 v = lut ? __ldg(lut + e) : make_lut_entry(e & 127, e >> 7, gs);
+            sts128(lut_base + s * kLut8Bytes + i * 16, v);
+        }
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    {   // the whole x (m rows, zero-filled to kpad) once per CTA
+        const uint32_t chunks_per_row = (uint32_t)(a.kpad >> 3);
+        for (uint32_t i = threadIdx.x; i < (uint32_t)m * chunks_per_row; i += kThreadsSm) {
+            const uint32_t r = i / chunks_per_row, c = i - r * chunks_per_row;
+            const uint32_t dst = x_base + r * xres_rs + c * 16;
+            const __nv_bfloat16* src = a.x + (size_t)r * a.ldx + c * 8;
+            if (a.x_vec) {
+                const bool in = c * 8 < k_lim;
+                cp_async16(dst, in ? static_cast<const void*>(src) : static_cast<const void*>(a.x), in ? 16u : 0u);
+            } else {
+                uint32_t e[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) e[q] = c * 8 + q < k_lim ? __bfloat16_as_ushort(src[q]) : 0u;
+                sts128(dst, make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16)));
+            }
+        }
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+
+    float acc[2][4];                     // two independent accumulation chains
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[0][i] = acc[1][i] = 0.0f;
+
+    uint4 xv = make_uint4(0u, 0u, 0u, 0u);   // lanes of unused batch columns keep zeros (never stored)
+    uint32_t use_off = 0, fill_off = (kDepth - 1) * kStageSm, parity = 0;
+    for (int c_tile = tile0; c_tile < ntiles; c_tile += tile_stride) {
+        const int cs = (c_tile >= a.seg[0].tile_end) + (c_tile >= a.seg[1].tile_end);
+        const uint32_t lut_seg = lut_lane + cs * kLut8Bytes;
+        for (int c_j = 0; c_j < spw; ++c_j) {
+            __syncwarp();                // the slot written now was read in the previous iteration
+            prefetch(fill_off);
+            cp_async_commit();
+            cp_async_wait<kDepth - 1>();
+            __syncwarp();                // scale bytes come from another lane's copy
+            const int sub = gw + c_j * kGW;
+            if (sub < subs) {
+                const uint32_t base = ring + use_off;
+                const uint4 cl = lds128(base + lane * 16);
+                const uint4 ch = lds128(base + 512 + lane * 16);
+                const uint32_t sl = lds16(base + 1024 + g * 8 + t * 2);
+                const uint32_t sh = lds16(base + 1024 + (g + 8) * 8 + t * 2);
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {                    // the 2 blocks of this lane's piece
+                    const uint4 tl = lds128(lut_seg + ((sl >> (8 * b)) & 0xffu) * 128u);
+                    const uint4 th = lds128(lut_seg + ((sh >> (8 * b)) & 0xffu) * 128u);
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {       // 8 elements = 2 MMAs
+                        const int i = 2 * b + half;              // word index inside the piece
+                        uint32_t pl[4], ph[4];
+                        decode8_kl(i == 0 ? cl.x : i == 1 ? cl.y : i == 2 ? cl.z : cl.w, tl, pl);
+                        decode8_kl(i == 0 ? ch.x : i == 1 ? ch.y : i == 2 ? ch.z : ch.w, th, ph);
+                        lds128_if(xv, x_base + xrow_off + (uint32_t)sub * 256u + i * 16, x_ok);
+                        mma_bf16(acc[0], pl[0], ph[0], pl[1], ph[1], xv.x, xv.y);
+                        mma_bf16(acc[1], pl[2], ph[2], pl[3], ph[3], xv.z, xv.w);
+                    }
+                }
+            }
+            use_off = use_off + kStageSm == kDepth * kStageSm ? 0 : use_off + kStageSm;
+            fill_off = fill_off + kStageSm == kDepth * kStageSm ? 0 : fill_off + kStageSm;
+        }
+
+        // Tile done: the group's warps add their partial sums in a fixed order.  The buffer
+        // alternates between tiles, so one barrier per tile is enough.
+        // accumulator fragment: c0,c1 = (row g, batch 2t, 2t+1); c2,c3 = (row g+8, same batches)
+        float* rbuf = red + parity * (kGW * kRowsPerCta * m);
+        float* rw = rbuf + gw * kRowsPerCta * m;
+        if (2 * t < m) {
+            rw[g * m + 2 * t] = acc[0][0] + acc[1][0];
+            rw[(g + 8) * m + 2 * t] = acc[0][2] + acc[1][2];
+        }
+        if (2 * t + 1 < m) {
+            rw[g * m + 2 * t + 1] = acc[0][1] + acc[1][1];
+            rw[(g + 8) * m + 2 * t + 1] = acc[0][3] + acc[1][3];
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[0][i] = acc[1][i] = 0.0f;
+        asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "n"(kGW * 32) : "memory");
+        const int first = cs == 0 ? 0 : cs == 1 ? a.seg[0].tile_end : a.seg[1].tile_end;
+        const uint32_t row0 = (uint32_t)(c_tile - first) * kRowsPerCta;
+        const uint32_t n_seg = (uint32_t)(cs == 0 ? a.seg[0].n : cs == 1 ? a.seg[1].n : a.seg[2].n);
+        void* y_seg = cs == 0 ? a.seg[0].y : cs == 1 ? a.seg[1].y : a.seg[2].y;
+        const int64_t ldy = cs == 0 ? a.seg[0].ldy : cs == 1 ? a.seg[1].ldy : a.seg[2].ldy;
+        for (int idx = gw * 32 + lane; idx < kRowsPerCta * m; idx += kGW * 32) {
+            const int r = idx % kRowsPerCta, b = idx / kRowsPerCta;
+            if (row0 + r >= n_seg) continue;
+            float sum = rbuf[r * m + b];
+#pragma unroll
+            for (int w = 1; w < kGW; ++w) sum += rbuf[(w * kRowsPerCta + r) * m + b];
+            if (a.out_dtype == MIXFP4_F32) static_cast<float*>(y_seg)[(int64_t)b * ldy + row0 + r] = sum;
+            else static_cast<__nv_bfloat16*>(y_seg)[(int64_t)b * ldy + row0 + r] = __float2bfloat16_rn(sum);
+        }
+        parity ^= 1u;
+    }
+    cp_async_wait<0>();
+}
+
+template <int kGroups, int kGW, int kDepth>
+int launch_sm(const GemvSmArgs& a, int flags, cudaStream_t st) {
+    const int64_t ctas = a.ntiles < 148 ? a.ntiles : 148;
+    const size_t smem = (size_t)a.nseg * kLut8Bytes + (((size_t)a.m * xres_row_bytes(a.kpad) + 15) & ~(size_t)15) +
+                        red_bytes_sm(kGroups, kGW, a.m) + (size_t)kGroups * kGW * kDepth * kStageSm;
+    if (smem > 227 * 1024) return MIXFP4_E_SHAPE;
+    static bool configured = false;          // one per instantiation
+    if (!configured) {
+        MIXFP4_CUDA_CHECK(cudaFuncSetAttribute(gemv_sm_kernel<kGroups, kGW, kDepth>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)ctas);
+    cfg.blockDim = dim3(kGroups * kGW * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (flags & MIXFP4_FLAG_OVERLAP_PREVIOUS) ? 1 : 0;
+    MIXFP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemv_sm_kernel<kGroups, kGW, kDepth>, a));
+    return MIXFP4_OK;
+}
+
+// One CTA per SM: three groups of 8 warps when there are row tiles for all of them, else two
+// groups of 16 warps (more warps per tile keep the SM busy).
+int dispatch_sm(const GemvSmArgs& g, int flags, cudaStream_t st) {
+    return g.ntiles >= 2 * 148 ? launch_sm<3, 8, 4>(g, flags, st) : launch_sm<2, 16, 3>(g, flags, st);
+}
+
 template <bool kKL>
 int dispatch(const GemvArgs& a, int flags, cudaStream_t st) {
     // x stays resident in shared memory when it is small (decode at M = 1..4 for Llama shapes)
@@ -391,6 +640,15 @@ int dispatch(const GemvArgs& a, int flags, cudaStream_t st) {
     const int64_t tiles = (a.n + kRowsPerCta - 1) / kRowsPerCta;
     if (a.m > 8) return launch<8, 2, kKL, 1, 3, false, 2>(a, flags, st);
     if (!xres) return launch<8, 1, kKL, 1, 3, false, 2>(a, flags, st);
+    if constexpr (kKL) {
+        GemvSmArgs g = {};
+        g.x = a.x; g.ldx = a.ldx; g.k = a.k; g.kpad = a.kpad;
+        g.m = (int)a.m; g.nseg = 1; g.ntiles = (int)tiles; g.out_dtype = a.out_dtype; g.x_vec = a.x_vec;
+        g.seg[0] = GemvSegment{a.codes, a.scales, a.global_scale, a.lut, a.y, a.ldy, (int)a.n, (int)tiles};
+        g.seg[1] = g.seg[2] = GemvSegment{a.codes, a.scales, a.global_scale, a.lut, a.y, a.ldy, (int)a.n, 0x7fffffff};
+        const int rc = dispatch_sm(g, flags, st);
+        if (rc != MIXFP4_E_SHAPE) return rc;     // does not fit this SM's shared memory: kernels above
+    }
     // few row tiles: more warps per tile keep the SMs busy; many: three 8-warp CTAs per SM
     if (tiles < 2 * 148) return launch<16, 1, kKL, 1, 3, true, 2>(a, flags, st);
     return launch<8, 1, kKL, 1, 4, true, 3>(a, flags, st);
@@ -420,4 +678,35 @@ extern "C" int mixfp4_gemv(const void* x, int64_t m, int64_t ldx, const uint8_t*
     a.x_vec = aligned(x, 16) && (ldx % 8 == 0) && (k % 8 == 0);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return layout == MIXFP4_LAYOUT_KERNEL ? dispatch<true>(a, flags, st) : dispatch<false>(a, flags, st);
+}
+
+extern "C" int mixfp4_gemv_grouped(const void* x, int64_t m, int64_t ldx, int64_t k,
+                                   const mixfp4_gemv_segment* segments, int count, int out_dtype, int flags,
+                                   void* stream) {
+    if (!x || !segments) return MIXFP4_E_NULL;
+    if (count < 1 || count > kMaxSegments) return MIXFP4_E_SHAPE;
+    if (m < 1 || m > 8 || k <= 0 || ldx < k) return MIXFP4_E_SHAPE;
+    if (out_dtype != MIXFP4_F32 && out_dtype != MIXFP4_BF16) return MIXFP4_E_DTYPE;
+    if (!aligned(x, 2)) return MIXFP4_E_ALIGN;
+    GemvSmArgs g = {};
+    g.x = static_cast<const __nv_bfloat16*>(x);
+    g.ldx = ldx; g.k = k; g.kpad = padded_k(k);
+    g.m = (int)m; g.nseg = count; g.out_dtype = out_dtype;
+    g.x_vec = aligned(x, 16) && (ldx % 8 == 0) && (k % 8 == 0);
+    if ((int64_t)m * xres_row_bytes(g.kpad) > 40 * 1024) return MIXFP4_E_SHAPE;   // x must fit in shared memory
+    int64_t tiles = 0;
+    for (int s = 0; s < kMaxSegments; ++s) {
+        const mixfp4_gemv_segment& in = segments[s < count ? s : count - 1];
+        if (s < count) {
+            if (!in.codes || !in.scales || !in.global_scale || !in.y) return MIXFP4_E_NULL;
+            if (in.n <= 0 || in.ldy < in.n || in.n > 0x7fffffffLL - 16) return MIXFP4_E_SHAPE;
+            if (!aligned(in.codes, 16) || !aligned(in.scales, 8) || (in.lut && !aligned(in.lut, 16))) return MIXFP4_E_ALIGN;
+            tiles += (in.n + kRowsPerCta - 1) / kRowsPerCta;
+            if (tiles > 0x7ffffff0LL) return MIXFP4_E_SHAPE;
+        }
+        g.seg[s] = GemvSegment{in.codes, in.scales, in.global_scale, static_cast<const uint4*>(in.lut), in.y, in.ldy,
+                               (int)in.n, s < count ? (int)tiles : 0x7fffffff};
+    }
+    g.ntiles = (int)tiles;
+    return dispatch_sm(g, flags, static_cast<cudaStream_t>(stream));
 }

@@ -116,6 +116,45 @@ def mixfp4_linear(x: torch.Tensor, packed: PackedWeight, *, bias: torch.Tensor |
     return y.reshape(*lead, packed.n)
 
 
+def mixfp4_linear_grouped(x: torch.Tensor, packs: list[PackedWeight], *, out_dtype: torch.dtype | None = None,
+                          overlap_previous: bool = False) -> list[torch.Tensor]:
+    """[x @ W_i^T for W_i in packs] for weights that take the same x (q/k/v, gate/up).
+
+    Decode shapes (at most 8 rows of x), up to three kernel-layout weights without a folded
+    rotation: one launch (``mixfp4_gemv_grouped``).  Anything else: one ``mixfp4_linear`` per
+    weight, same results.
+    """
+    if not packs:
+        return []
+    k = packs[0].k
+    lead = x.shape[:-1]
+    m = x.numel() // max(1, x.shape[-1])
+    grouped = (1 <= m <= 8 and 1 <= len(packs) <= 3 and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] == k
+               and all(p.k == k and p.layout == "kernel" and p.rotation is None for p in packs))
+    if grouped:
+        out_dtype = x.dtype if out_dtype is None else out_dtype
+        if out_dtype not in (torch.float32, torch.bfloat16):
+            raise TypeError("out_dtype must be float32 or bfloat16")
+        x2 = x.reshape(-1, k)
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        ys = [torch.empty((m, p.n), dtype=out_dtype, device=x.device) for p in packs]
+        segs = (nat.GemvSegment * len(packs))()
+        for seg, p, y in zip(segs, packs, ys):
+            seg.codes, seg.scales, seg.global_scale = p.codes.data_ptr(), p.scales.data_ptr(), p.global_scale.data_ptr()
+            seg.lut, seg.y, seg.ldy, seg.n = nat.ptr(p.lut), y.data_ptr(), y.stride(0), p.n
+        with torch.cuda.device(x.device):
+            st = nat.lib().mixfp4_gemv_grouped(x2.data_ptr(), m, x2.stride(0), k, segs, len(packs),
+                                               nat.DTYPE_CODE[out_dtype],
+                                               nat.FLAG_OVERLAP_PREVIOUS if overlap_previous else 0,
+                                               nat.stream_ptr(x.device))
+        if st != nat.E_SHAPE:
+            nat.check("mixfp4_gemv_grouped", st)
+            return [y.reshape(*lead, p.n) for y, p in zip(ys, packs)]
+    return [mixfp4_linear(x, p, out_dtype=out_dtype, overlap_previous=overlap_previous and i == 0)
+            for i, p in enumerate(packs)]
+
+
 class MixFP4Linear(nn.Module):
     """nn.Linear whose weight lives in the packed mixed-FP4 layout."""
 

@@ -53,6 +53,15 @@ def test_c_abi_argument_validation_needs_no_gpu():
     assert h.mixfp4_gemv(one, 1, 64, one, one, one, one, 8, 64, 0, None, one, nat.F16, 8, 0, None) == -4
     assert h.mixfp4_gemv(one, 1, 64, one, one, None, one, 8, 64, 0, None, one, nat.F32, 8, 0, None) == -1   # canonical needs fmt
     assert h.mixfp4_gemv(one, 1, 64, one, one, None, one, 8, 64, 3, None, one, nat.F32, 8, 0, None) == -5   # unknown layout
+    seg = (nat.GemvSegment * 1)()
+    seg[0].codes = seg[0].scales = seg[0].global_scale = seg[0].y = 16
+    seg[0].ldy, seg[0].n = 8, 8
+    assert h.mixfp4_gemv_grouped(one, 1, 64, 64, seg, 0, nat.F32, 0, None) == -2     # count out of range
+    assert h.mixfp4_gemv_grouped(one, 9, 64, 64, seg, 1, nat.F32, 0, None) == -2     # more than 8 rows of x
+    assert h.mixfp4_gemv_grouped(one, 1, 64, 64, None, 1, nat.F32, 0, None) == -1
+    assert h.mixfp4_gemv_grouped(one, 1, 64, 64, seg, 1, nat.F16, 0, None) == -4
+    seg[0].ldy = 4
+    assert h.mixfp4_gemv_grouped(one, 1, 64, 64, seg, 1, nat.F32, 0, None) == -2     # ldy < n
     assert h.mixfp4_repack(one, one, None, 4, 64, 1, one, one, None, None) == -1
     assert h.mixfp4_decode_table(None, one, None) == -1
     assert h.mixfp4_status_string(-3).decode().startswith("pointer or stride")

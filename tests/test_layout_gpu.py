@@ -68,3 +68,41 @@ def test_overlapped_launch_chain_matches_plain_chain():
     plain = chain(False)
     for _ in range(5):
         assert torch.equal(chain(True), plain)
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 8])
+@pytest.mark.parametrize("n,k", [(50, 70), (33, 131), (16, 14336), (1000, 512), (4800, 256), (4736, 1024), (7000, 128)])
+def test_kernel_layout_gemv_matches_oracle(m, n, k):
+    # ragged row counts (last tile partly outside N), K tails, fewer tiles than SMs and more
+    # tiles than warp groups: both instances of the one-CTA-per-SM decode kernel
+    w = synth.student_t_weight(n, k, seed=3 * n + k)
+    x = synth.activations(m, k, seed=m)
+    packed = mx.quantize_packed(w.cuda())[0].to_kernel_layout()
+    ref = oracle.quantize(w.float().numpy())
+    ystar = oracle.linear(x.float().numpy(), oracle.bf16_bits_to_f32(oracle.dequant(ref, "bf16")))
+    for p in (packed, packed.with_decode_table()):
+        y = mx.mixfp4_linear(x.cuda(), p, out_dtype=torch.float32).cpu().numpy()
+        assert oracle.relative_l2(y, ystar) <= 1e-3
+
+
+@pytest.mark.parametrize("m", [1, 4, 8])
+@pytest.mark.parametrize("ns", [(1024, 256, 256), (4096, 1024), (40, 17, 1000), (5000,)])
+def test_grouped_launch_equals_separate_launches(m, ns):
+    k = 1024
+    x = synth.activations(m, k, seed=11).cuda()
+    packs = [mx.quantize_packed(synth.student_t_weight(n, k, seed=n).cuda())[0].to_kernel_layout().with_decode_table()
+             for n in ns]
+    for dt in (torch.float32, torch.bfloat16):
+        together = mx.mixfp4_linear_grouped(x, packs, out_dtype=dt)
+        for y, p in zip(together, packs):
+            assert y.shape == (m, p.n)
+            assert torch.equal(y, mx.mixfp4_linear(x, p, out_dtype=dt))
+
+
+def test_grouped_falls_back_for_prefill_and_canonical():
+    k = 512
+    x = synth.activations(40, k, seed=2).cuda()
+    packs = [mx.quantize_packed(synth.student_t_weight(n, k, seed=n).cuda())[0] for n in (64, 96)]
+    ys = mx.mixfp4_linear_grouped(x, packs, out_dtype=torch.float32)
+    for y, p in zip(ys, packs):
+        assert torch.equal(y, mx.mixfp4_linear(x, p, out_dtype=torch.float32))
