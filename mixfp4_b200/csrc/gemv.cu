@@ -495,7 +495,9 @@ __global__ void __launch_bounds__(kGroups * kGW * 32, 1) gemv_sm_kernel(const Ge
         if (s >= a.nseg) break;
         const uint4* lut = a.seg[s].lut;
         const float gs = lut ? 0.0f : *a.seg[s].global_scale;
-        for (int i = threadIdx.x; i < 256 * 8; i += kThreadsSm) {   // (entry, copy): 512 contiguous bytes per warp
+        // (entry, copy): a warp writes 512 contiguous bytes.  Plain loads: the eight lanes that
+        // want the same entry share one L1 access (cp.async copies of the table measured slower).
+        for (int i = threadIdx.x; i < 256 * 8; i += kThreadsSm) {
             const int e = i >> 3;
             const uint4 v = lut ? __ldg(lut + e) : make_lut_entry(e & 127, e >> 7, gs);
             sts128(lut_base + s * kLut8Bytes + i * 16, v);
