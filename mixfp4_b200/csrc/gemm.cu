@@ -12,8 +12,8 @@
 //               tcgen05.mma.cta_group::1.kind::f16 (128x128x16, bf16 x bf16 -> fp32) per
 //               stage and commits the stage's "empty" barrier; after the last K step it
 //               commits the accumulator barrier.
-//   warps 2-9   weight transcoders, then epilogue.  Each thread owns half a row of the
-//               128 x 64 weight tile: it reads 16 B of codes from the shared-memory code
+//   warps 2-17  weight transcoders, then epilogue.  Each thread owns a quarter of a row of the
+//               128 x 64 weight tile (half a row of a 256-row tile): it reads 8 or 16 B of codes from the shared-memory code
 //               ring one K step ahead, takes its scale bytes (8 B per row and two K steps)
 //               straight from global memory, decodes with the shared (format, scale) ->
 //               bf16 table into exactly the reference's dequantized bf16 values and writes
@@ -21,7 +21,7 @@
 //               (conflict-free 16-byte stores), fences the async proxy and arrives on the
 //               stage's "full" barrier.  At the end the same warps read the accumulator
 //               with tcgen05.ld and store y.
-//   warp 10     TMA producer of the packed codes: a box of 32 bytes x tile rows per K step
+//   warp 18     TMA producer of the packed codes: a box of 32 bytes x tile rows per K step
 //               into its own ring (a per-thread global load of a row's 32 bytes touches 32
 //               lines per warp and made the load/store pipe the limiter).
 // Every mbarrier wait is bounded (wall-clock limit); on expiry the kernel records a code
@@ -44,7 +44,7 @@ namespace mixfp4 {
 namespace {
 
 constexpr int BK = 64;                     // K elements per pipeline stage (one 128-byte swizzle row)
-constexpr int kDecodeWarps = 8;
+constexpr int kDecodeWarps = 16;           // two warps per scheduler were too few to hide the decode latency
 constexpr int kThreads = (3 + kDecodeWarps) * 32;   // x producer, MMA issuer, transcoders, code producer
 constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s: far beyond any legitimate wait
 
@@ -72,9 +72,9 @@ struct Cfg {
     // and 10-12 = 1), both K-major (bits 15, 16 = 0), N >> 3 at bits 17-22, M >> 4 at bits 24-28.
     static constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) |
                                            ((uint32_t)(128 >> 4) << 24);
-    // transcoders: 256 threads over kBN rows
-    static constexpr int kThreadsPerRow = 256 / kBN;            // 2 or 1
-    static constexpr int kWords = 8 / kThreadsPerRow;           // 32-bit code words per thread and K step
+    // transcoders: 512 threads over kBN rows
+    static constexpr int kThreadsPerRow = kDecodeWarps * 32 / kBN;   // 4 or 2
+    static constexpr int kWords = 8 / kThreadsPerRow;           // 32-bit code words per thread and K step: 2 or 4
 };
 
 struct GemmArgs {
@@ -253,7 +253,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         fence_async_proxy();
     }
     if (warp == 1) tmem_alloc(base + C::kOffMisc, C::kTmemCols);
-    if (warp >= 2 && warp < 2 + kDecodeWarps) {   // the (format, scale) -> magnitudes table: 256 entries, 256 transcoder threads
+    if (warp >= 2 && warp < 2 + 8) {   // the (format, scale) -> magnitudes table: 256 entries, one thread each
         const int e = threadIdx.x - 64;
         reinterpret_cast<uint4*>(gen + C::kOffLut)[e] =
             a.lut ? __ldg(a.lut + e) : make_lut_entry(e & 127, e >> 7, *a.global_scale);
@@ -320,8 +320,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     } else {
         // -------------------------------------------------- weight transcoders / epilogue
         constexpr int kWords = C::kWords, kBlocks = kWords / 2;
-        const int dt = threadIdx.x - 64;                // 0..255
-        const int row = dt % kBN, part = dt / kBN;      // tile row, which part of the K step
+        // The threads of a row are neighbouring lanes, so a warp reads whole 32-byte code rows
+        // (conflict-free) and its 16-byte stores into the swizzled tile never share a bank.
+        constexpr int kTPR = C::kThreadsPerRow;
+        const int dt = threadIdx.x - 64;                // 0..511
+        const int row = dt / kTPR, part = dt % kTPR;    // tile row, which part of the K step
         const uint32_t last_row = (uint32_t)a.n - 1;
         const uint32_t grow = min(n0 + row, last_row);  // rows past N re-read the last row; never stored
         const uint8_t* srow = a.scales + (size_t)grow * (a.kpad / 16);
@@ -332,21 +335,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         const uint32_t sw = row & 7;
 
         // The code tile of a K step is in shared memory (32 bytes per row, rows past N zero-filled
-        // by TMA).  With one thread per row the two 16-byte halves are read in an order that
-        // depends on the row so that eight neighbouring lanes cover all 32 banks.
+        // by TMA).
         auto load_codes = [&](uint32_t (&w)[kWords], int kt) -> bool {
             const int ws = kt % kWStages;
             if (!__all_sync(0xffffffffu, mbar_wait(full_w(ws), (kt / kWStages) & 1, ctx, 9))) return false;
-            const uint32_t src = base + C::kOffW + ws * C::kWBytes + row * 32;
-            if constexpr (kWords == 8) {
-                const uint32_t c0 = (lane >> 2) & 1;
-                const uint4 va = lds128_lut(src + c0 * 16), vb = lds128_lut(src + (c0 ^ 1) * 16);
-                const uint4 lo = c0 ? vb : va, hi = c0 ? va : vb;
-                w[0] = lo.x; w[1] = lo.y; w[2] = lo.z; w[3] = lo.w;
-                w[4] = hi.x; w[5] = hi.y; w[6] = hi.z; w[7] = hi.w;
-            } else {
-                const uint4 v = lds128_lut(src + part * 16);
+            const uint32_t src = base + C::kOffW + ws * C::kWBytes + row * 32 + part * (kWords * 4);
+            if constexpr (kWords == 4) {
+                const uint4 v = lds128_lut(src);
                 w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+            } else {
+                asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(w[0]), "=r"(w[1]) : "r"(src));
             }
             __syncwarp();                               // every lane has read: the stage may be refilled
             if (lane == 0) mbar_arrive(empty_w(ws));
@@ -399,16 +397,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
             fb = nfb;
         }
 
-        // epilogue: TMEM lane quarter = warp % 4 (hardware rule), column half by warp group
+        // epilogue: TMEM lane quarter = warp % 4 (hardware rule), column quarter by warp group
         if (ok && mbar_wait(accum_bar, 0, ctx, 6)) {
             tcgen05_fence_after();
-            const int q = warp & 3, ch = (warp - 2) >> 2;
-            constexpr int kChunks = kBN / 64;           // 32-column chunks per warp and sub-tile
+            const int q = warp & 3, ch = (warp - 2) >> 2;   // ch: which quarter of the tile's columns
+            constexpr int kChunks = kBN / 128;          // 32-column chunks per warp and sub-tile
 #pragma unroll 1
             for (int it = 0; it < kMT * kChunks; ++it) {
                 const int mt = it / kChunks, c = it % kChunks;
                 const int64_t mrow = (int64_t)m0 + mt * 128 + q * 32 + lane;
-                const int col0 = ch * (kBN / 2) + c * 32;
+                const int col0 = ch * (kBN / 4) + c * 32;
                 uint32_t r[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(mt * kBN + col0), r);
                 const int64_t ncol = (int64_t)n0 + col0;
