@@ -12,16 +12,16 @@
 //               tcgen05.mma.cta_group::1.kind::f16 (128x128x16, bf16 x bf16 -> fp32) per
 //               stage and commits the stage's "empty" barrier; after the last K step it
 //               commits the accumulator barrier.
-//   warps 2-17  weight transcoders, then epilogue.  Each thread owns a quarter of a row of the
-//               128 x 64 weight tile (half a row of a 256-row tile): it reads 8 or 16 B of codes from the shared-memory code
-//               ring one K step ahead, takes its scale bytes (8 B per row and two K steps)
+//   warps 2-9   weight transcoders, then epilogue.  Each thread owns half a row of the
+//               128 x 64 weight tile (a whole row of a 256-row tile): it reads 16 or 32 B of
+//               codes from the shared-memory code ring one K step ahead, takes its scale bytes (8 B per row and two K steps)
 //               straight from global memory, decodes with the shared (format, scale) ->
 //               bf16 table into exactly the reference's dequantized bf16 values and writes
 //               them into the K-major 128B-swizzled operand layout tcgen05 reads
 //               (conflict-free 16-byte stores), fences the async proxy and arrives on the
 //               stage's "full" barrier.  At the end the same warps read the accumulator
 //               with tcgen05.ld and store y.
-//   warp 18     TMA producer of the packed codes: a box of 32 bytes x tile rows per K step
+//   warp 10     TMA producer of the packed codes: a box of 32 bytes x tile rows per K step
 //               into its own ring (a per-thread global load of a row's 32 bytes touches 32
 //               lines per warp and made the load/store pipe the limiter).
 // Every mbarrier wait is bounded (wall-clock limit); on expiry the kernel records a code
@@ -30,6 +30,9 @@
 //
 // Tensor-pipe roofline: 2*M*N*K flops against the measured dense bf16 peak.  The weight
 // tile is transcoded once per CTA, i.e. N*K elements are decoded M/128 times over.
+//
+// Large problems run gemm_pair_kernel (further down): two CTAs of a cluster share each
+// decoded weight tile through tcgen05.mma.cta_group::2.
 
 #include <cuda.h>
 #include <stdio.h>
@@ -44,7 +47,7 @@ namespace mixfp4 {
 namespace {
 
 constexpr int BK = 64;                     // K elements per pipeline stage (one 128-byte swizzle row)
-constexpr int kDecodeWarps = 16;           // two warps per scheduler were too few to hide the decode latency
+constexpr int kDecodeWarps = 8;             // more transcoder warps were measured: no gain alone, a loss in CTA pairs           // two warps per scheduler were too few to hide the decode latency
 constexpr int kThreads = (3 + kDecodeWarps) * 32;   // x producer, MMA issuer, transcoders, code producer
 constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s: far beyond any legitimate wait
 
@@ -72,9 +75,9 @@ struct Cfg {
     // and 10-12 = 1), both K-major (bits 15, 16 = 0), N >> 3 at bits 17-22, M >> 4 at bits 24-28.
     static constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) |
                                            ((uint32_t)(128 >> 4) << 24);
-    // transcoders: 512 threads over kBN rows
-    static constexpr int kThreadsPerRow = kDecodeWarps * 32 / kBN;   // 4 or 2
-    static constexpr int kWords = 8 / kThreadsPerRow;           // 32-bit code words per thread and K step: 2 or 4
+    // transcoders: 256 threads over kBN rows
+    static constexpr int kThreadsPerRow = kDecodeWarps * 32 / kBN;   // 2 or 1
+    static constexpr int kWords = 8 / kThreadsPerRow;           // 32-bit code words per thread and K step: 4 or 8
 };
 
 struct GemmArgs {
@@ -211,6 +214,59 @@ __device__ __forceinline__ uint4 lds128_lut(uint32_t addr) {
     return v;
 }
 
+// Epilogue of one CTA: the transcoder warps read the accumulators from TMEM (lane quarter =
+// warp % 4, a hardware rule; columns split between the warp groups) and store y.
+template <int kMT, int kBN>
+__device__ __forceinline__ void store_accumulators(const GemmArgs& a, uint32_t tmem_base, uint32_t m0, uint32_t n0,
+                                                   int warp, int lane) {
+    tcgen05_fence_after();
+    constexpr int kColGroups = kDecodeWarps / 4;                 // warp groups that split the tile's columns
+    const int q = warp & 3, ch = (warp - 2) >> 2;
+    constexpr int kChunks = kBN / (32 * kColGroups);             // 32-column chunks per warp and sub-tile
+#pragma unroll 1
+    for (int it = 0; it < kMT * kChunks; ++it) {
+        const int mt = it / kChunks, c = it % kChunks;
+        const int64_t mrow = (int64_t)m0 + mt * 128 + q * 32 + lane;
+        const int col0 = ch * (kBN / kColGroups) + c * 32;
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(mt * kBN + col0), r);
+        const int64_t ncol = (int64_t)n0 + col0;
+        if (mrow < a.m && ncol < a.n) {
+            const bool full = ncol + 32 <= a.n;
+            if (a.out_dtype == MIXFP4_F32) {
+                float* out = static_cast<float*>(a.y) + mrow * a.ldy + ncol;
+                if (full && (a.ldy & 3) == 0 && (reinterpret_cast<uintptr_t>(a.y) & 15) == 0) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        reinterpret_cast<uint4*>(out)[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (ncol + j < a.n) out[j] = __uint_as_float(r[j]);
+                }
+            } else {
+                __nv_bfloat16* out = static_cast<__nv_bfloat16*>(a.y) + mrow * a.ldy + ncol;
+                uint32_t pk[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                    pk[j] = *reinterpret_cast<const uint32_t*>(&v);
+                }
+                if (full && (a.ldy & 7) == 0 && (reinterpret_cast<uintptr_t>(a.y) & 15) == 0) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        reinterpret_cast<uint4*>(out)[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (ncol + j < a.n)
+                            out[j] = __ushort_as_bfloat16((unsigned short)((pk[j >> 1] >> (16 * (j & 1))) & 0xffffu));
+                }
+            }
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------ kernel
 template <int kMT, int kBN, bool kKL>
 __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
@@ -323,7 +379,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         // The threads of a row are neighbouring lanes, so a warp reads whole 32-byte code rows
         // (conflict-free) and its 16-byte stores into the swizzled tile never share a bank.
         constexpr int kTPR = C::kThreadsPerRow;
-        const int dt = threadIdx.x - 64;                // 0..511
+        const int dt = threadIdx.x - 64;                // transcoder thread index
         const int row = dt / kTPR, part = dt % kTPR;    // tile row, which part of the K step
         const uint32_t last_row = (uint32_t)a.n - 1;
         const uint32_t grow = min(n0 + row, last_row);  // rows past N re-read the last row; never stored
@@ -340,7 +396,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
             const int ws = kt % kWStages;
             if (!__all_sync(0xffffffffu, mbar_wait(full_w(ws), (kt / kWStages) & 1, ctx, 9))) return false;
             const uint32_t src = base + C::kOffW + ws * C::kWBytes + row * 32 + part * (kWords * 4);
-            if constexpr (kWords == 4) {
+            if constexpr (kWords == 8) {   // one thread per row: read the halves in an order that spreads the banks
+                const uint32_t c0 = (lane >> 2) & 1;
+                const uint4 va = lds128_lut(src + c0 * 16), vb = lds128_lut(src + (c0 ^ 1) * 16);
+                const uint4 lo = c0 ? vb : va, hi = c0 ? va : vb;
+                w[0] = lo.x; w[1] = lo.y; w[2] = lo.z; w[3] = lo.w;
+                w[4] = hi.x; w[5] = hi.y; w[6] = hi.z; w[7] = hi.w;
+            } else if constexpr (kWords == 4) {
                 const uint4 v = lds128_lut(src);
                 w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
             } else {
@@ -397,54 +459,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
             fb = nfb;
         }
 
-        // epilogue: TMEM lane quarter = warp % 4 (hardware rule), column quarter by warp group
-        if (ok && mbar_wait(accum_bar, 0, ctx, 6)) {
-            tcgen05_fence_after();
-            const int q = warp & 3, ch = (warp - 2) >> 2;   // ch: which quarter of the tile's columns
-            constexpr int kChunks = kBN / 128;          // 32-column chunks per warp and sub-tile
-#pragma unroll 1
-            for (int it = 0; it < kMT * kChunks; ++it) {
-                const int mt = it / kChunks, c = it % kChunks;
-                const int64_t mrow = (int64_t)m0 + mt * 128 + q * 32 + lane;
-                const int col0 = ch * (kBN / 4) + c * 32;
-                uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(mt * kBN + col0), r);
-                const int64_t ncol = (int64_t)n0 + col0;
-                if (mrow < a.m && ncol < a.n) {
-                    const bool full = ncol + 32 <= a.n;
-                    if (a.out_dtype == MIXFP4_F32) {
-                        float* out = static_cast<float*>(a.y) + mrow * a.ldy + ncol;
-                        if (full && (a.ldy & 3) == 0 && (reinterpret_cast<uintptr_t>(a.y) & 15) == 0) {
-#pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                reinterpret_cast<uint4*>(out)[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (ncol + j < a.n) out[j] = __uint_as_float(r[j]);
-                        }
-                    } else {
-                        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(a.y) + mrow * a.ldy + ncol;
-                        uint32_t pk[16];
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
-                            pk[j] = *reinterpret_cast<const uint32_t*>(&v);
-                        }
-                        if (full && (a.ldy & 7) == 0 && (reinterpret_cast<uintptr_t>(a.y) & 15) == 0) {
-#pragma unroll
-                            for (int j = 0; j < 4; ++j)
-                                reinterpret_cast<uint4*>(out)[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (ncol + j < a.n)
-                                    out[j] = __ushort_as_bfloat16((unsigned short)((pk[j >> 1] >> (16 * (j & 1))) & 0xffffu));
-                        }
-                    }
-                }
-            }
-        }
+        if (ok && mbar_wait(accum_bar, 0, ctx, 6)) store_accumulators<kMT, kBN>(a, tmem_base, m0, n0, warp, lane);
     }
 
     tcgen05_fence_before();
@@ -452,6 +467,308 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     if (warp == 1) {
         tcgen05_fence_after();
         tmem_dealloc(tmem_base, C::kTmemCols);
+    }
+}
+
+// ------------------------------------------------------------------- CTA-pair kernel
+// The single-CTA kernel above is bound by the shared-memory data path: per K step the
+// transcoders store and the tensor core re-reads the whole decoded 256-row weight tile, once
+// per 128-row accumulator.  Here two CTAs of a cluster share one weight tile of 256 rows:
+// each decodes only its own 128 rows, and one tcgen05.mma.cta_group::2 (M = 256: 128 token
+// rows from each CTA, N = 256: 128 weight rows from each CTA's shared memory) feeds both
+// SMs' tensor cores, so each CTA stores half as much and the hardware reads every half once.
+// The even CTA of the pair (the leader) issues all MMAs; its "full" barriers collect the TMA
+// bytes and the transcoder arrivals of both CTAs, and its commits release the stages of both
+// CTAs (tcgen05.commit with a cluster multicast mask).  No TMA load is multicast.
+constexpr uint32_t kPeerMask = 0xFEFFFFFFu;          // clears the CTA-rank bit of a shared::cluster address
+
+template <int kMT>
+struct PairCfg {
+    static constexpr int BM = 128 * kMT;             // token rows per CTA
+    static constexpr int BN = 256, BNH = 128;        // weight rows per pair / per CTA
+    static constexpr uint32_t kABytes = BM * BK * 2, kBBytes = BNH * BK * 2;
+    static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+    static constexpr int kStages = (196608 / kStageBytes) < 6 ? (196608 / kStageBytes) : 6;
+    static constexpr uint32_t kTmemCols = kMT * BN;
+    static constexpr uint32_t kWBytes = BNH * (BK / 2);
+    static constexpr int kWStages = 4;
+    static constexpr uint32_t kOffA = 0;
+    static constexpr uint32_t kOffB = kStages * kABytes;
+    static constexpr uint32_t kOffLut = kOffB + kStages * kBBytes;
+    static constexpr uint32_t kOffW = kOffLut + 4096;
+    static constexpr uint32_t kOffBar = kOffW + kWStages * kWBytes;   // full_a[S] full_b[S] empty[S] accum full_w[WS] empty_w[WS]
+    static constexpr uint32_t kOffMisc = kOffBar + (3 * kStages + 1 + 2 * kWStages) * 8;
+    static constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;
+    // kind::f16 instruction descriptor as above with M = 256 (the pair), N = 256
+    static constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                                           ((uint32_t)(256 >> 4) << 24);
+    static constexpr int kThreadsPerRow = kDecodeWarps * 32 / BNH;   // 2
+    static constexpr int kWords = 8 / kThreadsPerRow;                // 4
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrive on the leader CTA's copy of a barrier (from either CTA of the pair).
+__device__ __forceinline__ void mbar_arrive_leader(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar & kPeerMask) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait with cluster-scope acquire (the barrier is also signalled by the peer CTA).
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int code) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    uint32_t spins = 0;
+    while (!mbar_try_wait_cluster(bar, parity)) {
+        if ((++spins & 63u) == 0) {
+            if (*ctx.abort_flag) return false;
+            if (global_timer_ns() - t0 > kWaitLimitNs) {
+                *ctx.abort_flag = 1;
+                if (ctx.status) atomicCAS(ctx.status, 0, code);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+// TMA load into this CTA's shared memory whose bytes are counted on the leader's barrier.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar & kPeerMask), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_pair_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrive on the barrier at this shared-memory offset in both CTAs once all MMAs issued so far are done.
+__device__ __forceinline__ void umma_pair_commit(uint32_t bar) {
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(mask) : "memory");
+}
+
+template <int kMT, bool kKL>
+__global__ void __launch_bounds__(kThreads, 1) gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_x,
+                                                                const __grid_constant__ CUtensorMap tmap_w,
+                                                                const GemmArgs a) {
+    using C = PairCfg<kMT>;
+    constexpr int kStages = C::kStages, kWStages = C::kWStages;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;      // same offset in both CTAs of the pair
+    uint8_t* gen = smem_raw + (base - raw);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();           // 0 = leader
+    const uint32_t m0 = blockIdx.x * C::BM;            // this CTA's token rows
+    const uint32_t n0 = blockIdx.y * C::BN;            // the pair's weight rows; this CTA decodes n0 + rank*128 ...
+    const uint32_t nh0 = n0 + rank * C::BNH;
+    const int num_kt = static_cast<int>(a.kpad / BK);
+
+    auto full_a = [&](int s) { return base + C::kOffBar + 8u * s; };
+    auto full_b = [&](int s) { return base + C::kOffBar + 8u * (kStages + s); };
+    auto empty = [&](int s) { return base + C::kOffBar + 8u * (2 * kStages + s); };
+    const uint32_t accum_bar = base + C::kOffBar + 8u * (3 * kStages);
+    auto full_w = [&](int s) { return base + C::kOffBar + 8u * (3 * kStages + 1 + s); };
+    auto empty_w = [&](int s) { return base + C::kOffBar + 8u * (3 * kStages + 1 + kWStages + s); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + C::kOffMisc);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + C::kOffMisc + 4);
+    const WaitCtx ctx{abort_flag, a.status};
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(full_a(s), 1);                    // leader: its own expect_tx arrival; bytes of both CTAs
+            mbar_init(full_b(s), 2 * kDecodeWarps);     // leader: the transcoder warps of both CTAs
+            mbar_init(empty(s), 1);                     // each CTA: the leader's commit
+        }
+        mbar_init(accum_bar, 1);
+        for (int s = 0; s < kWStages; ++s) {
+            mbar_init(full_w(s), 1);
+            mbar_init(empty_w(s), kDecodeWarps);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_proxy();
+    }
+    if (warp == 1) tmem_alloc_pair(base + C::kOffMisc, C::kTmemCols);   // the same warp in both CTAs
+    if (warp >= 2 && warp < 2 + 8) {
+        const int e = threadIdx.x - 64;
+        reinterpret_cast<uint4*>(gen + C::kOffLut)[e] =
+            a.lut ? __ldg(a.lut + e) : make_lut_entry(e & 127, e >> 7, *a.global_scale);
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync_all();          // the peer's barriers are initialised before anything signals them
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------- TMA producer of this CTA's x tile
+        if (lane == 0) {
+            int issued = 0;
+            for (int kt = 0; kt < num_kt; ++kt) {
+                const int s = kt % kStages;
+                const uint32_t ph = (kt / kStages) & 1;
+                if (!mbar_wait_cluster(empty(s), ph ^ 1, ctx, 1)) break;
+                if (rank == 0) mbar_arrive_expect_tx(full_a(s), 2 * C::kABytes);   // both CTAs' tiles
+                tma_load_2d_pair(base + C::kOffA + s * C::kABytes, &tmap_x, full_a(s), kt * BK, (int)m0);
+                issued = kt + 1;
+            }
+            // never leave with a bulk copy still writing into this CTA's shared memory: the stage's
+            // "empty" barrier completes only after the MMAs that read the landed tile
+            for (int kt = max(0, issued - kStages); kt < issued; ++kt)
+                if (!mbar_wait_cluster(empty(kt % kStages), (kt / kStages) & 1, ctx, 2)) break;
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------ MMA issuer (leader only)
+        if (rank == 0 && lane == 0) {
+            bool ok = true;
+            for (int kt = 0; kt < num_kt && ok; ++kt) {
+                const int s = kt % kStages;
+                const uint32_t ph = (kt / kStages) & 1;
+                ok = mbar_wait_cluster(full_a(s), ph, ctx, 3) && mbar_wait_cluster(full_b(s), ph, ctx, 4);
+                if (!ok) break;
+                tcgen05_fence_after();
+                const uint64_t db = make_smem_desc(base + C::kOffB + s * C::kBBytes);
+#pragma unroll
+                for (int mt = 0; mt < kMT; ++mt) {
+                    const uint64_t da = make_smem_desc(base + C::kOffA + s * C::kABytes + mt * 16384u);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        umma_pair_bf16(tmem_base + mt * C::BN, da + 2u * k, db + 2u * k, C::kInstrDesc,
+                                       (kt | k) != 0 ? 1u : 0u);
+                }
+                umma_pair_commit(empty(s));             // frees the stage in both CTAs
+            }
+            if (ok) umma_pair_commit(accum_bar);
+        }
+    } else if (warp == 2 + kDecodeWarps) {
+        // ------------------------------------------ TMA producer of this CTA's code tiles
+        if (lane == 0) {
+            int issued = 0;
+            for (int kt = 0; kt < num_kt; ++kt) {
+                const int s = kt % kWStages;
+                const uint32_t ph = (kt / kWStages) & 1;
+                if (!mbar_wait(empty_w(s), ph ^ 1, ctx, 7)) break;
+                mbar_arrive_expect_tx(full_w(s), C::kWBytes);
+                tma_load_2d(base + C::kOffW + s * C::kWBytes, &tmap_w, full_w(s), kt * (BK / 2), (int)nh0);
+                issued = kt + 1;
+            }
+            for (int kt = max(0, issued - kWStages); kt < issued; ++kt)
+                if (!mbar_wait(full_w(kt % kWStages), (kt / kWStages) & 1, ctx, 8)) break;
+        }
+    } else {
+        // -------------------------------------------------- weight transcoders / epilogue
+        constexpr int kWords = C::kWords, kBlocks = kWords / 2, kTPR = C::kThreadsPerRow;
+        const int dt = threadIdx.x - 64;                // transcoder thread index
+        const int row = dt / kTPR, part = dt % kTPR;    // row of this CTA's half tile, part of the K step
+        const uint32_t last_row = (uint32_t)a.n - 1;
+        const uint32_t grow = min(nh0 + row, last_row);
+        const uint8_t* srow = a.scales + (size_t)grow * (a.kpad / 16);
+        const uint8_t* fptr = kKL ? a.scales : a.fmt + (size_t)grow * (a.kpad / 128);
+        const uint32_t lut_base = base + C::kOffLut;
+        const uint32_t row_off = (row >> 3) * 1024u + (row & 7) * 128u;
+        const uint32_t sw = row & 7;
+
+        auto load_codes = [&](uint32_t (&w)[kWords], int kt) -> bool {
+            const int ws = kt % kWStages;
+            if (!__all_sync(0xffffffffu, mbar_wait(full_w(ws), (kt / kWStages) & 1, ctx, 9))) return false;
+            const uint32_t src = base + C::kOffW + ws * C::kWBytes + row * 32 + part * (kWords * 4);
+            if constexpr (kWords == 4) {
+                const uint4 v = lds128_lut(src);
+                w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+            } else {
+                asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(w[0]), "=r"(w[1]) : "r"(src));
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty_w(ws));
+            return true;
+        };
+        auto load_scale_pair = [&](int pair) -> uint2 { return __ldg(reinterpret_cast<const uint2*>(srow) + pair); };
+
+        uint32_t codes[kWords], ncodes[kWords];
+        bool ok = load_codes(codes, 0);
+        uint2 sc2 = load_scale_pair(0), nsc2 = sc2;
+        uint32_t fb = kKL ? 0u : __ldg(fptr);
+        for (int kt = 0; kt < num_kt && ok; ++kt) {
+            const int s = kt % kStages;
+            const uint32_t ph = (kt / kStages) & 1;
+            uint32_t nfb = fb;
+            if (kt + 1 < num_kt) {
+                ok = load_codes(ncodes, kt + 1);
+                if (!ok) break;
+                if ((kt & 1) == 0 && kt + 2 < num_kt) nsc2 = load_scale_pair((kt >> 1) + 1);
+                if constexpr (!kKL) nfb = __ldg(fptr + ((kt + 1) >> 1));
+            }
+            const uint32_t scs = ((kt & 1) ? sc2.y : sc2.x) >> (8 * part * kBlocks);
+            ok = __all_sync(0xffffffffu, mbar_wait_cluster(empty(s), ph ^ 1, ctx, 5));
+            if (!ok) break;
+            const uint32_t dst = base + C::kOffB + s * C::kBBytes + row_off;
+            const uint32_t fbits = fb >> ((kt & 1) * 4 + part * kBlocks);
+#pragma unroll
+            for (int b = 0; b < kBlocks; ++b) {
+                const uint32_t idx = kKL ? ((scs >> (8 * b)) & 0xffu)
+                                         : ((((fbits >> b) & 1u) << 7) | ((scs >> (8 * b)) & 0x7fu));
+                const uint4 tab = lds128_lut(lut_base + idx * 16);
+#pragma unroll
+                for (int w = 0; w < 2; ++w) {
+                    const int i = 2 * b + w;
+                    uint32_t p[4];
+                    decode_word<kKL>(codes[i], tab, p);
+                    const uint32_t chunk = (uint32_t)(part * kWords + i) ^ sw;
+                    sts128(dst + chunk * 16, p[0], p[1], p[2], p[3]);
+                }
+            }
+            fence_async_proxy();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_leader(full_b(s));   // this CTA's half is in place
+#pragma unroll
+            for (int i = 0; i < kWords; ++i) codes[i] = ncodes[i];
+            if (kt & 1) sc2 = nsc2;
+            fb = nfb;
+        }
+
+        if (ok && mbar_wait_cluster(accum_bar, 0, ctx, 6))
+            store_accumulators<kMT, C::BN>(a, tmem_base, m0, n0, warp, lane);
+    }
+
+    // Both CTAs stay until the pair is done: the leader's MMAs read the peer's shared memory and
+    // its commits signal the peer's barriers.
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc_pair(tmem_base, C::kTmemCols);
     }
 }
 
@@ -507,6 +824,51 @@ int launch_gemm(const void* xa, int64_t lda, const GemmArgs& a, cudaStream_t st)
     if (grid.y > 65535) return MIXFP4_E_SHAPE;
     gemm_kernel<kMT, kBN, kKL><<<grid, kThreads, C::kSmemBytes, st>>>(tmap, tmap_w, a);
     return check_launch("gemm_kernel");
+}
+
+template <int kMT, bool kKL>
+int launch_gemm_pair(const void* xa, int64_t lda, const GemmArgs& a, cudaStream_t st) {
+    using C = PairCfg<kMT>;
+    EncodeTiledFn encode = encode_tiled_fn();
+    if (!encode) return record_error_text("cuTensorMapEncodeTiled is not available from the driver");
+    CUtensorMap tmap, tmap_w;
+    const cuuint32_t estr[2] = {1, 1};
+    const cuuint64_t dims[2] = {(cuuint64_t)a.k, (cuuint64_t)a.m};
+    const cuuint64_t strides[1] = {(cuuint64_t)lda * 2};
+    const cuuint32_t box[2] = {BK, (cuuint32_t)C::BM};
+    if (encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(xa), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return record_error_text("cuTensorMapEncodeTiled failed");
+    const cuuint64_t wdims[2] = {(cuuint64_t)(a.kpad / 2), (cuuint64_t)a.n};
+    const cuuint64_t wstrides[1] = {(cuuint64_t)(a.kpad / 2)};
+    const cuuint32_t wbox[2] = {BK / 2, (cuuint32_t)C::BNH};
+    if (encode(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(a.codes), wdims, wstrides, wbox, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return record_error_text("cuTensorMapEncodeTiled failed for the code matrix");
+    static bool configured = false;          // one per instantiation
+    if (!configured) {
+        MIXFP4_CUDA_CHECK(cudaFuncSetAttribute(gemm_pair_kernel<kMT, kKL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)C::kSmemBytes));
+        configured = true;
+    }
+    const int64_t pairs = (a.m + 2 * C::BM - 1) / (2 * C::BM);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(2 * pairs), (unsigned)((a.n + C::BN - 1) / C::BN));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = C::kSmemBytes;
+    cfg.stream = st;
+    if (cfg.gridDim.y > 65535) return MIXFP4_E_SHAPE;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    MIXFP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_pair_kernel<kMT, kKL>, tmap, tmap_w, a));
+    return check_launch("gemm_pair_kernel");
 }
 
 }  // namespace
@@ -571,6 +933,10 @@ extern "C" int mixfp4_gemm(const void* x, int64_t m, int64_t ldx, const uint8_t*
         }
     }
     const bool kl = layout == MIXFP4_LAYOUT_KERNEL;
+    // Enough 256 x 256 tiles to occupy most SMs: CTA pairs (two SMs share each decoded weight tile;
+    // measured 1.25-1.3 x the single-CTA kernel at M >= 2048, slower below about 100 CTAs).
+    const int64_t pair_ctas = 2 * ((m + 511) / 512) * ((n + 255) / 256);
+    if (pair_ctas >= 112) return kl ? launch_gemm_pair<2, true>(xa, lda, a, st) : launch_gemm_pair<2, false>(xa, lda, a, st);
     if (mt == 1 && bn == 128) return kl ? launch_gemm<1, 128, true>(xa, lda, a, st) : launch_gemm<1, 128, false>(xa, lda, a, st);
     if (mt == 1 && bn == 256) return kl ? launch_gemm<1, 256, true>(xa, lda, a, st) : launch_gemm<1, 256, false>(xa, lda, a, st);
     if (mt == 2 && bn == 128) return kl ? launch_gemm<2, 128, true>(xa, lda, a, st) : launch_gemm<2, 128, false>(xa, lda, a, st);

@@ -38,6 +38,29 @@ def test_gemm_matches_oracle(m, n, k):
     assert oracle.relative_l2(y.cpu().numpy(), ystar) <= TOL
 
 
+@pytest.mark.parametrize("layout", ["canonical", "kernel"])
+@pytest.mark.parametrize("m,n,k", [
+    (257, 256, 64), (512, 256, 128), (512, 100, 131), (700, 300, 1024), (1024, 1000, 512), (513, 640, 4096),
+])
+def test_gemm_cta_pair_shapes(m, n, k, layout):
+    # more than 256 tokens: two CTAs share every decoded weight tile; ragged token and weight
+    # tiles, an odd number of token tiles (the second CTA of the last pair has no rows), K tails
+    w = synth.student_t_weight(n, k, seed=7 * n + k)
+    x = synth.activations(m, k, seed=m, outlier_fraction=0.01)
+    packed = mx.quantize_packed(w.cuda())[0]
+    if layout == "kernel":
+        packed = packed.to_kernel_layout().with_decode_table()
+    for dt in (torch.float32, torch.bfloat16):
+        y = mx.mixfp4_linear(x.cuda(), packed, out_dtype=dt)
+        assert mxl.gemm_status() == 0
+        ystar = oracle.linear(x.float().numpy(), dequant_oracle(w))
+        if dt == torch.float32:
+            assert oracle.relative_l2(y.cpu().numpy(), ystar) <= TOL
+        else:
+            # one bf16 ulp of the exact result, plus fp32 summation noise where the result cancels to ~0
+            assert np.all(np.abs(y.float().cpu().numpy() - ystar) <= np.abs(ystar) * 2.0 ** -7 + 2e-6 * np.abs(ystar).max())
+
+
 def test_gemm_fp32_accumulation_is_tight():
     w, x = synth.config1(0, n=256, k=4096, m=256)
     packed, _, _ = mx.quantize_packed(w.cuda())
