@@ -109,7 +109,8 @@ MIXFP4_API int mixfp4_quantize(const void* x, int dtype, int64_t rows, int64_t k
 
 /* Diagnostic: the quantizer divides by block scales with a reciprocal-and-residual sequence
  * instead of a full IEEE division.  This runs the exhaustive proof that the two agree (all 2^23
- * dividend significands x the 8 significands an E4M3 scale or the constants 6 and 7 can have)
+ * dividend significands x the 8 significands an E4M3 scale or the constants 6 and 7 can have;
+ * likewise for the Hadamard kernel's division by sqrt(32) and sqrt(128))
  * and leaves the number of disagreements (expected 0) in *mismatches (device memory). */
 MIXFP4_API int mixfp4_selftest_division(unsigned long long* mismatches, void* stream);
 

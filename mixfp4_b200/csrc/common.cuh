@@ -66,4 +66,7 @@ __device__ __forceinline__ float level_value(uint32_t idx, bool e0m3) {
     return idx >= 2 ? __uint_as_float((idx + 252u) << 22) : 0.5f * static_cast<float>(idx);
 }
 
+// fwht.cu: sweep of its reciprocal-form division (called by mixfp4_selftest_division).
+int fwht_selftest_division(unsigned long long* mismatches, cudaStream_t st);
+
 }  // namespace mixfp4

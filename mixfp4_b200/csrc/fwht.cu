@@ -4,9 +4,10 @@
 // to (l + r, l - r); after log2(size) stages the block is divided by sqrt(size) (IEEE
 // division by the fp32 value of sqrt(size), as the reference's CPU path does).  Each
 // output of a stage is a single add, so the result does not depend on how the work is
-// split across threads.  One lane keeps 4 consecutive elements: strides 1 and 2 stay in
-// registers, strides 4..64 are warp shuffles.  A warp covers 128 consecutive elements of
-// a row, i.e. 128/size whole blocks.  HBM-bound: one read and one write of the tensor.
+// split across threads.  One lane keeps 16 consecutive elements (32 bytes of bf16 in flight
+// per thread): strides 1..8 stay in registers, strides 16..64 are warp shuffles.  A warp
+// covers 512 consecutive elements of a row, i.e. whole blocks.  HBM-bound: one read and one
+// write of the tensor.
 
 #include <math.h>
 
@@ -16,6 +17,7 @@ namespace mixfp4 {
 namespace {
 
 constexpr int kThreads = 256;
+constexpr int kE = 16;                    // elements per lane
 
 template <typename T>
 __device__ __forceinline__ float round_to(float v) { return static_cast<float>(Elem<T>::round(v)); }
@@ -24,6 +26,22 @@ template <> __device__ __forceinline__ float round_to<__nv_bfloat16>(float v) {
 }
 template <> __device__ __forceinline__ float round_to<__half>(float v) { return __half2float(__float2half_rn(v)); }
 template <> __device__ __forceinline__ float round_to<float>(float v) { return v; }
+
+// v / root, IEEE round-to-nearest.  Block sizes 16 and 64 have a power-of-two root (an exact
+// scaling).  For sqrt(32) and sqrt(128) the quotient comes from the reciprocal and two fused
+// corrections, which equals the IEEE quotient for every significand of the dividend (swept
+// by mixfp4_selftest_division); dividends outside [2^-100, 2^100] (zeros, subnormals,
+// infinities, NaN) take the division instruction sequence.
+__device__ __forceinline__ float div_root(float v, float root, float inv, bool pow2) {
+    if (pow2) return __fmul_rn(v, inv);
+    const float mag = fabsf(v);
+    if (mag >= 7.888609e-31f && mag <= 1.2676506e30f) {
+        const float q = __fmul_rn(v, inv);
+        const float rem = __fmaf_rn(-q, root, v);
+        return __fmaf_rn(rem, inv, q);
+    }
+    return __fdiv_rn(v, root);
+}
 
 template <typename T, bool kStagewise>
 __global__ void __launch_bounds__(kThreads) fwht_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows,
@@ -34,88 +52,108 @@ __global__ void __launch_bounds__(kThreads) fwht_kernel(const T* __restrict__ x,
     const int64_t row = warp / chunks;
     if (row >= rows) return;
     const int64_t chunk = warp - row * chunks;
-    const int64_t col = chunk * 128 + lane * 4;
+    const int64_t col = chunk * (32 * kE) + lane * kE;
     const int64_t full_k = k / size * size;
     const T* xr = x + row * ldx;
     T* yr = y + row * ldy;
-    const bool inside = col + 4 <= full_k;       // quads never straddle full_k (size % 4 == 0)
+    const bool inside = col + kE <= full_k;      // a lane's 16 elements never straddle full_k (size % 16 == 0)
 
-    float v[4];
-    if (inside && vec) {
-        if constexpr (sizeof(T) == 2) {
-            const uint2 w = *reinterpret_cast<const uint2*>(xr + col);
+    float v[kE];
+    if (col + kE <= k && vec) {
+        constexpr int kPerVec = 16 / sizeof(T);
+#pragma unroll
+        for (int q = 0; q < kE / kPerVec; ++q) {
+            const uint4 w = *reinterpret_cast<const uint4*>(xr + col + q * kPerVec);
             const T* e = reinterpret_cast<const T*>(&w);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) v[j] = Elem<T>::load(e + j);
-        } else {
-            const float4 w = *reinterpret_cast<const float4*>(xr + col);
-            v[0] = w.x; v[1] = w.y; v[2] = w.z; v[3] = w.w;
+            for (int j = 0; j < kPerVec; ++j) v[q * kPerVec + j] = Elem<T>::load(e + j);
         }
     } else {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) v[j] = col + j < k ? Elem<T>::load(xr + col + j) : 0.0f;
+        for (int j = 0; j < kE; ++j) v[j] = col + j < k ? Elem<T>::load(xr + col + j) : 0.0f;
     }
 
     if (inside) {
         if (signs) {
             const int e0 = static_cast<int>(col % size);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < kE; ++j) {
                 v[j] = __fmul_rn(v[j], signs[e0 + j]);
                 if (kStagewise) v[j] = round_to<T>(v[j]);
             }
         }
-        // strides 1 and 2 inside the lane
-        float a = __fadd_rn(v[0], v[1]), b = __fsub_rn(v[0], v[1]);
-        float c = __fadd_rn(v[2], v[3]), d = __fsub_rn(v[2], v[3]);
-        if (kStagewise) { a = round_to<T>(a); b = round_to<T>(b); c = round_to<T>(c); d = round_to<T>(d); }
-        v[0] = __fadd_rn(a, c); v[2] = __fsub_rn(a, c);
-        v[1] = __fadd_rn(b, d); v[3] = __fsub_rn(b, d);
-        if (kStagewise) {
+        // strides 1, 2, 4, 8 inside the lane
 #pragma unroll
-            for (int j = 0; j < 4; ++j) v[j] = round_to<T>(v[j]);
+        for (int s = 1; s < kE; s <<= 1) {
+#pragma unroll
+            for (int j = 0; j < kE; ++j) {
+                if (j & s) continue;
+                const float l = v[j], r = v[j | s];
+                v[j] = __fadd_rn(l, r);
+                v[j | s] = __fsub_rn(l, r);
+                if (kStagewise) { v[j] = round_to<T>(v[j]); v[j | s] = round_to<T>(v[j | s]); }
+            }
         }
     }
-    // strides 4, 8, ... size/2 across lanes; every lane of the warp takes part in the
-    // shuffles, lanes outside a whole block simply discard what they receive
-    for (int bit = 1; bit * 4 < size; bit <<= 1) {
+    // strides 16 ... size/2 across lanes; every lane of the warp takes part in the shuffles,
+    // lanes outside a whole block simply discard what they receive
+    for (int bit = 1; bit * kE < size; bit <<= 1) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < kE; ++j) {
             const float other = __shfl_xor_sync(0xffffffffu, v[j], bit);
             if (inside) {
-                float r = (lane & bit) ? __fsub_rn(other, v[j]) : __fadd_rn(v[j], other);
+                const float r = (lane & bit) ? __fsub_rn(other, v[j]) : __fadd_rn(v[j], other);
                 v[j] = kStagewise ? round_to<T>(r) : r;
             }
         }
     }
     if (inside) {
+        const bool pow2 = size == 16 || size == 64;
+        const float inv = __frcp_rn(root);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) v[j] = __fdiv_rn(v[j], root);
+        for (int j = 0; j < kE; ++j) v[j] = div_root(v[j], root, inv, pow2);
     }
 
-    if (inside && vec) {
-        T o[4];
+    if (col + kE <= k && vec) {
+        constexpr int kPerVec = 16 / sizeof(T);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) o[j] = Elem<T>::round(v[j]);
-        if constexpr (sizeof(T) == 2) *reinterpret_cast<uint2*>(yr + col) = *reinterpret_cast<const uint2*>(o);
-        else *reinterpret_cast<float4*>(yr + col) = *reinterpret_cast<const float4*>(o);
+        for (int q = 0; q < kE / kPerVec; ++q) {
+            T o[kPerVec];
+#pragma unroll
+            for (int j = 0; j < kPerVec; ++j) o[j] = Elem<T>::round(v[q * kPerVec + j]);
+            *reinterpret_cast<uint4*>(yr + col + q * kPerVec) = *reinterpret_cast<const uint4*>(o);
+        }
     } else {
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
+        for (int j = 0; j < kE; ++j)
             if (col + j < k) yr[col + j] = Elem<T>::round(v[j]);   // tail values pass through unchanged
     }
+}
+
+// Sweep of div_root's reciprocal form against IEEE division: all 2^23 significands of the
+// dividend for both irrational roots.
+__global__ void fwht_selftest_kernel(unsigned long long* mismatches) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    const float a = __uint_as_float(0x3f800000u | i);
+    unsigned long long bad = 0;
+    const float roots[2] = {static_cast<float>(sqrt(32.0)), static_cast<float>(sqrt(128.0))};
+#pragma unroll
+    for (int d = 0; d < 2; ++d) {
+        const float inv = __frcp_rn(roots[d]);
+        bad += __float_as_uint(div_root(a, roots[d], inv, false)) != __float_as_uint(__fdiv_rn(a, roots[d]));
+        bad += __float_as_uint(div_root(-a * 3.0e-5f, roots[d], inv, false)) != __float_as_uint(__fdiv_rn(-a * 3.0e-5f, roots[d]));
+    }
+    if (bad) atomicAdd(mismatches, bad);
 }
 
 template <typename T>
 int launch(const void* x, void* y, int64_t rows, int64_t k, int64_t ldx, int64_t ldy, int size,
            const float* signs, int stagewise, cudaStream_t st) {
-    const int64_t chunks = (k + 127) / 128;
+    const int64_t chunks = (k + 32 * kE - 1) / (32 * kE);
     const int64_t warps = rows * chunks;
     const int64_t ctas = (warps + kThreads / 32 - 1) / (kThreads / 32);
     if (ctas > 0x7fffffffLL) return MIXFP4_E_SHAPE;
-    const size_t quad = 4 * sizeof(T);
-    const bool vec = aligned(x, quad) && aligned(y, quad) && (ldx * sizeof(T)) % quad == 0 &&
-                     (ldy * sizeof(T)) % quad == 0;
+    const bool vec = aligned(x, 16) && aligned(y, 16) && (ldx * sizeof(T)) % 16 == 0 && (ldy * sizeof(T)) % 16 == 0;
     const float root = static_cast<float>(sqrt(static_cast<double>(size)));
     if (stagewise && sizeof(T) == 2)
         fwht_kernel<T, true><<<(unsigned)ctas, kThreads, 0, st>>>(static_cast<const T*>(x), static_cast<T*>(y), rows, k,
@@ -127,6 +165,13 @@ int launch(const void* x, void* y, int64_t rows, int64_t k, int64_t ldx, int64_t
 }
 
 }  // namespace
+
+// Part of mixfp4_selftest_division: adds this file's mismatches to the counter.
+int fwht_selftest_division(unsigned long long* mismatches, cudaStream_t st) {
+    fwht_selftest_kernel<<<(1u << 23) / 256, 256, 0, st>>>(mismatches);
+    return check_launch("fwht_selftest_kernel");
+}
+
 }  // namespace mixfp4
 
 using namespace mixfp4;

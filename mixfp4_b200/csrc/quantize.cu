@@ -524,5 +524,6 @@ extern "C" int mixfp4_selftest_division(unsigned long long* mismatches, void* st
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     MIXFP4_CUDA_CHECK(cudaMemsetAsync(mismatches, 0, sizeof(unsigned long long), st));
     selftest_division_kernel<<<(1u << 23) / 256, 256, 0, st>>>(mismatches);
-    return check_launch("selftest_division_kernel");
+    const int rc = check_launch("selftest_division_kernel");
+    return rc != MIXFP4_OK ? rc : fwht_selftest_division(mismatches, st);
 }
