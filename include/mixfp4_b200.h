@@ -75,7 +75,8 @@ enum {
 };
 
 /* format selection (project_quant/region.py:22-39 mode names) */
-enum { MIXFP4_MODE_ORACLE16 = 0, MIXFP4_MODE_ALL_E2M1 = 1, MIXFP4_MODE_ALL_E0M3 = 2 };
+enum { MIXFP4_MODE_ORACLE16 = 0, MIXFP4_MODE_ALL_E2M1 = 1, MIXFP4_MODE_ALL_E0M3 = 2,
+       MIXFP4_MODE_GIVEN = 3 /* take every block's format from the bits already in fmt */ };
 
 MIXFP4_API int mixfp4_abi_version(void);
 MIXFP4_API const char* mixfp4_status_string(int status);
@@ -106,6 +107,16 @@ MIXFP4_API int mixfp4_quantize(const void* x, int dtype, int64_t rows, int64_t k
                     uint8_t* codes, uint8_t* scales, uint8_t* fmt, float* global_scale,
                     float* e2_err, float* e0_err, float* e2_scale, float* e0_scale,
                     void* dequant, int64_t ld_dequant, void* stream);
+
+/* Coarse format regions (project_quant/region.py:42-86 region_shape / aggregate_regions and
+ * selector.py:28-33 mse_selection): one format per region of region_rows x region_groups K16
+ * blocks, E0M3 iff the region's summed E0M3 error is smaller (ties keep E2M1), summed in the
+ * reference's fp32 order.  e2_err / e0_err: f32 [rows, ceil(k/16)] from mixfp4_quantize; fmt:
+ * [rows, kpad/128] format bits out.  Follow with mixfp4_quantize(mode = MIXFP4_MODE_GIVEN) on the
+ * same fmt.  region_groups 2 or 4 (k32 / k64 regions); MIXFP4_E_MODE for other widths and for
+ * multi-row regions when K has a single region (the reference's sum order differs there). */
+MIXFP4_API int mixfp4_select_regions(const float* e2_err, const float* e0_err, int64_t rows, int64_t k,
+                          int region_rows, int region_groups, uint8_t* fmt, void* stream);
 
 /* Diagnostic: the quantizer divides by block scales with a reciprocal-and-residual sequence
  * instead of a full IEEE division.  This runs the exhaustive proof that the two agree (all 2^23

@@ -17,7 +17,7 @@ from . import build as _build
 OK = 0
 E_SHAPE = -2
 BF16, F16, F32 = 0, 1, 2
-MODE_ORACLE16, MODE_ALL_E2M1, MODE_ALL_E0M3 = 0, 1, 2
+MODE_ORACLE16, MODE_ALL_E2M1, MODE_ALL_E0M3, MODE_GIVEN = 0, 1, 2, 3
 LAYOUT_CANONICAL, LAYOUT_KERNEL = 0, 1
 FLAG_OVERLAP_PREVIOUS = 1
 
@@ -57,6 +57,8 @@ def _declare(h: ctypes.CDLL) -> None:
     h.mixfp4_amax.argtypes = [p, i32, i64, i64, i64, p, p]
     h.mixfp4_quantize.restype = i32
     h.mixfp4_quantize.argtypes = [p, i32, i64, i64, i64, i32, p, p, p, p, p, p, p, p, p, p, i64, p]
+    h.mixfp4_select_regions.restype = i32
+    h.mixfp4_select_regions.argtypes = [p, p, i64, i64, i32, i32, p, p]
     h.mixfp4_selftest_division.restype = i32
     h.mixfp4_selftest_division.argtypes = [p, p]
     h.mixfp4_dequant.restype = i32
@@ -84,7 +86,7 @@ def _declare(h: ctypes.CDLL) -> None:
 # every symbol include/mixfp4_b200.h declares
 EXPORTED = (
     "mixfp4_abi_version", "mixfp4_status_string", "mixfp4_last_cuda_error", "mixfp4_padded_k",
-    "mixfp4_amax", "mixfp4_quantize", "mixfp4_selftest_division", "mixfp4_dequant", "mixfp4_repack", "mixfp4_decode_table", "mixfp4_fwht",
+    "mixfp4_amax", "mixfp4_quantize", "mixfp4_select_regions", "mixfp4_selftest_division", "mixfp4_dequant", "mixfp4_repack", "mixfp4_decode_table", "mixfp4_fwht",
     "mixfp4_gemv", "mixfp4_gemv_grouped",
     "mixfp4_gemm_workspace_bytes", "mixfp4_gemm", "mixfp4_gemm_h128_static_max_bytes", "mixfp4_gemm_h128_static",
 )

@@ -255,7 +255,10 @@ __global__ void __launch_bounds__(kThreads) quantize_kernel(const QuantArgs a) {
             candidate<false, false>(ax, s, amax_s, gs, lo2, hi2, b2, sc2, err2, d2);
             candidate<true, false>(ax, s, amax_s, gs, lo0, hi0, b0, sc0, err0, d0);
         }
-        use_e0 = a.mode == MIXFP4_MODE_ORACLE16 ? (err0 < err2) : (a.mode == MIXFP4_MODE_ALL_E0M3);
+        if (a.mode == MIXFP4_MODE_GIVEN)   // the caller's format bits (read before this warp rewrites the byte below)
+            use_e0 = (a.fmt[row * (a.blocks_pad / 8) + (blk >> 3)] >> (blk & 7)) & 1;
+        else
+            use_e0 = a.mode == MIXFP4_MODE_ORACLE16 ? (err0 < err2) : (a.mode == MIXFP4_MODE_ALL_E0M3);
         lo = use_e0 ? lo0 : lo2;
         hi = use_e0 ? hi0 : hi2;
         scale_byte = use_e0 ? b0 : b2;
@@ -429,6 +432,43 @@ extern "C" int mixfp4_amax(const void* x, int dtype, int64_t rows, int64_t k, in
     return check_launch("amax_kernel");
 }
 
+// One format per region of region_rows x region_groups K16 blocks (project_quant/region.py:73-86
+// aggregate_regions + selector.py:28-33 mse_selection): E0M3 iff the region's summed E0M3 error
+// is smaller.  The fp32 sums follow the reference's CPU reduction order: inside a row the
+// region's blocks left to right, then the rows top to bottom, cells past the tensor's edge
+// counting as zero.  One thread owns one format byte (8 blocks) of one row of regions and
+// writes it to every row of the region.
+__global__ void __launch_bounds__(kThreads) select_regions_kernel(const float* __restrict__ e2_err,
+                                                                  const float* __restrict__ e0_err, int64_t rows,
+                                                                  int64_t groups, int64_t fmt_cols, int region_rows,
+                                                                  int region_groups, uint8_t* __restrict__ fmt) {
+    const int64_t t = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    const int64_t region_row = t / fmt_cols, col = t - region_row * fmt_cols;
+    const int64_t r0 = region_row * region_rows;
+    if (r0 >= rows) return;
+    uint32_t byte = 0;
+    for (int sub = 0; sub < 8 / region_groups; ++sub) {
+        const int64_t g0 = col * 8 + sub * region_groups;
+        if (g0 >= groups) break;
+        float sum2 = 0.0f, sum0 = 0.0f;
+        for (int r = 0; r < region_rows; ++r) {
+            float t2 = 0.0f, t0 = 0.0f;
+            for (int g = 0; g < region_groups; ++g) {
+                const bool in = r0 + r < rows && g0 + g < groups;
+                t2 = __fadd_rn(t2, in ? __ldg(e2_err + (r0 + r) * groups + g0 + g) : 0.0f);
+                t0 = __fadd_rn(t0, in ? __ldg(e0_err + (r0 + r) * groups + g0 + g) : 0.0f);
+            }
+            sum2 = __fadd_rn(sum2, t2);
+            sum0 = __fadd_rn(sum0, t0);
+        }
+        if (sum0 < sum2) {
+            for (int g = 0; g < region_groups; ++g)
+                if (g0 + g < groups) byte |= 1u << (sub * region_groups + g);
+        }
+    }
+    for (int r = 0; r < region_rows && r0 + r < rows; ++r) fmt[(r0 + r) * fmt_cols + col] = static_cast<uint8_t>(byte);
+}
+
 extern "C" int mixfp4_quantize(const void* x, int dtype, int64_t rows, int64_t k, int64_t ldx, int mode,
                                const float* amax, uint8_t* codes, uint8_t* scales, uint8_t* fmt,
                                float* global_scale, float* e2_err, float* e0_err, float* e2_scale,
@@ -436,7 +476,7 @@ extern "C" int mixfp4_quantize(const void* x, int dtype, int64_t rows, int64_t k
     if (!x || !amax || !codes || !scales || !fmt || !global_scale) return MIXFP4_E_NULL;
     if (rows <= 0 || k <= 0 || ldx < k || (dequant && ld_dequant < k)) return MIXFP4_E_SHAPE;
     if (dtype < MIXFP4_BF16 || dtype > MIXFP4_F32) return MIXFP4_E_DTYPE;
-    if (mode < MIXFP4_MODE_ORACLE16 || mode > MIXFP4_MODE_ALL_E0M3) return MIXFP4_E_MODE;
+    if (mode < MIXFP4_MODE_ORACLE16 || mode > MIXFP4_MODE_GIVEN) return MIXFP4_E_MODE;
     if (!aligned(codes, 8)) return MIXFP4_E_ALIGN;
     QuantArgs a;
     a.x = x; a.rows = rows; a.k = k; a.ldx = ldx;
@@ -526,4 +566,21 @@ extern "C" int mixfp4_selftest_division(unsigned long long* mismatches, void* st
     selftest_division_kernel<<<(1u << 23) / 256, 256, 0, st>>>(mismatches);
     const int rc = check_launch("selftest_division_kernel");
     return rc != MIXFP4_OK ? rc : fwht_selftest_division(mismatches, st);
+}
+
+extern "C" int mixfp4_select_regions(const float* e2_err, const float* e0_err, int64_t rows, int64_t k,
+                                     int region_rows, int region_groups, uint8_t* fmt, void* stream) {
+    if (!e2_err || !e0_err || !fmt) return MIXFP4_E_NULL;
+    if (rows <= 0 || k <= 0 || region_rows <= 0) return MIXFP4_E_SHAPE;
+    if (region_groups != 2 && region_groups != 4) return MIXFP4_E_MODE;
+    const int64_t groups = (k + 15) / 16;
+    // with a single region along K the reference's reduction takes another order (not reproduced)
+    if (region_rows > 1 && (groups + region_groups - 1) / region_groups == 1) return MIXFP4_E_MODE;
+    const int64_t fmt_cols = padded_k(k) / 128;
+    const int64_t threads = (rows + region_rows - 1) / region_rows * fmt_cols;
+    const int64_t ctas = (threads + kThreads - 1) / kThreads;
+    if (ctas > 0x7fffffffLL) return MIXFP4_E_SHAPE;
+    select_regions_kernel<<<(unsigned)ctas, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        e2_err, e0_err, rows, groups, fmt_cols, region_rows, region_groups, fmt);
+    return check_launch("select_regions_kernel");
 }

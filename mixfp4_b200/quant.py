@@ -30,10 +30,26 @@ TAIL_POLICY = (
 )
 
 _MODE_CODE = {"oracle16": nat.MODE_ORACLE16, "all_e2m1": nat.MODE_ALL_E2M1, "all_e0m3": nat.MODE_ALL_E0M3}
-_COARSE_REGIONS = {
-    "layer", "k32_row", "k64_row", "n8k16", "n2k64", "n4k64", "n8k64", "n16k64", "n32k64", "n64k64",
-    "m16k16", "m4k64", "m8k64", "m16k64", "m32k64",
-}
+# coarse format regions (project_quant/region.py:42-70): name -> (rows, K16 blocks) of a region
+_WEIGHT_REGIONS = {"k32_row": (1, 2), "k64_row": (1, 4), "n2k64": (2, 4), "n4k64": (4, 4), "n8k64": (8, 4),
+                   "n16k64": (16, 4), "n32k64": (32, 4), "n64k64": (64, 4)}
+_ACTIVATION_REGIONS = {"k64_row": (1, 4), "m4k64": (4, 4), "m8k64": (8, 4), "m16k64": (16, 4), "m32k64": (32, 4)}
+# regions whose fp32 error sum the reference reduces in an order that depends on the host's
+# vector width (16-wide columns, whole-tensor cascade): not reproduced
+_UNSUPPORTED_REGIONS = {"layer", "n8k16", "m16k16"}
+
+
+def region_shape(mode: str, operand_role: str) -> tuple[int, int] | None:
+    """(rows, K16 blocks) of a coarse format region, None for the per-block / whole-tensor modes."""
+    if mode in _MODE_CODE:
+        return None
+    table = _WEIGHT_REGIONS if operand_role == "weight_b" else _ACTIVATION_REGIONS
+    if mode in table:
+        return table[mode]
+    if mode in _UNSUPPORTED_REGIONS and (mode != "m16k16" or operand_role == "activation_a") \
+            and (mode != "n8k16" or operand_role == "weight_b"):
+        raise NotImplementedError(f"format_region={mode!r}: this region's error sum order is not reproduced")
+    raise ValueError(f"format_region={mode!r} is invalid for {operand_role}")
 
 
 def padded_k(k: int) -> int:
@@ -222,15 +238,21 @@ def _as_rows(x: torch.Tensor) -> torch.Tensor:
 
 
 def quantize_packed(x: torch.Tensor, *, mode: str = "oracle16", amax: torch.Tensor | None = None,
-                    want_dequant: bool = False, want_stats: bool = False, rotation: str | None = None):
+                    want_dequant: bool = False, want_stats: bool = False, rotation: str | None = None,
+                    region: tuple[int, int] | None = None):
     """Quantize a CUDA tensor [..., K] (leading dims fold into rows) into a PackedWeight.
 
     amax: optional float32 [1] device tensor holding max|x| of the WHOLE tensor this is a
     shard of (see mixfp4_amax); default: this tensor's own.
+    region: (rows, K16 blocks) of a coarse format region (see region_shape): the errors of both
+    candidates are computed first, one format is chosen per region, then the tensor is
+    quantized with those formats.
     Returns (packed, dequant_or_None, stats_or_None); stats = dict of per-block float32
     [rows, G] tensors e2_errors, e0_errors, e2_scales, e0_scales.
     """
-    if mode not in _MODE_CODE:
+    if region is None:
+        region = _WEIGHT_REGIONS.get(mode) or _ACTIVATION_REGIONS.get(mode)
+    if region is None and mode not in _MODE_CODE:
         raise ValueError(f"unsupported mode {mode!r}")
     x2 = _as_rows(x)
     rows, k = x2.shape
@@ -248,9 +270,24 @@ def quantize_packed(x: torch.Tensor, *, mode: str = "oracle16", amax: torch.Tens
         stats = {name: torch.empty((rows, groups), dtype=torch.float32, device=dev)
                  for name in ("e2_errors", "e0_errors", "e2_scales", "e0_scales")}
     dq = torch.empty((rows, k), dtype=x2.dtype, device=dev) if want_dequant else None
+    mode_code = _MODE_CODE[mode] if region is None else nat.MODE_GIVEN
+    if region is not None:
+        if region[0] > 1 and -(-groups // region[1]) == 1:
+            raise NotImplementedError("coarse regions over several rows need more than one region along K")
+        e2e = stats["e2_errors"] if stats else torch.empty((rows, groups), dtype=torch.float32, device=dev)
+        e0e = stats["e0_errors"] if stats else torch.empty((rows, groups), dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            st = nat.lib().mixfp4_quantize(
+                x2.data_ptr(), nat.DTYPE_CODE[x2.dtype], rows, k, x2.stride(0), nat.MODE_ORACLE16, amax.data_ptr(),
+                codes.data_ptr(), scales.data_ptr(), fmt.data_ptr(), gs.data_ptr(), e2e.data_ptr(), e0e.data_ptr(),
+                None, None, None, k, nat.stream_ptr(dev))
+            nat.check("mixfp4_quantize", st)
+            st = nat.lib().mixfp4_select_regions(e2e.data_ptr(), e0e.data_ptr(), rows, k, region[0], region[1],
+                                                 fmt.data_ptr(), nat.stream_ptr(dev))
+            nat.check("mixfp4_select_regions", st)
     with torch.cuda.device(dev):
         st = nat.lib().mixfp4_quantize(
-            x2.data_ptr(), nat.DTYPE_CODE[x2.dtype], rows, k, x2.stride(0), _MODE_CODE[mode], amax.data_ptr(),
+            x2.data_ptr(), nat.DTYPE_CODE[x2.dtype], rows, k, x2.stride(0), mode_code, amax.data_ptr(),
             codes.data_ptr(), scales.data_ptr(), fmt.data_ptr(), gs.data_ptr(),
             nat.ptr(stats["e2_errors"]) if stats else None, nat.ptr(stats["e0_errors"]) if stats else None,
             nat.ptr(stats["e2_scales"]) if stats else None, nat.ptr(stats["e0_scales"]) if stats else None,
@@ -312,9 +349,10 @@ def quant_mixfp4_granularity(
 
     Drop-in for the reference function of the same name: returns a new tensor of
     ``x.shape`` / ``x.dtype`` (or a GranularityResult with ``return_stats=True``).
-    Supported here: format_region oracle16 / all_e2m1 / all_e0m3, selector "mse",
-    scale_rule "standard"; the coarse regions, the output-aware selector and the
-    four_over_six rule raise NotImplementedError.
+    Supported here: format_region oracle16 / all_e2m1 / all_e0m3 and the coarse regions
+    k32_row, k64_row, n2k64 ... n64k64 (weights), m4k64 ... m32k64 (activations) with
+    selector "mse" and scale_rule "standard"; layer / n8k16 / m16k16 regions, the
+    output-aware selector and the four_over_six rule raise NotImplementedError.
     """
     working = x
     if permutation is not None:
@@ -335,10 +373,7 @@ def quant_mixfp4_granularity(
         raise NotImplementedError("output-aware selection is not implemented in the CUDA path")
     if selector != "mse":
         raise ValueError(f"unknown selector={selector!r}")
-    if mode in _COARSE_REGIONS:
-        raise NotImplementedError(f"format_region={mode!r}: coarse format regions are not implemented yet")
-    if mode not in _MODE_CODE:
-        raise ValueError(f"format_region={mode!r} is invalid for {operand_role}")
+    region = region_shape(mode, operand_role)
 
     host_input = not working.is_cuda
     if host_input:
@@ -346,7 +381,7 @@ def quant_mixfp4_granularity(
     if transform is not None:
         working = _rotation.apply_transform(working, transform)
 
-    packed, dq, stats = quantize_packed(working, mode=mode, want_dequant=True, want_stats=return_stats)
+    packed, dq, stats = quantize_packed(working, mode=mode, want_dequant=True, want_stats=return_stats, region=region)
     dequant = dq.reshape(working.shape)
     if host_input:
         dequant = dequant.to(x.device)
@@ -370,9 +405,9 @@ def quant_mixfp4_granularity(
     summary: dict[str, Any] = {
         **_tensor_error_metrics(working, dq.reshape(working.shape)),
         "scale_group_size": scale_group_size, "scale_rule": scale_rule, "format_granularity": mode,
-        "format_region_rows": 1 if mode == "oracle16" else rows,
-        "format_region_k16_groups": 1 if mode == "oracle16" else packed.groups,
-        "format_region_k_values": 16 if mode == "oracle16" else packed.groups * 16,
+        "format_region_rows": region[0] if region else (1 if mode == "oracle16" else rows),
+        "format_region_k16_groups": region[1] if region else (1 if mode == "oracle16" else packed.groups),
+        "format_region_k_values": 16 * (region[1] if region else (1 if mode == "oracle16" else packed.groups)),
         "operand_role": operand_role, "selector": "mse", "tail_policy": TAIL_POLICY,
         "tail_padding_values": (-k) % 16, "rows": rows, "N_or_M": rows, "K": k, "numel": numel,
         "num_scale_blocks": blocks, "e0_count": e0_count, "e2_count": blocks - e0_count,

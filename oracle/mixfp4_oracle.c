@@ -20,6 +20,7 @@
  *   project_quant/codebook.py:41-43      quantize_e0m3  (round-half-even, saturate 7)
  *   project_quant/core.py:115-143        oracle16 choice (e0 < e2, ties keep E2M1), select, un-pad, cast
  *   project_quant/rotation.py:47-75      fwht / apply_transform
+ *   project_quant/region.py:42-86, selector.py:28-33   coarse format regions (mse selector)
  *
  * All arithmetic is IEEE binary32, round-to-nearest-even, with NO fused
  * multiply-add (compile with -ffp-contract=off, no -ffast-math).
@@ -199,6 +200,58 @@ int mixfp4_oracle_quantize(const float* x, int64_t rows, int64_t k, int64_t ldx,
             if (e0_scale) e0_scale[r * groups + g] = s0;
             if (e2_nib) memcpy(e2_nib + (r * groups + g) * 16, n2, 16);
             if (e0_nib) memcpy(e0_nib + (r * groups + g) * 16, n0, 16);
+        }
+    }
+    return 0;
+}
+
+/* Coarse format regions (project_quant/region.py:73-86 aggregate_regions,
+ * selector.py:28-33 mse_selection): one format per region of region_rows x
+ * region_groups K16 blocks, E0M3 iff the region's summed E0M3 error is smaller
+ * (ties keep E2M1); every block keeps its own scale of the chosen format.
+ * The fp32 sum of a region follows torch's CPU reduction of the padded
+ * [R, region_rows, G, region_groups] view over dims (1, 3): inside a row the
+ * region's blocks left to right, then the rows top to bottom; cells past the
+ * tensor's edge count as zero.  (Checked against the reference for region_groups
+ * in {2, 4} and more than one region along K.)
+ * Inputs: the per-block candidate errors, nibbles and scales written by
+ * mixfp4_oracle_quantize.  Outputs: the packed bytes. */
+int mixfp4_oracle_apply_regions(const float* e2_err, const float* e0_err,
+                                const uint8_t* e2_nib, const uint8_t* e0_nib,
+                                const float* e2_scale, const float* e0_scale,
+                                int64_t rows, int64_t k, int region_rows, int region_groups,
+                                uint8_t* codes, uint8_t* scales, uint8_t* fmt) {
+    if (rows <= 0 || k <= 0 || region_rows <= 0 || region_groups <= 0) return -1;
+    const int64_t groups = (k + 15) / 16;
+    const int64_t kpad = (k + 127) / 128 * 128;
+    const int64_t ld_codes = kpad / 2, ld_scales = kpad / 16, ld_fmt = kpad / 128;
+    memset(codes, 0, (size_t)(rows * ld_codes));
+    memset(scales, 0x01, (size_t)(rows * ld_scales));
+    memset(fmt, 0, (size_t)(rows * ld_fmt));
+    for (int64_t r0 = 0; r0 < rows; r0 += region_rows) {
+        for (int64_t g0 = 0; g0 < groups; g0 += region_groups) {
+            float sum2 = 0.0f, sum0 = 0.0f;
+            for (int64_t r = r0; r < r0 + region_rows; ++r) {
+                float t2 = 0.0f, t0 = 0.0f;
+                for (int64_t g = g0; g < g0 + region_groups; ++g) {
+                    const int in = r < rows && g < groups;
+                    t2 = t2 + (in ? e2_err[r * groups + g] : 0.0f);
+                    t0 = t0 + (in ? e0_err[r * groups + g] : 0.0f);
+                }
+                sum2 = sum2 + t2;
+                sum0 = sum0 + t0;
+            }
+            const int use_e0 = sum0 < sum2;
+            for (int64_t r = r0; r < r0 + region_rows && r < rows; ++r) {
+                for (int64_t g = g0; g < g0 + region_groups && g < groups; ++g) {
+                    const uint8_t* nib = (use_e0 ? e0_nib : e2_nib) + (r * groups + g) * 16;
+                    uint8_t* crow = codes + r * ld_codes + g * 8;
+                    for (int i = 0; i < 8; ++i) crow[i] = (uint8_t)(nib[2 * i] | (nib[2 * i + 1] << 4));
+                    float back;
+                    scales[r * ld_scales + g] = e4m3_round(use_e0 ? e0_scale[r * groups + g] : e2_scale[r * groups + g], &back);
+                    if (use_e0) fmt[r * ld_fmt + (g >> 3)] |= (uint8_t)(1u << (g & 7));
+                }
+            }
         }
     }
     return 0;

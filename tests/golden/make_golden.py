@@ -138,6 +138,25 @@ def quant_case_list():
     ties = torch.stack([grid * (1 if i % 2 == 0 else -1) * 2.0 ** (i // 2 - 3) for i in range(12)])
     ties = torch.cat([ties, ties.flip(1), ties * 1.0000001, ties * 0.9999999], dim=1)
     cases.append(("ties_12x64_f32", ties.contiguous(), "oracle16", "weight_b"))
+    # coarse format regions (project_quant/region.py): ragged rows and K16 columns against the
+    # region grid, one region row only, bf16 sources, activations folded to [M, K]
+    cases += [
+        ("reg_64x256_s21", s((64, 256), 21), "n8k64", "weight_b"),
+        ("reg_100x1120_s22", s((100, 1120), 22), "n8k64", "weight_b"),
+        ("reg_70x200_s23", s((70, 200), 23), "n8k64", "weight_b"),
+        ("reg_5x1000_s24", s((5, 1000), 24), "n8k64", "weight_b"),
+        ("reg_48x384_st_bf16", synth.student_t_weight(48, 384, 1), "n8k64", "weight_b"),
+        ("reg_64x512_go_bf16", synth.gaussian_outlier_weight(64, 512, 0), "k64_row", "weight_b"),
+        ("reg_33x200_s25_k64row", s((33, 200), 25), "k64_row", "weight_b"),
+        ("reg_33x200_s25_k32row", s((33, 200), 25), "k32_row", "weight_b"),
+        ("reg_70x328_s26_n2k64", s((70, 328), 26), "n2k64", "weight_b"),
+        ("reg_70x328_s26_n4k64", s((70, 328), 26), "n4k64", "weight_b"),
+        ("reg_70x328_s26_n16k64", s((70, 328), 26), "n16k64", "weight_b"),
+        ("reg_70x328_s26_n32k64", s((70, 328), 26), "n32k64", "weight_b"),
+        ("reg_130x328_s27_n64k64", s((130, 328), 27), "n64k64", "weight_b"),
+        ("reg_2x17x200_s28_act_m8k64", s((2, 17, 200), 28), "m8k64", "activation_a"),
+        ("reg_33x256_act_k64row_bf16", synth.activations(33, 256, 3, outlier_fraction=0.02), "k64_row", "activation_a"),
+    ]
     neg_zero = torch.zeros((4, 32))
     neg_zero[:, ::2] = -0.0
     neg_zero[0, 5] = 1.0

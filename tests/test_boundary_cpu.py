@@ -62,6 +62,12 @@ def test_c_abi_argument_validation_needs_no_gpu():
     assert h.mixfp4_gemv_grouped(one, 1, 64, 64, seg, 1, nat.F16, 0, None) == -4
     seg[0].ldy = 4
     assert h.mixfp4_gemv_grouped(one, 1, 64, 64, seg, 1, nat.F32, 0, None) == -2     # ldy < n
+    assert h.mixfp4_select_regions(one, one, 8, 256, 8, 4, None, None) == -1
+    assert h.mixfp4_select_regions(one, one, 8, 256, 8, 3, one, None) == -5      # region width must be 2 or 4 blocks
+    assert h.mixfp4_select_regions(one, one, 8, 64, 8, 4, one, None) == -5       # one region along K, several rows
+    assert h.mixfp4_select_regions(one, one, 0, 64, 1, 4, one, None) == -2
+    bad = list(args); bad[5] = 4
+    assert h.mixfp4_quantize(*bad) == -5          # modes are 0..3
     assert h.mixfp4_repack(one, one, None, 4, 64, 1, one, one, None, None) == -1
     assert h.mixfp4_decode_table(None, one, None) == -1
     assert h.mixfp4_status_string(-3).decode().startswith("pointer or stride")
@@ -90,8 +96,14 @@ def test_reference_error_conventions():
         mx.quant_mixfp4_granularity(x, permutation=torch.arange(3))
     with pytest.raises(ValueError, match="invalid for"):
         mx.quant_mixfp4_granularity(x, format_region="n3k7")
+    with pytest.raises(ValueError, match="invalid for"):
+        mx.quant_mixfp4_granularity(x, format_region="m8k64")            # an activation region on a weight
     with pytest.raises(NotImplementedError):
-        mx.quant_mixfp4_granularity(x, format_region="n8k64")
+        mx.quant_mixfp4_granularity(x, format_region="n8k16")            # sum order not reproduced
+    with pytest.raises(NotImplementedError):
+        mx.quant_mixfp4_granularity(x, format_region="layer")
+    with pytest.raises(NotImplementedError):
+        mx.quant_mixfp4_granularity(x, scale_rule="four_over_six")
     with pytest.raises(ValueError, match="unknown transform"):
         mx.get_transform("H7")
 

@@ -159,6 +159,28 @@ def test_largest_8b_layer_against_oracle():
     assert err2 <= err1 * 1.05       # re-quantizing a quantized tensor does not drift
 
 
+@pytest.mark.parametrize("mode", ["n8k64", "k64_row", "n64k64"])
+def test_coarse_regions_full_size_against_oracle(mode):
+    """q projection shape 4096 x 4096: region choices, bytes and dequantized tensor equal to the
+    oracle's; every block of a region carries the region's format; a coarse choice is never
+    better than the per-block choice and never worse than the better fixed format."""
+    w = synth.student_t_weight(4096, 4096, 4)
+    wd = w.cuda()
+    packed, dq, stats = mx.quantize_packed(wd, mode=mode, want_dequant=True, want_stats=True)
+    ref = oracle.quantize(w.float().numpy(), mode)
+    assert np.array_equal(packed.codes.cpu().numpy(), ref.codes)
+    assert np.array_equal(packed.scales.cpu().numpy(), ref.scales)
+    assert np.array_equal(packed.fmt.cpu().numpy(), ref.fmt)
+    assert np.array_equal(raw_bits(dq), oracle.dequant(ref, "bf16"))
+    rr, rg = oracle.REGIONS[mode]
+    ids = packed.format_ids()
+    tiles = ids.reshape(4096 // rr, rr, 256 // rg, rg)
+    assert torch.equal(tiles, tiles[:, :1, :, :1].expand_as(tiles))
+    e2, e0 = stats["e2_errors"].double(), stats["e0_errors"].double()
+    chosen = torch.where(ids.bool(), e0, e2).sum().item()
+    assert torch.minimum(e2, e0).sum().item() <= chosen <= min(e2.sum().item(), e0.sum().item()) * (1 + 1e-9)
+
+
 def test_reciprocal_division_is_ieee_exact():
     """Exhaustive on-device proof behind the quantizer's fast division (see
     mixfp4_selftest_division): zero disagreements with IEEE division."""
