@@ -183,6 +183,30 @@ MIXFP4_API int mixfp4_gemv_grouped(const void* x, int64_t m, int64_t ldx, int64_
                         const mixfp4_gemv_segment* segments, int count,
                         int out_dtype, int flags, void* stream);
 
+/* Row-parallel decode linear with the all-reduce fused into the kernel (tensor parallelism over
+ * the GPUs of one node, one process per GPU; replaces F.linear on a K shard of the weight,
+ * modeling.py:629, followed by the sum over ranks that a row-parallel split needs -- the reference
+ * itself is single-device).  Every rank calls with its own K shard (x [M, k_shard], kernel-layout
+ * weight [n, k_shard]) and receives the same y = sum over ranks, added in rank order.  Partial sums
+ * travel as 8-byte {value, sequence} packets stored directly into the peers' buffers; every wait
+ * is bounded (2 s) and reports through *status (device int, optional).  1 <= M <= 8.
+ *
+ * Communicator: mixfp4_comm_create allocates this rank's receive buffer (slot_floats >= M * n of
+ * the largest call) on the current device; mixfp4_comm_handle exports it (mixfp4_comm_handle_bytes
+ * bytes); after the ranks have exchanged the handles, mixfp4_comm_open maps the peers' buffers
+ * (handles = world entries in rank order).  All ranks must issue the same sequence of
+ * mixfp4_gemv_allreduce calls. */
+typedef struct mixfp4_comm mixfp4_comm;
+MIXFP4_API int mixfp4_comm_create(int rank, int world, int64_t slot_floats, mixfp4_comm** out);
+MIXFP4_API int mixfp4_comm_handle_bytes(void);
+MIXFP4_API int mixfp4_comm_handle(const mixfp4_comm* comm, void* handle);
+MIXFP4_API int mixfp4_comm_open(mixfp4_comm* comm, const void* handles);
+MIXFP4_API int mixfp4_comm_destroy(mixfp4_comm* comm);
+MIXFP4_API int mixfp4_gemv_allreduce(const mixfp4_comm* comm, const void* x, int64_t m, int64_t ldx,
+                          const uint8_t* codes, const uint8_t* scales, const float* global_scale,
+                          const void* lut, int64_t n, int64_t k, void* y, int out_dtype, int64_t ldy,
+                          int* status, int flags, void* stream);
+
 /* Prefill-shape dequant-linear on the tcgen05 tensor cores (any M >= 1, meant for
  * M >= 128).  rotation_block: 0, or 128 to apply the block-Hadamard H128 to x on the
  * fly (the reference's forward-pre-hook, modeling.py:662-668) -- the rotated operand is

@@ -73,6 +73,19 @@ def _declare(h: ctypes.CDLL) -> None:
     h.mixfp4_gemv.argtypes = [p, i64, i64, p, p, p, p, i64, i64, i32, p, p, i32, i64, i32, p]
     h.mixfp4_gemv_grouped.restype = i32
     h.mixfp4_gemv_grouped.argtypes = [p, i64, i64, i64, ctypes.POINTER(GemvSegment), i32, i32, i32, p]
+    pp = ctypes.POINTER(ctypes.c_void_p)
+    h.mixfp4_comm_create.restype = i32
+    h.mixfp4_comm_create.argtypes = [i32, i32, i64, pp]
+    h.mixfp4_comm_handle_bytes.restype = i32
+    h.mixfp4_comm_handle_bytes.argtypes = []
+    h.mixfp4_comm_handle.restype = i32
+    h.mixfp4_comm_handle.argtypes = [p, p]
+    h.mixfp4_comm_open.restype = i32
+    h.mixfp4_comm_open.argtypes = [p, p]
+    h.mixfp4_comm_destroy.restype = i32
+    h.mixfp4_comm_destroy.argtypes = [p]
+    h.mixfp4_gemv_allreduce.restype = i32
+    h.mixfp4_gemv_allreduce.argtypes = [p, p, i64, i64, p, p, p, p, i64, i64, p, i32, i64, p, i32, p]
     h.mixfp4_gemm_workspace_bytes.restype = i64
     h.mixfp4_gemm_workspace_bytes.argtypes = [i64, i64, i64]
     h.mixfp4_gemm.restype = i32
@@ -88,6 +101,8 @@ EXPORTED = (
     "mixfp4_abi_version", "mixfp4_status_string", "mixfp4_last_cuda_error", "mixfp4_padded_k",
     "mixfp4_amax", "mixfp4_quantize", "mixfp4_select_regions", "mixfp4_selftest_division", "mixfp4_dequant", "mixfp4_repack", "mixfp4_decode_table", "mixfp4_fwht",
     "mixfp4_gemv", "mixfp4_gemv_grouped",
+    "mixfp4_comm_create", "mixfp4_comm_handle_bytes", "mixfp4_comm_handle", "mixfp4_comm_open", "mixfp4_comm_destroy",
+    "mixfp4_gemv_allreduce",
     "mixfp4_gemm_workspace_bytes", "mixfp4_gemm", "mixfp4_gemm_h128_static_max_bytes", "mixfp4_gemm_h128_static",
 )
 

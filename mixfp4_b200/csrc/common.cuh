@@ -69,4 +69,8 @@ __device__ __forceinline__ float level_value(uint32_t idx, bool e0m3) {
 // fwht.cu: sweep of its reciprocal-form division (called by mixfp4_selftest_division).
 int fwht_selftest_division(unsigned long long* mismatches, cudaStream_t st);
 
+// comm.cu: the parts of a communicator the fused GEMV + all-reduce kernel needs (peers: 8 entries).
+int comm_view(const mixfp4_comm* c, int* rank, int* world, int64_t* slot_packets, uint2** recv, uint2** peers,
+              uint32_t** words);
+
 }  // namespace mixfp4

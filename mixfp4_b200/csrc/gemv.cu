@@ -420,12 +420,27 @@ struct GemvSegment {
     int n;
     int tile_end;                          // first tile index after this segment's tiles
 };
+// Fused all-reduce of a row-parallel GEMV (every rank holds a K shard of the same N rows): the
+// partial sums of a row tile go straight into every peer's receive buffer as 8-byte packets
+// {fp32 bits, sequence number}, the tile's owner threads then poll their own buffer and add the
+// world partials in rank order (identical bits on every rank).  See comm.cu for the buffers.
+struct AllReduceArgs {
+    int rank, world;
+    int64_t slot_packets;        // packets per source rank and parity
+    uint2* recv;                 // this rank's buffer
+    uint2* peer[8];              // every rank's buffer as seen from this GPU
+    uint32_t* words;             // [0] sequence number, [1] finished-CTA counter
+    int* status;                 // optional device word: nonzero after an expired wait
+};
+constexpr uint64_t kPeerWaitLimitNs = 2000000000ull;   // 2 s: far beyond any legitimate wait
+
 struct GemvSmArgs {
     const __nv_bfloat16* x;
     int64_t ldx, k, kpad;
     int m, nseg, ntiles, out_dtype;
     bool x_vec;
     GemvSegment seg[kMaxSegments];
+    AllReduceArgs ar;            // used by the all-reduce instantiation only
 };
 constexpr uint32_t kStageSm = 1024u + 128u;          // codes [row half][lane] 16 B, scales [row] 8 B
 
@@ -433,7 +448,21 @@ __host__ __device__ inline uint32_t red_bytes_sm(int groups, int gw, int64_t m) 
     return (uint32_t)(groups * 2 * gw * kRowsPerCta * (int)m * 4);
 }
 
-template <int kGroups, int kGW, int kDepth>
+__device__ __forceinline__ void st_packet(uint2* p, uint32_t value, uint32_t flag) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(value), "r"(flag) : "memory");
+}
+__device__ __forceinline__ uint2 ld_packet(const uint2* p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint64_t gemv_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+template <int kGroups, int kGW, int kDepth, bool kAR = false>
 __global__ void __launch_bounds__(kGroups * kGW * 32, 1) gemv_sm_kernel(const GemvSmArgs a) {
     extern __shared__ __align__(16) uint8_t smem[];
     constexpr int kThreadsSm = kGroups * kGW * 32;
@@ -505,6 +534,9 @@ __global__ void __launch_bounds__(kGroups * kGW * 32, 1) gemv_sm_kernel(const Ge
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // sequence number of this launch (advanced by the previous launch's last CTA); flags are seq + 1
+    uint32_t seq = 0;
+    if constexpr (kAR) seq = *reinterpret_cast<volatile uint32_t*>(a.ar.words);
     {   // the whole x (m rows, zero-filled to kpad) once per CTA
         const uint32_t chunks_per_row = (uint32_t)(a.kpad >> 3);
         for (uint32_t i = threadIdx.x; i < (uint32_t)m * chunks_per_row; i += kThreadsSm) {
@@ -595,15 +627,55 @@ __global__ void __launch_bounds__(kGroups * kGW * 32, 1) gemv_sm_kernel(const Ge
             float sum = rbuf[r * m + b];
 #pragma unroll
             for (int w = 1; w < kGW; ++w) sum += rbuf[(w * kRowsPerCta + r) * m + b];
+            if constexpr (kAR) {
+                const int64_t slot = (int64_t)b * n_seg + row0 + r;
+                const int64_t par = (int64_t)(seq & 1u) * a.ar.world * a.ar.slot_packets;
+                const uint32_t flag = seq + 1u;
+                for (int p = 0; p < a.ar.world; ++p)
+                    if (p != a.ar.rank)
+                        st_packet(a.ar.peer[p] + par + a.ar.rank * a.ar.slot_packets + slot, __float_as_uint(sum), flag);
+                float total = 0.0f;
+                for (int src = 0; src < a.ar.world; ++src) {
+                    float v = sum;
+                    if (src != a.ar.rank) {
+                        const uint2* q = a.ar.recv + par + src * a.ar.slot_packets + slot;
+                        uint2 pk = ld_packet(q);
+                        if (pk.y != flag) {     // bounded wait for the peer's packet
+                            const uint64_t t0 = gemv_timer_ns();
+                            uint32_t spins = 0;
+                            while ((pk = ld_packet(q)).y != flag) {
+                                if ((++spins & 63u) == 0 && gemv_timer_ns() - t0 > kPeerWaitLimitNs) {
+                                    if (a.ar.status) atomicCAS(a.ar.status, 0, 100 + src);
+                                    break;
+                                }
+                            }
+                        }
+                        v = __uint_as_float(pk.x);
+                    }
+                    total = src == 0 ? v : total + v;
+                }
+                sum = total;
+            }
             if (a.out_dtype == MIXFP4_F32) static_cast<float*>(y_seg)[(int64_t)b * ldy + row0 + r] = sum;
             else static_cast<__nv_bfloat16*>(y_seg)[(int64_t)b * ldy + row0 + r] = __float2bfloat16_rn(sum);
         }
         parity ^= 1u;
     }
     cp_async_wait<0>();
+    if constexpr (kAR) {   // the last CTA to finish advances the sequence number for the next launch
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence();
+            if (atomicAdd(a.ar.words + 1, 1u) == gridDim.x - 1) {
+                a.ar.words[1] = 0;
+                __threadfence();
+                *reinterpret_cast<volatile uint32_t*>(a.ar.words) = seq + 1u;
+            }
+        }
+    }
 }
 
-template <int kGroups, int kGW, int kDepth>
+template <int kGroups, int kGW, int kDepth, bool kAR = false>
 int launch_sm(const GemvSmArgs& a, int flags, cudaStream_t st) {
     const int64_t ctas = a.ntiles < 148 ? a.ntiles : 148;
     const size_t smem = (size_t)a.nseg * kLut8Bytes + (((size_t)a.m * xres_row_bytes(a.kpad) + 15) & ~(size_t)15) +
@@ -611,7 +683,7 @@ int launch_sm(const GemvSmArgs& a, int flags, cudaStream_t st) {
     if (smem > 227 * 1024) return MIXFP4_E_SHAPE;
     static bool configured = false;          // one per instantiation
     if (!configured) {
-        MIXFP4_CUDA_CHECK(cudaFuncSetAttribute(gemv_sm_kernel<kGroups, kGW, kDepth>,
+        MIXFP4_CUDA_CHECK(cudaFuncSetAttribute(gemv_sm_kernel<kGroups, kGW, kDepth, kAR>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         configured = true;
     }
@@ -625,7 +697,7 @@ int launch_sm(const GemvSmArgs& a, int flags, cudaStream_t st) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (flags & MIXFP4_FLAG_OVERLAP_PREVIOUS) ? 1 : 0;
-    MIXFP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemv_sm_kernel<kGroups, kGW, kDepth>, a));
+    MIXFP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemv_sm_kernel<kGroups, kGW, kDepth, kAR>, a));
     return MIXFP4_OK;
 }
 
@@ -711,4 +783,30 @@ extern "C" int mixfp4_gemv_grouped(const void* x, int64_t m, int64_t ldx, int64_
     }
     g.ntiles = (int)tiles;
     return dispatch_sm(g, flags, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int mixfp4_gemv_allreduce(const mixfp4_comm* comm, const void* x, int64_t m, int64_t ldx,
+                                     const uint8_t* codes, const uint8_t* scales, const float* global_scale,
+                                     const void* lut, int64_t n, int64_t k, void* y, int out_dtype, int64_t ldy,
+                                     int* status, int flags, void* stream) {
+    if (!comm || !x || !codes || !scales || !global_scale || !y) return MIXFP4_E_NULL;
+    if (m < 1 || m > 8 || n <= 0 || k <= 0 || ldx < k || ldy < n || n > 0x7fffffffLL - 16) return MIXFP4_E_SHAPE;
+    if (out_dtype != MIXFP4_F32 && out_dtype != MIXFP4_BF16) return MIXFP4_E_DTYPE;
+    if (!aligned(codes, 16) || !aligned(scales, 8) || !aligned(x, 2) || (lut && !aligned(lut, 16))) return MIXFP4_E_ALIGN;
+    GemvSmArgs g = {};
+    g.x = static_cast<const __nv_bfloat16*>(x);
+    g.ldx = ldx; g.k = k; g.kpad = padded_k(k);
+    g.m = (int)m; g.nseg = 1; g.out_dtype = out_dtype;
+    g.x_vec = aligned(x, 16) && (ldx % 8 == 0) && (k % 8 == 0);
+    if ((int64_t)m * xres_row_bytes(g.kpad) > 40 * 1024) return MIXFP4_E_SHAPE;   // x must fit in shared memory
+    const int64_t tiles = (n + kRowsPerCta - 1) / kRowsPerCta;
+    g.ntiles = (int)tiles;
+    g.seg[0] = GemvSegment{codes, scales, global_scale, static_cast<const uint4*>(lut), y, ldy, (int)n, (int)tiles};
+    g.seg[1] = g.seg[2] = GemvSegment{codes, scales, global_scale, static_cast<const uint4*>(lut), y, ldy, (int)n, 0x7fffffff};
+    const int rc = comm_view(comm, &g.ar.rank, &g.ar.world, &g.ar.slot_packets, &g.ar.recv, g.ar.peer, &g.ar.words);
+    if (rc != MIXFP4_OK) return rc;
+    if (m * n > g.ar.slot_packets) return MIXFP4_E_TOO_LARGE;
+    g.ar.status = status;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return g.ntiles >= 2 * 148 ? launch_sm<3, 8, 4, true>(g, flags, st) : launch_sm<2, 16, 3, true>(g, flags, st);
 }

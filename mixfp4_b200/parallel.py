@@ -79,16 +79,91 @@ class ColumnParallelMixFP4Linear(torch.nn.Module):
         return self.inner(x, **kw)
 
 
-class RowParallelMixFP4Linear(torch.nn.Module):
-    """y = sum over ranks of x[:, k0:k1] @ W[:, k0:k1]^T (all-reduce of the partials)."""
+class PeerCommunicator:
+    """Peer-memory exchange area of the fused row-parallel GEMV + all-reduce (one per process).
 
-    def __init__(self, packed_shard, group=None):
+    slot_floats: the largest M * N a fused call will produce.  The ranks of `group` exchange
+    the buffers' IPC handles through torch.distributed; afterwards no host communication
+    happens on the data path.  All ranks must issue the same sequence of fused calls.
+    """
+
+    def __init__(self, slot_floats: int, group=None, device=None):
+        import ctypes
+        from . import _native as nat
+        self._nat = nat
+        self.group = group
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.slot_floats = int(slot_floats)
+        handle = ctypes.c_void_p()
+        with torch.cuda.device(self.device):
+            nat.check("mixfp4_comm_create", nat.lib().mixfp4_comm_create(self.rank, self.world, self.slot_floats,
+                                                                         ctypes.byref(handle)))
+            self.handle = handle
+            if self.world > 1:
+                nbytes = nat.lib().mixfp4_comm_handle_bytes()
+                mine = ctypes.create_string_buffer(nbytes)
+                nat.check("mixfp4_comm_handle", nat.lib().mixfp4_comm_handle(self.handle, mine))
+                everyone = [None] * self.world
+                dist.all_gather_object(everyone, bytes(mine.raw), group=group)
+                blob = ctypes.create_string_buffer(b"".join(everyone), nbytes * self.world)
+                nat.check("mixfp4_comm_open", nat.lib().mixfp4_comm_open(self.handle, blob))
+                dist.barrier(group=group)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    def close(self) -> None:
+        if getattr(self, "handle", None) is not None:
+            torch.cuda.synchronize(self.device)
+            if self.world > 1 and dist.is_initialized():
+                dist.barrier(group=self.group)      # nobody unmaps while a peer may still write
+            self._nat.lib().mixfp4_comm_destroy(self.handle)
+            self.handle = None
+
+    def linear(self, x_shard: torch.Tensor, packed_shard, *, out_dtype: torch.dtype | None = None,
+               overlap_previous: bool = False) -> torch.Tensor | None:
+        """sum over ranks of x_shard @ W_shard^T in one kernel per rank, or None when the shape does
+        not qualify (more than 8 rows of x, canonical layout, x too large for shared memory)."""
+        nat = self._nat
+        k = packed_shard.k
+        m = x_shard.numel() // max(1, x_shard.shape[-1])
+        if not (1 <= m <= 8 and packed_shard.layout == "kernel" and packed_shard.rotation is None
+                and x_shard.dtype == torch.bfloat16 and x_shard.shape[-1] == k and m * packed_shard.n <= self.slot_floats):
+            return None
+        out_dtype = x_shard.dtype if out_dtype is None else out_dtype
+        x2 = x_shard.reshape(-1, k)
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        y = torch.empty((m, packed_shard.n), dtype=out_dtype, device=x_shard.device)
+        with torch.cuda.device(x_shard.device):
+            st = nat.lib().mixfp4_gemv_allreduce(
+                self.handle, x2.data_ptr(), m, x2.stride(0), packed_shard.codes.data_ptr(), packed_shard.scales.data_ptr(),
+                packed_shard.global_scale.data_ptr(), nat.ptr(packed_shard.lut), packed_shard.n, k, y.data_ptr(),
+                nat.DTYPE_CODE[out_dtype], y.stride(0), self.status.data_ptr(),
+                nat.FLAG_OVERLAP_PREVIOUS if overlap_previous else 0, nat.stream_ptr(x_shard.device))
+        if st == nat.E_SHAPE:
+            return None
+        nat.check("mixfp4_gemv_allreduce", st)
+        return y.reshape(*x_shard.shape[:-1], packed_shard.n)
+
+
+class RowParallelMixFP4Linear(torch.nn.Module):
+    """y = sum over ranks of x[:, k0:k1] @ W[:, k0:k1]^T.  With a PeerCommunicator decode shapes run
+    the GEMV with the all-reduce fused in; otherwise the partials are summed by torch.distributed."""
+
+    def __init__(self, packed_shard, group=None, comm: PeerCommunicator | None = None):
         super().__init__()
         from .linear import MixFP4Linear
         self.inner = MixFP4Linear(packed_shard)
         self.group = group
+        self.comm = comm
 
     def forward(self, x_shard, **kw):
+        if self.comm is not None and self.comm.world > 1:
+            y = self.comm.linear(x_shard, self.inner.packed, out_dtype=kw.get("out_dtype"),
+                                 overlap_previous=kw.get("overlap_previous", False))
+            if y is not None:
+                return y
         y = self.inner(x_shard, **kw)
         if dist.is_initialized() and dist.get_world_size(self.group) > 1:
             dist.all_reduce(y, group=self.group)
