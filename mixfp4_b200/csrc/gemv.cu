@@ -519,17 +519,20 @@ __global__ void __launch_bounds__(kGroups * kGW * 32, 1) gemv_sm_kernel(const Ge
     if (p_tile < ntiles) set_rows();
 #pragma unroll
     for (int d = 0; d < kDepth - 1; ++d) { prefetch(d * kStageSm); cp_async_commit(); }
+    // Table entries go through registers: loaded here, stored after the x copies have been issued,
+    // so the two latencies overlap.  (entry, copy) pairs: a warp writes 512 contiguous bytes; the
+    // eight lanes that want the same entry share one L1 access (cp.async copies measured slower).
+    constexpr int kLutIters = (256 * 8 + kThreadsSm - 1) / kThreadsSm;
+    uint4 tv[kMaxSegments][kLutIters];
 #pragma unroll
     for (int s = 0; s < kMaxSegments; ++s) {
         if (s >= a.nseg) break;
         const uint4* lut = a.seg[s].lut;
         const float gs = lut ? 0.0f : *a.seg[s].global_scale;
-        // (entry, copy): a warp writes 512 contiguous bytes.  Plain loads: the eight lanes that
-        // want the same entry share one L1 access (cp.async copies of the table measured slower).
-        for (int i = threadIdx.x; i < 256 * 8; i += kThreadsSm) {
-            const int e = i >> 3;
-            const uint4 v = lut ? __ldg(lut + e) : make_lut_entry(e & 127, e >> 7, gs);
-            sts128(lut_base + s * kLut8Bytes + i * 16, v);
+#pragma unroll
+        for (int it = 0; it < kLutIters; ++it) {
+            const int e = min((int)threadIdx.x + it * kThreadsSm, 256 * 8 - 1) >> 3;
+            tv[s][it] = lut ? __ldg(lut + e) : make_lut_entry(e & 127, e >> 7, gs);
         }
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -555,6 +558,15 @@ __global__ void __launch_bounds__(kGroups * kGW * 32, 1) gemv_sm_kernel(const Ge
         }
     }
     cp_async_commit();
+#pragma unroll
+    for (int s = 0; s < kMaxSegments; ++s) {
+        if (s >= a.nseg) break;
+#pragma unroll
+        for (int it = 0; it < kLutIters; ++it) {
+            const int i = threadIdx.x + it * kThreadsSm;
+            if (i < 256 * 8) sts128(lut_base + s * kLut8Bytes + i * 16, tv[s][it]);
+        }
+    }
     cp_async_wait<0>();
     __syncthreads();
 
