@@ -462,7 +462,9 @@ __device__ __forceinline__ uint64_t gemv_timer_ns() {
     return t;
 }
 
-template <int kGroups, int kGW, int kDepth, bool kAR = false>
+// kNT: MMA column tiles (8 batch rows each).  kLutRep: copies of the decode table (8: no bank
+// conflicts; 1: 9..16 batch rows, where x takes the shared memory the copies would need).
+template <int kGroups, int kGW, int kDepth, bool kAR = false, int kNT = 1, int kLutRep = 8>
 __global__ void __launch_bounds__(kGroups * kGW * 32, 1) gemv_sm_kernel(const GemvSmArgs a) {
     extern __shared__ __align__(16) uint8_t smem[];
     constexpr int kThreadsSm = kGroups * kGW * 32;
@@ -473,8 +475,9 @@ __global__ void __launch_bounds__(kGroups * kGW * 32, 1) gemv_sm_kernel(const Ge
     const uint32_t xres_rs = xres_row_bytes(a.kpad);
     const uint32_t x_bytes = ((uint32_t)m * xres_rs + 15u) & ~15u;
     const uint32_t lut_base = (uint32_t)__cvta_generic_to_shared(smem);
-    const uint32_t x_base = lut_base + a.nseg * kLut8Bytes;
-    float* red = reinterpret_cast<float*>(smem + a.nseg * kLut8Bytes + x_bytes) + grp * (2 * kGW * kRowsPerCta * m);
+    constexpr uint32_t kLutBytesSm = 256u * 16u * kLutRep;
+    const uint32_t x_base = lut_base + a.nseg * kLutBytesSm;
+    float* red = reinterpret_cast<float*>(smem + a.nseg * kLutBytesSm + x_bytes) + grp * (2 * kGW * kRowsPerCta * m);
     const uint32_t ring = x_base + x_bytes + red_bytes_sm(kGroups, kGW, m) + warp * kDepth * kStageSm;
 
     const uint32_t ld_codes = (uint32_t)(a.kpad >> 1), ld_scales = (uint32_t)(a.kpad >> 4);
@@ -483,9 +486,14 @@ __global__ void __launch_bounds__(kGroups * kGW * 32, 1) gemv_sm_kernel(const Ge
     const int ntiles = a.ntiles;
     const int tile0 = blockIdx.x + gridDim.x * grp, tile_stride = gridDim.x * kGroups;
     const uint32_t k_lim = (uint32_t)a.k;
-    const bool x_ok = g < m;                                 // this lane's MMA column is a batch row
-    const uint32_t xrow_off = (x_ok ? (uint32_t)g * xres_rs : 0u) + t * 64;
-    const uint32_t lut_lane = lut_base + (lane & 7) * 16;
+    bool x_ok[kNT];                                          // this lane's MMA column is a batch row
+    uint32_t xrow_off[kNT];
+#pragma unroll
+    for (int nt = 0; nt < kNT; ++nt) {
+        x_ok[nt] = g + 8 * nt < m;
+        xrow_off[nt] = (x_ok[nt] ? (uint32_t)(g + 8 * nt) * xres_rs : 0u) + t * 64;
+    }
+    const uint32_t lut_lane = lut_base + (lane & (kLutRep - 1)) * 16;
 
     int p_tile = tile0, p_j = 0;
     const uint8_t* pc[2] = {a.seg[0].codes, a.seg[0].codes};
@@ -522,7 +530,7 @@ __global__ void __launch_bounds__(kGroups * kGW * 32, 1) gemv_sm_kernel(const Ge
     // Table entries go through registers: loaded here, stored after the x copies have been issued,
     // so the two latencies overlap.  (entry, copy) pairs: a warp writes 512 contiguous bytes; the
     // eight lanes that want the same entry share one L1 access (cp.async copies measured slower).
-    constexpr int kLutIters = (256 * 8 + kThreadsSm - 1) / kThreadsSm;
+    constexpr int kLutIters = (256 * kLutRep + kThreadsSm - 1) / kThreadsSm;
     uint4 tv[kMaxSegments][kLutIters];
 #pragma unroll
     for (int s = 0; s < kMaxSegments; ++s) {
@@ -531,7 +539,7 @@ __global__ void __launch_bounds__(kGroups * kGW * 32, 1) gemv_sm_kernel(const Ge
         const float gs = lut ? 0.0f : *a.seg[s].global_scale;
 #pragma unroll
         for (int it = 0; it < kLutIters; ++it) {
-            const int e = min((int)threadIdx.x + it * kThreadsSm, 256 * 8 - 1) >> 3;
+            const int e = min((int)threadIdx.x + it * kThreadsSm, 256 * kLutRep - 1) / kLutRep;
             tv[s][it] = lut ? __ldg(lut + e) : make_lut_entry(e & 127, e >> 7, gs);
         }
     }
@@ -564,21 +572,25 @@ __global__ void __launch_bounds__(kGroups * kGW * 32, 1) gemv_sm_kernel(const Ge
 #pragma unroll
         for (int it = 0; it < kLutIters; ++it) {
             const int i = threadIdx.x + it * kThreadsSm;
-            if (i < 256 * 8) sts128(lut_base + s * kLut8Bytes + i * 16, tv[s][it]);
+            if (i < 256 * kLutRep) sts128(lut_base + s * kLutBytesSm + i * 16, tv[s][it]);
         }
     }
     cp_async_wait<0>();
     __syncthreads();
 
-    float acc[2][4];                     // two independent accumulation chains
+    float acc[kNT][2][4];                // two independent accumulation chains per column tile
+    uint4 xv[kNT];                       // lanes of unused batch columns keep zeros (never stored)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) acc[0][i] = acc[1][i] = 0.0f;
+    for (int nt = 0; nt < kNT; ++nt) {
+        xv[nt] = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[nt][0][i] = acc[nt][1][i] = 0.0f;
+    }
 
-    uint4 xv = make_uint4(0u, 0u, 0u, 0u);   // lanes of unused batch columns keep zeros (never stored)
     uint32_t use_off = 0, fill_off = (kDepth - 1) * kStageSm, parity = 0;
     for (int c_tile = tile0; c_tile < ntiles; c_tile += tile_stride) {
         const int cs = (c_tile >= a.seg[0].tile_end) + (c_tile >= a.seg[1].tile_end);
-        const uint32_t lut_seg = lut_lane + cs * kLut8Bytes;
+        const uint32_t lut_seg = lut_lane + cs * kLutBytesSm;
         for (int c_j = 0; c_j < spw; ++c_j) {
             __syncwarp();                // the slot written now was read in the previous iteration
             prefetch(fill_off);
@@ -594,17 +606,20 @@ __global__ void __launch_bounds__(kGroups * kGW * 32, 1) gemv_sm_kernel(const Ge
                 const uint32_t sh = lds16(base + 1024 + (g + 8) * 8 + t * 2);
 #pragma unroll
                 for (int b = 0; b < 2; ++b) {                    // the 2 blocks of this lane's piece
-                    const uint4 tl = lds128(lut_seg + ((sl >> (8 * b)) & 0xffu) * 128u);
-                    const uint4 th = lds128(lut_seg + ((sh >> (8 * b)) & 0xffu) * 128u);
+                    const uint4 tl = lds128(lut_seg + ((sl >> (8 * b)) & 0xffu) * (16u * kLutRep));
+                    const uint4 th = lds128(lut_seg + ((sh >> (8 * b)) & 0xffu) * (16u * kLutRep));
 #pragma unroll
                     for (int half = 0; half < 2; ++half) {       // 8 elements = 2 MMAs
                         const int i = 2 * b + half;              // word index inside the piece
                         uint32_t pl[4], ph[4];
                         decode8_kl(i == 0 ? cl.x : i == 1 ? cl.y : i == 2 ? cl.z : cl.w, tl, pl);
                         decode8_kl(i == 0 ? ch.x : i == 1 ? ch.y : i == 2 ? ch.z : ch.w, th, ph);
-                        lds128_if(xv, x_base + xrow_off + (uint32_t)sub * 256u + i * 16, x_ok);
-                        mma_bf16(acc[0], pl[0], ph[0], pl[1], ph[1], xv.x, xv.y);
-                        mma_bf16(acc[1], pl[2], ph[2], pl[3], ph[3], xv.z, xv.w);
+#pragma unroll
+                        for (int nt = 0; nt < kNT; ++nt) {
+                            lds128_if(xv[nt], x_base + xrow_off[nt] + (uint32_t)sub * 256u + i * 16, x_ok[nt]);
+                            mma_bf16(acc[nt][0], pl[0], ph[0], pl[1], ph[1], xv[nt].x, xv[nt].y);
+                            mma_bf16(acc[nt][1], pl[2], ph[2], pl[3], ph[3], xv[nt].z, xv[nt].w);
+                        }
                     }
                 }
             }
@@ -617,16 +632,20 @@ __global__ void __launch_bounds__(kGroups * kGW * 32, 1) gemv_sm_kernel(const Ge
         // accumulator fragment: c0,c1 = (row g, batch 2t, 2t+1); c2,c3 = (row g+8, same batches)
         float* rbuf = red + parity * (kGW * kRowsPerCta * m);
         float* rw = rbuf + gw * kRowsPerCta * m;
-        if (2 * t < m) {
-            rw[g * m + 2 * t] = acc[0][0] + acc[1][0];
-            rw[(g + 8) * m + 2 * t] = acc[0][2] + acc[1][2];
-        }
-        if (2 * t + 1 < m) {
-            rw[g * m + 2 * t + 1] = acc[0][1] + acc[1][1];
-            rw[(g + 8) * m + 2 * t + 1] = acc[0][3] + acc[1][3];
-        }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) acc[0][i] = acc[1][i] = 0.0f;
+        for (int nt = 0; nt < kNT; ++nt) {
+            const int b0 = 8 * nt + 2 * t;
+            if (b0 < m) {
+                rw[g * m + b0] = acc[nt][0][0] + acc[nt][1][0];
+                rw[(g + 8) * m + b0] = acc[nt][0][2] + acc[nt][1][2];
+            }
+            if (b0 + 1 < m) {
+                rw[g * m + b0 + 1] = acc[nt][0][1] + acc[nt][1][1];
+                rw[(g + 8) * m + b0 + 1] = acc[nt][0][3] + acc[nt][1][3];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[nt][0][i] = acc[nt][1][i] = 0.0f;
+        }
         asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "n"(kGW * 32) : "memory");
         const int first = cs == 0 ? 0 : cs == 1 ? a.seg[0].tile_end : a.seg[1].tile_end;
         const uint32_t row0 = (uint32_t)(c_tile - first) * kRowsPerCta;
@@ -687,15 +706,15 @@ __global__ void __launch_bounds__(kGroups * kGW * 32, 1) gemv_sm_kernel(const Ge
     }
 }
 
-template <int kGroups, int kGW, int kDepth, bool kAR = false>
+template <int kGroups, int kGW, int kDepth, bool kAR = false, int kNT = 1, int kLutRep = 8>
 int launch_sm(const GemvSmArgs& a, int flags, cudaStream_t st) {
     const int64_t ctas = a.ntiles < 148 ? a.ntiles : 148;
-    const size_t smem = (size_t)a.nseg * kLut8Bytes + (((size_t)a.m * xres_row_bytes(a.kpad) + 15) & ~(size_t)15) +
+    const size_t smem = (size_t)a.nseg * 256 * 16 * kLutRep + (((size_t)a.m * xres_row_bytes(a.kpad) + 15) & ~(size_t)15) +
                         red_bytes_sm(kGroups, kGW, a.m) + (size_t)kGroups * kGW * kDepth * kStageSm;
     if (smem > 227 * 1024) return MIXFP4_E_SHAPE;
     static bool configured = false;          // one per instantiation
     if (!configured) {
-        MIXFP4_CUDA_CHECK(cudaFuncSetAttribute(gemv_sm_kernel<kGroups, kGW, kDepth, kAR>,
+        MIXFP4_CUDA_CHECK(cudaFuncSetAttribute(gemv_sm_kernel<kGroups, kGW, kDepth, kAR, kNT, kLutRep>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         configured = true;
     }
@@ -709,7 +728,7 @@ int launch_sm(const GemvSmArgs& a, int flags, cudaStream_t st) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (flags & MIXFP4_FLAG_OVERLAP_PREVIOUS) ? 1 : 0;
-    MIXFP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemv_sm_kernel<kGroups, kGW, kDepth, kAR>, a));
+    MIXFP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemv_sm_kernel<kGroups, kGW, kDepth, kAR, kNT, kLutRep>, a));
     return MIXFP4_OK;
 }
 
@@ -724,17 +743,26 @@ int dispatch(const GemvArgs& a, int flags, cudaStream_t st) {
     // x stays resident in shared memory when it is small (decode at M = 1..4 for Llama shapes)
     const bool xres = (int64_t)a.m * xres_row_bytes(a.kpad) <= 40 * 1024;
     const int64_t tiles = (a.n + kRowsPerCta - 1) / kRowsPerCta;
-    if (a.m > 8) return launch<8, 2, kKL, 1, 3, false, 2>(a, flags, st);
-    if (!xres) return launch<8, 1, kKL, 1, 3, false, 2>(a, flags, st);
     if constexpr (kKL) {
         GemvSmArgs g = {};
         g.x = a.x; g.ldx = a.ldx; g.k = a.k; g.kpad = a.kpad;
         g.m = (int)a.m; g.nseg = 1; g.ntiles = (int)tiles; g.out_dtype = a.out_dtype; g.x_vec = a.x_vec;
         g.seg[0] = GemvSegment{a.codes, a.scales, a.global_scale, a.lut, a.y, a.ldy, (int)a.n, (int)tiles};
         g.seg[1] = g.seg[2] = GemvSegment{a.codes, a.scales, a.global_scale, a.lut, a.y, a.ldy, (int)a.n, 0x7fffffff};
-        const int rc = dispatch_sm(g, flags, st);
-        if (rc != MIXFP4_E_SHAPE) return rc;     // does not fit this SM's shared memory: kernels above
+        // Largest configuration whose shared memory (tables + resident x + rings) fits; each
+        // launch_sm answers MIXFP4_E_SHAPE when it does not.
+        int rc = MIXFP4_E_SHAPE;
+        if (a.m > 8) {
+            rc = launch_sm<2, 8, 3, false, 2, 1>(g, flags, st);               // 9..16 rows: single table copy
+        } else {
+            rc = dispatch_sm(g, flags, st);
+            if (rc == MIXFP4_E_SHAPE) rc = launch_sm<3, 8, 3>(g, flags, st);              // shallower rings
+            if (rc == MIXFP4_E_SHAPE) rc = launch_sm<2, 8, 3, false, 1, 1>(g, flags, st); // single table copy
+        }
+        if (rc != MIXFP4_E_SHAPE) return rc;     // x too large for shared memory: kernels above
     }
+    if (a.m > 8) return launch<8, 2, kKL, 1, 3, false, 2>(a, flags, st);
+    if (!xres) return launch<8, 1, kKL, 1, 3, false, 2>(a, flags, st);
     // few row tiles: more warps per tile keep the SMs busy; many: three 8-warp CTAs per SM
     if (tiles < 2 * 148) return launch<16, 1, kKL, 1, 3, true, 2>(a, flags, st);
     return launch<8, 1, kKL, 1, 4, true, 3>(a, flags, st);

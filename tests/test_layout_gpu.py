@@ -70,7 +70,7 @@ def test_overlapped_launch_chain_matches_plain_chain():
         assert torch.equal(chain(True), plain)
 
 
-@pytest.mark.parametrize("m", [1, 2, 3, 4, 8])
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 8, 9, 13, 16])
 @pytest.mark.parametrize("n,k", [(50, 70), (33, 131), (16, 14336), (1000, 512), (4800, 256), (4736, 1024), (7000, 128)])
 def test_kernel_layout_gemv_matches_oracle(m, n, k):
     # ragged row counts (last tile partly outside N), K tails, fewer tiles than SMs and more
