@@ -49,8 +49,7 @@ class Layer:
 
 
 def rms_norm(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    v = x.float()
-    return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + EPS)).to(x.dtype) * w
+    return F.rms_norm(x, (x.shape[-1],), w, EPS)
 
 
 def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
@@ -141,6 +140,7 @@ def run(layers: int = 32, batch: int = 1, prompt: int = 2048, tokens: int = 32, 
     ids = torch.randint(0, VOCAB, (batch, prompt), generator=gen, device=device)
     # prefill (tcgen05 GEMM path), timed with events
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    model.forward(ids, torch.arange(prompt, device=device), prompt)      # first call: one-time set-up costs
     torch.cuda.synchronize()
     e0.record()
     logits = model.forward(ids, torch.arange(prompt, device=device), prompt)
