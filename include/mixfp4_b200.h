@@ -211,7 +211,11 @@ MIXFP4_API int mixfp4_gemv_allreduce(const mixfp4_comm* comm, const void* x, int
  * M >= 128).  rotation_block: 0, or 128 to apply the block-Hadamard H128 to x on the
  * fly (the reference's forward-pre-hook, modeling.py:662-668) -- the rotated operand is
  * bf16(FWHT_fp32(x)).  workspace: device scratch of at least
- * mixfp4_gemm_workspace_bytes(m, n, k) bytes (may be NULL when that is 0).
+ * mixfp4_gemm_workspace_bytes(m, n, k) bytes: a staging area for x (needed with rotation_block =
+ * 128 or an x that TMA cannot address: MIXFP4_E_WORKSPACE without it) followed by room for
+ * split-K partial sums (problems with few output tiles and a long K run several CTAs per tile;
+ * optional: with a smaller or NULL workspace one CTA per tile does the whole K range, the result
+ * then differs in fp32 summation order only).
  * status: optional device int[1]; non-zero after completion if a bounded device-side
  * wait gave up (the output is then invalid). */
 MIXFP4_API int64_t mixfp4_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k);
@@ -228,7 +232,9 @@ MIXFP4_API int mixfp4_gemm(const void* x, int64_t m, int64_t ldx,
  * cudaMalloc's implicit synchronisation is unacceptable.  It computes exactly what
  * mixfp4_gemm(..., rotation_block = 128, ...) computes, but the buffer that holds the
  * rotated activations bf16(H128 x) is a fixed array inside the library instead of a
- * caller-supplied workspace.  The call makes no cudaMalloc/cudaFree and calls no routine
+ * caller-supplied workspace (split-K partial sums go into the same array when they fit behind
+ * the activations; when they do not, the result differs from the workspace form in fp32
+ * summation order only).  The call makes no cudaMalloc/cudaFree and calls no routine
  * that allocates.
  *   Limit: m * round_up(k, 8) * 2 bytes must not exceed
  *   mixfp4_gemm_h128_static_max_bytes() (8 MiB, e.g. 1024 x 4096); larger requests return

@@ -91,7 +91,23 @@ struct GemmArgs {
     int out_dtype;
     int64_t ldy;
     int* status;
+    int kt_per_split;           // K steps per CTA along grid.z (all of them without split K)
+    float* partial;             // split K: fp32 partial sums [splits][m][ld_partial]
+    int64_t ld_partial;
 };
+
+// Sum of the split-K partials in split order (deterministic), converted to the output type.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, int splits, int64_t m,
+                                                            int64_t n, int64_t ld_partial, void* __restrict__ y,
+                                                            int out_dtype, int64_t ldy) {
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= m * n) return;
+    const int64_t r = i / n, c = i - r * n;
+    float sum = partial[r * ld_partial + c];
+    for (int z = 1; z < splits; ++z) sum += partial[((int64_t)z * m + r) * ld_partial + c];
+    if (out_dtype == MIXFP4_F32) static_cast<float*>(y)[r * ldy + c] = sum;
+    else static_cast<__nv_bfloat16*>(y)[r * ldy + c] = __float2bfloat16_rn(sum);
+}
 
 // ------------------------------------------------------------------------- PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -281,7 +297,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t n0 = blockIdx.x * C::BN, m0 = blockIdx.y * C::BM;
-    const int num_kt = static_cast<int>(a.kpad / BK);
+    // split K: grid.z CTAs share an output tile, each takes a run of K steps (an even number, so
+    // scale pairs and format bytes stay aligned) and stores fp32 partial sums
+    const int total_kt = static_cast<int>(a.kpad / BK);
+    const int kt0 = blockIdx.z * a.kt_per_split;
+    const int num_kt = min(a.kt_per_split, total_kt - kt0);
 
     auto full_a = [&](int s) { return base + C::kOffBar + 8u * s; };
     auto full_b = [&](int s) { return base + C::kOffBar + 8u * (kStages + s); };
@@ -328,7 +348,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                 const uint32_t ph = (kt / kStages) & 1;
                 if (!mbar_wait(empty(s), ph ^ 1, ctx, 1)) break;
                 mbar_arrive_expect_tx(full_a(s), C::kABytes);
-                tma_load_2d(base + C::kOffA + s * C::kABytes, &tmap_x, full_a(s), kt * BK, (int)m0);
+                tma_load_2d(base + C::kOffA + s * C::kABytes, &tmap_x, full_a(s), (kt0 + kt) * BK, (int)m0);
                 issued = kt + 1;
             }
             // never leave with a bulk copy still writing into this CTA's shared memory
@@ -367,7 +387,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                 const uint32_t ph = (kt / kWStages) & 1;
                 if (!mbar_wait(empty_w(s), ph ^ 1, ctx, 7)) break;
                 mbar_arrive_expect_tx(full_w(s), C::kWBytes);
-                tma_load_2d(base + C::kOffW + s * C::kWBytes, &tmap_w, full_w(s), kt * (BK / 2), (int)n0);
+                tma_load_2d(base + C::kOffW + s * C::kWBytes, &tmap_w, full_w(s), (kt0 + kt) * (BK / 2), (int)n0);
                 issued = kt + 1;
             }
             for (int kt = max(0, issued - kWStages); kt < issued; ++kt)
@@ -419,8 +439,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
 
         uint32_t codes[kWords], ncodes[kWords];
         bool ok = load_codes(codes, 0);
-        uint2 sc2 = load_scale_pair(0), nsc2 = sc2;
-        uint32_t fb = kKL ? 0u : __ldg(fptr);
+        uint2 sc2 = load_scale_pair(kt0 >> 1), nsc2 = sc2;
+        uint32_t fb = kKL ? 0u : __ldg(fptr + (kt0 >> 1));
         for (int kt = 0; kt < num_kt && ok; ++kt) {
             const int s = kt % kStages;
             const uint32_t ph = (kt / kStages) & 1;
@@ -428,8 +448,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
             if (kt + 1 < num_kt) {                      // next K step's packed data, one step ahead
                 ok = load_codes(ncodes, kt + 1);
                 if (!ok) break;
-                if ((kt & 1) == 0 && kt + 2 < num_kt) nsc2 = load_scale_pair((kt >> 1) + 1);
-                if constexpr (!kKL) nfb = __ldg(fptr + ((kt + 1) >> 1));
+                if ((kt & 1) == 0 && kt + 2 < num_kt) nsc2 = load_scale_pair(((kt0 + kt) >> 1) + 1);
+                if constexpr (!kKL) nfb = __ldg(fptr + ((kt0 + kt + 1) >> 1));
             }
             const uint32_t scs = ((kt & 1) ? sc2.y : sc2.x) >> (8 * part * kBlocks);
             ok = __all_sync(0xffffffffu, mbar_wait(empty(s), ph ^ 1, ctx, 5));   // warp-uniform: lanes stay together
@@ -459,7 +479,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
             fb = nfb;
         }
 
-        if (ok && mbar_wait(accum_bar, 0, ctx, 6)) store_accumulators<kMT, kBN>(a, tmem_base, m0, n0, warp, lane);
+        if (ok && mbar_wait(accum_bar, 0, ctx, 6)) {
+            if (gridDim.z == 1) {
+                store_accumulators<kMT, kBN>(a, tmem_base, m0, n0, warp, lane);
+            } else {                     // this split's partial sums, fp32 [m, ld_partial]
+                GemmArgs p = a;
+                p.y = a.partial + (size_t)blockIdx.z * a.m * a.ld_partial;
+                p.out_dtype = MIXFP4_F32;
+                p.ldy = a.ld_partial;
+                store_accumulators<kMT, kBN>(p, tmem_base, m0, n0, warp, lane);
+            }
+        }
     }
 
     tcgen05_fence_before();
@@ -820,11 +850,54 @@ int launch_gemm(const void* xa, int64_t lda, const GemmArgs& a, cudaStream_t st)
                                                (int)C::kSmemBytes));
         configured = true;
     }
-    const dim3 grid((unsigned)((a.n + C::BN - 1) / C::BN), (unsigned)((a.m + C::BM - 1) / C::BM));
+    const int total_kt = static_cast<int>(a.kpad / BK);
+    const int splits = (total_kt + a.kt_per_split - 1) / a.kt_per_split;
+    const dim3 grid((unsigned)((a.n + C::BN - 1) / C::BN), (unsigned)((a.m + C::BM - 1) / C::BM), (unsigned)splits);
     if (grid.y > 65535) return MIXFP4_E_SHAPE;
     gemm_kernel<kMT, kBN, kKL><<<grid, kThreads, C::kSmemBytes, st>>>(tmap, tmap_w, a);
-    return check_launch("gemm_kernel");
+    int rc = check_launch("gemm_kernel");
+    if (rc == MIXFP4_OK && splits > 1) {
+        const int64_t total = a.m * a.n;
+        splitk_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(a.partial, splits, a.m, a.n, a.ld_partial,
+                                                                             a.y, a.out_dtype, a.ldy);
+        rc = check_launch("splitk_reduce_kernel");
+    }
+    return rc;
 }
+
+// Tile choice of the single-CTA kernel: estimated time = waves over the 148 SMs x relative time of
+// one tile (measured: a tile with two 128-row sub-tiles or 256 weight rows amortises the transcode
+// better), and how many CTAs share a tile along K when the tiles alone would leave SMs idle.
+struct GemmPlan {
+    int mt, bn, splits, kt_per_split;
+};
+GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k) {
+    GemmPlan p = {1, 128, 1, static_cast<int>(padded_k(k) / BK)};
+    const int mts[4] = {1, 2, 1, 2}, bns[4] = {128, 128, 256, 256};
+    const double cost[4] = {1.0, 1.35, 1.78, 2.2};
+    double best = 1e300;
+    int64_t best_tiles = 1;
+    for (int i = 0; i < 4; ++i) {
+        const int64_t tiles = ((m + 128 * mts[i] - 1) / (128 * mts[i])) * ((n + bns[i] - 1) / bns[i]);
+        const double t = (double)((tiles + 147) / 148) * cost[i];
+        if (t < best) { best = t; p.mt = mts[i]; p.bn = bns[i]; best_tiles = tiles; }
+    }
+    // Each K step costs a CTA about the same whatever M is (the weight tile has to be decoded),
+    // so a problem with few tiles and a long K runs several CTAs per tile: fp32 partial sums go to
+    // the workspace and are added in split order.  At least 8 K steps per CTA, even counts.
+    const int total_kt = p.kt_per_split;
+    int splits = static_cast<int>(148 / best_tiles);
+    if (splits > 8) splits = 8;
+    if (splits > total_kt / 8) splits = total_kt / 8;
+    if (splits >= 2) {
+        int per = (total_kt + splits - 1) / splits;
+        per += per & 1;
+        p.kt_per_split = per;
+        p.splits = (total_kt + per - 1) / per;
+    }
+    return p;
+}
+int64_t partial_ld(int64_t n) { return (n + 3) / 4 * 4; }
 
 template <int kMT, bool kKL>
 int launch_gemm_pair(const void* xa, int64_t lda, const GemmArgs& a, cudaStream_t st) {
@@ -876,9 +949,14 @@ int launch_gemm_pair(const void* xa, int64_t lda, const GemmArgs& a, cudaStream_
 
 using namespace mixfp4;
 
-extern "C" int64_t mixfp4_gemm_workspace_bytes(int64_t m, int64_t /*n*/, int64_t k) {
+extern "C" int64_t mixfp4_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k) {
     if (m <= 0 || k <= 0) return 0;
-    return (x_staging_bytes(m, k) + 255) / 256 * 256;
+    int64_t bytes = (x_staging_bytes(m, k) + 255) / 256 * 256;
+    if (n > 0) {
+        const GemmPlan p = plan_gemm(m, n, k);
+        if (p.splits > 1) bytes += (int64_t)p.splits * m * partial_ld(n) * 4;
+    }
+    return bytes;
 }
 
 extern "C" int mixfp4_gemm(const void* x, int64_t m, int64_t ldx, const uint8_t* codes, const uint8_t* scales,
@@ -919,17 +997,16 @@ extern "C" int mixfp4_gemm(const void* x, int64_t m, int64_t ldx, const uint8_t*
     a.lut = static_cast<const uint4*>(lut);
     a.m = m; a.n = n; a.k = k; a.kpad = padded_k(k);
     a.y = y; a.out_dtype = out_dtype; a.ldy = ldy; a.status = status;
-    // Tile choice: estimated time = waves over the 148 SMs x relative time of one tile (measured:
-    // a tile with two 128-row sub-tiles or 256 weight rows amortises the transcode better).
-    int mt = 1, bn = 128;
-    {
-        const int mts[4] = {1, 2, 1, 2}, bns[4] = {128, 128, 256, 256};
-        const double cost[4] = {1.0, 1.35, 1.78, 2.2};
-        double best = 1e300;
-        for (int i = 0; i < 4; ++i) {
-            const int64_t tiles = ((m + 128 * mts[i] - 1) / (128 * mts[i])) * ((n + bns[i] - 1) / bns[i]);
-            const double t = (double)((tiles + 147) / 148) * cost[i];
-            if (t < best) { best = t; mt = mts[i]; bn = bns[i]; }
+    a.kt_per_split = static_cast<int>(a.kpad / BK); a.partial = nullptr; a.ld_partial = 0;
+    const GemmPlan plan = plan_gemm(m, n, k);
+    const int mt = plan.mt, bn = plan.bn;
+    if (plan.splits > 1) {     // split K needs room for the partial sums after the staging area; without it: one CTA per tile
+        const int64_t staging = (x_staging_bytes(m, k) + 255) / 256 * 256;
+        const int64_t need = staging + (int64_t)plan.splits * m * partial_ld(n) * 4;
+        if (workspace && workspace_bytes >= need && aligned(workspace, 16)) {
+            a.kt_per_split = plan.kt_per_split;
+            a.partial = reinterpret_cast<float*>(static_cast<char*>(workspace) + staging);
+            a.ld_partial = partial_ld(n);
         }
     }
     const bool kl = layout == MIXFP4_LAYOUT_KERNEL;
@@ -991,6 +1068,9 @@ extern "C" int mixfp4_gemm_h128_static(const void* x, int64_t m, int64_t ldx, co
     // rewritten here, so nothing left over from an earlier call is ever consumed)
     rc = mixfp4_fwht(x, scratch, MIXFP4_BF16, m, k, ldx, lda, 128, nullptr, 0, stream);
     if (rc != MIXFP4_OK) return rc;
+    // The rest of the array is offered as workspace: mixfp4_gemm puts split-K partial sums behind the
+    // staging area (which is where the rotated activations already are) when they fit, exactly as it
+    // does with a caller's workspace, so both entry points take the same decisions.
     return mixfp4_gemm(scratch, m, lda, codes, scales, fmt, global_scale, n, k, layout, lut, 0, y, out_dtype, ldy,
-                       nullptr, 0, status, 0, stream);
+                       scratch, kStaticScratchBytes, status, 0, stream);
 }

@@ -120,6 +120,28 @@ def test_gemm_with_online_h128_rotation(m, n, k):
     assert oracle.relative_l2(y, plain) <= 0.2
 
 
+@pytest.mark.parametrize("m,n,k", [(32, 512, 4096), (100, 300, 14336), (128, 1000, 2048), (17, 4096, 4096)])
+def test_gemm_split_k_small_m(m, n, k):
+    # few output tiles and a long K: several CTAs share a tile along K, fp32 partials are summed
+    # in split order; with and without room for the partials (NULL workspace: one CTA per tile)
+    from mixfp4_b200 import _native as nat
+    w = synth.student_t_weight(n, k, seed=n + k)
+    x = synth.activations(m, k, seed=m, outlier_fraction=0.01).cuda()
+    packed = mx.quantize_packed(w.cuda())[0].to_kernel_layout().with_decode_table()
+    ystar = oracle.linear(x.float().cpu().numpy(), dequant_oracle(w))
+    y = mx.mixfp4_linear(x, packed, out_dtype=torch.float32)
+    assert mxl.gemm_status() == 0
+    assert oracle.relative_l2(y.cpu().numpy(), ystar) <= TOL
+    assert torch.equal(y, mx.mixfp4_linear(x, packed, out_dtype=torch.float32))     # deterministic
+    if m > 16:
+        y2 = torch.empty_like(y)
+        st = nat.lib().mixfp4_gemm(x.data_ptr(), m, k, packed.codes.data_ptr(), packed.scales.data_ptr(), None,
+                                   packed.global_scale.data_ptr(), n, k, nat.LAYOUT_KERNEL, packed.lut.data_ptr(), 0,
+                                   y2.data_ptr(), nat.F32, n, None, 0, None, 0, torch.cuda.current_stream().cuda_stream)
+        assert st == 0
+        assert oracle.relative_l2(y2.cpu().numpy(), ystar) <= TOL
+
+
 def test_c_abi_workspace_contract():
     from mixfp4_b200 import _native as nat
     lib = nat.lib()
