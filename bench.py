@@ -272,6 +272,15 @@ def run_ours(args):
     if rank == 0 and world == 1 and not args.no_extra:
         extra = secondary_numbers(dev)
         extra["decode_tokens_per_s_linears_only"] = round(1e3 / dev_ms * m, 1)
+        # whole decoder (norms, RoPE, attention over a 2048-token bf16 KV cache, bf16 head as stock
+        # PyTorch operators around the packed linears): tokens/s and the linears' share of a step
+        del model, graph
+        torch.cuda.empty_cache()
+        from mixfp4_b200 import llama_decode
+        for batch in (1, 8):
+            r = llama_decode.run(layers=nlayers, batch=batch, prompt=2048, tokens=16, device=dev)
+            extra["decode_full_model_b%d" % batch] = {k: r[k] for k in (
+                "decode_tokens_per_s", "decode_ms_per_step", "mixfp4_linear_time_fraction", "prefill_tokens_per_s")}
 
     if rank == 0:
         peak, peak_kind = measured_peak()
