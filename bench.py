@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (BASELINE config 2): the linear layers of a Llama-3-8B decode step at M=1 --
+Workload: the linear layers of a Llama-3-8B decode step at M=1 --
 32 layers x (q 4096x4096, k/v 1024x4096, o 4096x4096, gate/up 14336x4096, down
 4096x14336) = 224 mixed-FP4 linears over 3.98 GB of packed weights (every weight is a
 distinct buffer, so the working set is ~30x the L2).  One step = one pass over all 224

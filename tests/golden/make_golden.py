@@ -224,7 +224,7 @@ def digest_cases(pq) -> dict:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a checkout of the reference project")
     ap.add_argument("--skip-digests", action="store_true")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
