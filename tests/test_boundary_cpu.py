@@ -120,3 +120,30 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(build, "LIB_PATH", str(tmp_path / "absent.so"))
     with pytest.raises(RuntimeError, match="no fallback"):
         nat.lib()
+
+
+def test_model_walk_helpers_follow_the_reference_rules():
+    # project_quant/modeling.py:55-68: heads are skipped, the type is the last name component
+    from torch import nn
+    from mixfp4_b200 import convert
+
+    class Attn(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.q_proj, self.o_proj = nn.Linear(8, 8), nn.Linear(8, 8)
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.layers = nn.ModuleList([Attn(), Attn()])
+            self.score_head = nn.Linear(8, 2)
+            self.lm_head = nn.Linear(8, 16)
+            self.proj = nn.Linear(8, 8)
+
+    names = [n for n, _ in convert.named_linears(Net())]
+    assert names == ["layers.0.q_proj", "layers.0.o_proj", "layers.1.q_proj", "layers.1.o_proj", "proj"]
+    assert convert.module_type("layers.1.q_proj") == "q_proj" and convert.module_type("proj") == "other_linear"
+    assert convert.layer_index("model.layers.17.mlp.down_proj") == 17 and convert.layer_index("proj") is None
+    assert convert.quantize_model_weights(Net(), "fp16") == []          # high-precision modes convert nothing
+    with pytest.raises(ValueError, match="packed checkpoint"):
+        convert.load_packed(Net(), {"format": "something else", "version": 1, "layers": {}})
