@@ -872,28 +872,27 @@ struct GemmPlan {
     int mt, bn, splits, kt_per_split;
 };
 GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k) {
-    GemmPlan p = {1, 128, 1, static_cast<int>(padded_k(k) / BK)};
+    const int total_kt = static_cast<int>(padded_k(k) / BK);
+    GemmPlan p = {1, 128, 1, total_kt};
     const int mts[4] = {1, 2, 1, 2}, bns[4] = {128, 128, 256, 256};
-    const double cost[4] = {1.0, 1.35, 1.78, 2.2};
+    const double cost[4] = {1.0, 1.35, 1.78, 2.2};      // time of one K step of a tile, in units of ~0.45 us
+    // Each K step costs a CTA about the same whatever M is (the weight tile has to be decoded), so
+    // a problem with few tiles and a long K can run several CTAs per tile: fp32 partial sums go to
+    // the workspace and are added in split order.  At least 8 K steps per CTA, even counts; the
+    // partial sums cost their bytes once written and once read (about 3 TB/s through L2).
     double best = 1e300;
-    int64_t best_tiles = 1;
     for (int i = 0; i < 4; ++i) {
         const int64_t tiles = ((m + 128 * mts[i] - 1) / (128 * mts[i])) * ((n + bns[i] - 1) / bns[i]);
-        const double t = (double)((tiles + 147) / 148) * cost[i];
-        if (t < best) { best = t; p.mt = mts[i]; p.bn = bns[i]; best_tiles = tiles; }
-    }
-    // Each K step costs a CTA about the same whatever M is (the weight tile has to be decoded),
-    // so a problem with few tiles and a long K runs several CTAs per tile: fp32 partial sums go to
-    // the workspace and are added in split order.  At least 8 K steps per CTA, even counts.
-    const int total_kt = p.kt_per_split;
-    int splits = static_cast<int>(148 / best_tiles);
-    if (splits > 8) splits = 8;
-    if (splits > total_kt / 8) splits = total_kt / 8;
-    if (splits >= 2) {
-        int per = (total_kt + splits - 1) / splits;
-        per += per & 1;
-        p.kt_per_split = per;
-        p.splits = (total_kt + per - 1) / per;
+        for (int splits = 1; splits <= 8; ++splits) {
+            if (splits > 1 && (splits > total_kt / 8 || tiles * splits > 148)) break;
+            int per = (total_kt + splits - 1) / splits;
+            per += (splits > 1) ? (per & 1) : 0;
+            const int real_splits = (total_kt + per - 1) / per;
+            const double waves = (double)((tiles * real_splits + 147) / 148);
+            double t = waves * per * cost[i];
+            if (real_splits > 1) t += (double)real_splits * m * n * 8.0 / 3.0e6 / 0.45;
+            if (t < best) { best = t; p.mt = mts[i]; p.bn = bns[i]; p.splits = real_splits; p.kt_per_split = per; }
+        }
     }
     return p;
 }
@@ -1014,6 +1013,10 @@ extern "C" int mixfp4_gemm(const void* x, int64_t m, int64_t ldx, const uint8_t*
     // measured 1.25-1.3 x the single-CTA kernel at M >= 2048, slower below about 100 CTAs).
     const int64_t pair_ctas = 2 * ((m + 511) / 512) * ((n + 255) / 256);
     if (pair_ctas >= 112) return kl ? launch_gemm_pair<2, true>(xa, lda, a, st) : launch_gemm_pair<2, false>(xa, lda, a, st);
+    // fewer tokens: pairs of 128-row CTAs (the pair still shares a 256-row weight tile)
+    const int64_t pair_ctas_small = 2 * ((m + 255) / 256) * ((n + 255) / 256);
+    if (pair_ctas_small >= 112 && m > 256)
+        return kl ? launch_gemm_pair<1, true>(xa, lda, a, st) : launch_gemm_pair<1, false>(xa, lda, a, st);
     if (mt == 1 && bn == 128) return kl ? launch_gemm<1, 128, true>(xa, lda, a, st) : launch_gemm<1, 128, false>(xa, lda, a, st);
     if (mt == 1 && bn == 256) return kl ? launch_gemm<1, 256, true>(xa, lda, a, st) : launch_gemm<1, 256, false>(xa, lda, a, st);
     if (mt == 2 && bn == 128) return kl ? launch_gemm<2, 128, true>(xa, lda, a, st) : launch_gemm<2, 128, false>(xa, lda, a, st);

@@ -41,6 +41,8 @@ def test_gemm_matches_oracle(m, n, k):
 @pytest.mark.parametrize("layout", ["canonical", "kernel"])
 @pytest.mark.parametrize("m,n,k", [
     (257, 256, 64), (512, 256, 128), (512, 100, 131), (700, 300, 1024), (1024, 1000, 512), (513, 640, 4096),
+    (1000, 3600, 192),      # enough tiles for pairs of 128-row CTAs, too few for pairs of 256-row CTAs
+    (1024, 14336, 128),     # pairs of 256-row CTAs
 ])
 def test_gemm_cta_pair_shapes(m, n, k, layout):
     # more than 256 tokens: two CTAs share every decoded weight tile; ragged token and weight
