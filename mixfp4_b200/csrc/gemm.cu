@@ -439,7 +439,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
 
         uint32_t codes[kWords], ncodes[kWords];
         bool ok = load_codes(codes, 0);
-        uint2 sc2 = load_scale_pair(kt0 >> 1), nsc2 = sc2;
+        // scale pairs are fetched two pairs (four K steps) ahead: a global load takes longer than two steps
+        uint2 sc2 = load_scale_pair(kt0 >> 1), nsc2 = num_kt > 2 ? load_scale_pair((kt0 >> 1) + 1) : sc2, nnsc2 = nsc2;
         uint32_t fb = kKL ? 0u : __ldg(fptr + (kt0 >> 1));
         for (int kt = 0; kt < num_kt && ok; ++kt) {
             const int s = kt % kStages;
@@ -448,7 +449,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
             if (kt + 1 < num_kt) {                      // next K step's packed data, one step ahead
                 ok = load_codes(ncodes, kt + 1);
                 if (!ok) break;
-                if ((kt & 1) == 0 && kt + 2 < num_kt) nsc2 = load_scale_pair(((kt0 + kt) >> 1) + 1);
+                if ((kt & 1) == 0 && kt + 4 < num_kt) nnsc2 = load_scale_pair(((kt0 + kt) >> 1) + 2);
                 if constexpr (!kKL) nfb = __ldg(fptr + ((kt0 + kt + 1) >> 1));
             }
             const uint32_t scs = ((kt & 1) ? sc2.y : sc2.x) >> (8 * part * kBlocks);
@@ -475,7 +476,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
             if (lane == 0) mbar_arrive(full_b(s));
 #pragma unroll
             for (int i = 0; i < kWords; ++i) codes[i] = ncodes[i];
-            if (kt & 1) sc2 = nsc2;
+            if (kt & 1) { sc2 = nsc2; nsc2 = nnsc2; }
             fb = nfb;
         }
 
@@ -747,7 +748,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_pair_kernel(const __grid_con
 
         uint32_t codes[kWords], ncodes[kWords];
         bool ok = load_codes(codes, 0);
-        uint2 sc2 = load_scale_pair(0), nsc2 = sc2;
+        uint2 sc2 = load_scale_pair(0), nsc2 = num_kt > 2 ? load_scale_pair(1) : sc2, nnsc2 = nsc2;   // two pairs ahead
         uint32_t fb = kKL ? 0u : __ldg(fptr);
         for (int kt = 0; kt < num_kt && ok; ++kt) {
             const int s = kt % kStages;
@@ -756,7 +757,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_pair_kernel(const __grid_con
             if (kt + 1 < num_kt) {
                 ok = load_codes(ncodes, kt + 1);
                 if (!ok) break;
-                if ((kt & 1) == 0 && kt + 2 < num_kt) nsc2 = load_scale_pair((kt >> 1) + 1);
+                if ((kt & 1) == 0 && kt + 4 < num_kt) nnsc2 = load_scale_pair((kt >> 1) + 2);
                 if constexpr (!kKL) nfb = __ldg(fptr + ((kt + 1) >> 1));
             }
             const uint32_t scs = ((kt & 1) ? sc2.y : sc2.x) >> (8 * part * kBlocks);
@@ -783,7 +784,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_pair_kernel(const __grid_con
             if (lane == 0) mbar_arrive_leader(full_b(s));   // this CTA's half is in place
 #pragma unroll
             for (int i = 0; i < kWords; ++i) codes[i] = ncodes[i];
-            if (kt & 1) sc2 = nsc2;
+            if (kt & 1) { sc2 = nsc2; nsc2 = nnsc2; }
             fb = nfb;
         }
 
