@@ -167,7 +167,7 @@ MIXFP4_API int mixfp4_gemv(const void* x, int64_t m, int64_t ldx,
 /* Several weights that take the same x in one launch (q/k/v, gate/up of a decoder layer; no
  * single counterpart in the reference, which calls nn.Linear.forward once per projection,
  * modeling.py:629): y_i[M,n_i] = x[M,K] * W_i[n_i,K]^T for i < count, 1 <= count <= 3,
- * 1 <= M <= 8, all weights in MIXFP4_LAYOUT_KERNEL with the same K.  Saves the per-launch
+ * 1 <= M <= 16, all weights in MIXFP4_LAYOUT_KERNEL with the same K.  Saves the per-launch
  * ramp of the small projections.  Returns MIXFP4_E_SHAPE when x (M * (2 * padded K + 16)
  * bytes) or the tables do not fit in shared memory: call mixfp4_gemv per weight then. */
 typedef struct mixfp4_gemv_segment {

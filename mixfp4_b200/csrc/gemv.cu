@@ -738,6 +738,16 @@ int dispatch_sm(const GemvSmArgs& g, int flags, cudaStream_t st) {
     return g.ntiles >= 2 * 148 ? launch_sm<3, 8, 4>(g, flags, st) : launch_sm<2, 16, 3>(g, flags, st);
 }
 
+// Largest configuration whose shared memory (tables + resident x + rings) fits; each launch_sm
+// answers MIXFP4_E_SHAPE when it does not, and so does this when nothing fits.
+int dispatch_sm_chain(const GemvSmArgs& g, int flags, cudaStream_t st) {
+    if (g.m > 8) return launch_sm<2, 8, 3, false, 2, 1>(g, flags, st);               // 9..16 rows: single table copy
+    int rc = dispatch_sm(g, flags, st);
+    if (rc == MIXFP4_E_SHAPE) rc = launch_sm<3, 8, 3>(g, flags, st);                  // shallower rings
+    if (rc == MIXFP4_E_SHAPE) rc = launch_sm<2, 8, 3, false, 1, 1>(g, flags, st);     // single table copy
+    return rc;
+}
+
 template <bool kKL>
 int dispatch(const GemvArgs& a, int flags, cudaStream_t st) {
     // x stays resident in shared memory when it is small (decode at M = 1..4 for Llama shapes)
@@ -749,16 +759,7 @@ int dispatch(const GemvArgs& a, int flags, cudaStream_t st) {
         g.m = (int)a.m; g.nseg = 1; g.ntiles = (int)tiles; g.out_dtype = a.out_dtype; g.x_vec = a.x_vec;
         g.seg[0] = GemvSegment{a.codes, a.scales, a.global_scale, a.lut, a.y, a.ldy, (int)a.n, (int)tiles};
         g.seg[1] = g.seg[2] = GemvSegment{a.codes, a.scales, a.global_scale, a.lut, a.y, a.ldy, (int)a.n, 0x7fffffff};
-        // Largest configuration whose shared memory (tables + resident x + rings) fits; each
-        // launch_sm answers MIXFP4_E_SHAPE when it does not.
-        int rc = MIXFP4_E_SHAPE;
-        if (a.m > 8) {
-            rc = launch_sm<2, 8, 3, false, 2, 1>(g, flags, st);               // 9..16 rows: single table copy
-        } else {
-            rc = dispatch_sm(g, flags, st);
-            if (rc == MIXFP4_E_SHAPE) rc = launch_sm<3, 8, 3>(g, flags, st);              // shallower rings
-            if (rc == MIXFP4_E_SHAPE) rc = launch_sm<2, 8, 3, false, 1, 1>(g, flags, st); // single table copy
-        }
+        const int rc = dispatch_sm_chain(g, flags, st);
         if (rc != MIXFP4_E_SHAPE) return rc;     // x too large for shared memory: kernels above
     }
     if (a.m > 8) return launch<8, 2, kKL, 1, 3, false, 2>(a, flags, st);
@@ -799,7 +800,7 @@ extern "C" int mixfp4_gemv_grouped(const void* x, int64_t m, int64_t ldx, int64_
                                    void* stream) {
     if (!x || !segments) return MIXFP4_E_NULL;
     if (count < 1 || count > kMaxSegments) return MIXFP4_E_SHAPE;
-    if (m < 1 || m > 8 || k <= 0 || ldx < k) return MIXFP4_E_SHAPE;
+    if (m < 1 || m > 16 || k <= 0 || ldx < k) return MIXFP4_E_SHAPE;
     if (out_dtype != MIXFP4_F32 && out_dtype != MIXFP4_BF16) return MIXFP4_E_DTYPE;
     if (!aligned(x, 2)) return MIXFP4_E_ALIGN;
     GemvSmArgs g = {};
@@ -807,7 +808,6 @@ extern "C" int mixfp4_gemv_grouped(const void* x, int64_t m, int64_t ldx, int64_
     g.ldx = ldx; g.k = k; g.kpad = padded_k(k);
     g.m = (int)m; g.nseg = count; g.out_dtype = out_dtype;
     g.x_vec = aligned(x, 16) && (ldx % 8 == 0) && (k % 8 == 0);
-    if ((int64_t)m * xres_row_bytes(g.kpad) > 40 * 1024) return MIXFP4_E_SHAPE;   // x must fit in shared memory
     int64_t tiles = 0;
     for (int s = 0; s < kMaxSegments; ++s) {
         const mixfp4_gemv_segment& in = segments[s < count ? s : count - 1];
@@ -822,7 +822,7 @@ extern "C" int mixfp4_gemv_grouped(const void* x, int64_t m, int64_t ldx, int64_
                                (int)in.n, s < count ? (int)tiles : 0x7fffffff};
     }
     g.ntiles = (int)tiles;
-    return dispatch_sm(g, flags, static_cast<cudaStream_t>(stream));
+    return dispatch_sm_chain(g, flags, static_cast<cudaStream_t>(stream));   // MIXFP4_E_SHAPE: x does not fit
 }
 
 extern "C" int mixfp4_gemv_allreduce(const mixfp4_comm* comm, const void* x, int64_t m, int64_t ldx,

@@ -120,7 +120,7 @@ def mixfp4_linear_grouped(x: torch.Tensor, packs: list[PackedWeight], *, out_dty
                           overlap_previous: bool = False) -> list[torch.Tensor]:
     """[x @ W_i^T for W_i in packs] for weights that take the same x (q/k/v, gate/up).
 
-    Decode shapes (at most 8 rows of x), up to three kernel-layout weights without a folded
+    Decode shapes (at most 16 rows of x), up to three kernel-layout weights without a folded
     rotation: one launch (``mixfp4_gemv_grouped``).  Anything else: one ``mixfp4_linear`` per
     weight, same results.
     """
@@ -129,7 +129,7 @@ def mixfp4_linear_grouped(x: torch.Tensor, packs: list[PackedWeight], *, out_dty
     k = packs[0].k
     lead = x.shape[:-1]
     m = x.numel() // max(1, x.shape[-1])
-    grouped = (1 <= m <= 8 and 1 <= len(packs) <= 3 and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] == k
+    grouped = (1 <= m <= 16 and 1 <= len(packs) <= 3 and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] == k
                and all(p.k == k and p.layout == "kernel" and p.rotation is None for p in packs))
     if grouped:
         out_dtype = x.dtype if out_dtype is None else out_dtype

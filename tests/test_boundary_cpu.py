@@ -57,7 +57,7 @@ def test_c_abi_argument_validation_needs_no_gpu():
     seg[0].codes = seg[0].scales = seg[0].global_scale = seg[0].y = 16
     seg[0].ldy, seg[0].n = 8, 8
     assert h.mixfp4_gemv_grouped(one, 1, 64, 64, seg, 0, nat.F32, 0, None) == -2     # count out of range
-    assert h.mixfp4_gemv_grouped(one, 9, 64, 64, seg, 1, nat.F32, 0, None) == -2     # more than 8 rows of x
+    assert h.mixfp4_gemv_grouped(one, 17, 64, 64, seg, 1, nat.F32, 0, None) == -2    # more than 16 rows of x
     assert h.mixfp4_gemv_grouped(one, 1, 64, 64, None, 1, nat.F32, 0, None) == -1
     assert h.mixfp4_gemv_grouped(one, 1, 64, 64, seg, 1, nat.F16, 0, None) == -4
     seg[0].ldy = 4

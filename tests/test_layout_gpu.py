@@ -85,7 +85,7 @@ def test_kernel_layout_gemv_matches_oracle(m, n, k):
         assert oracle.relative_l2(y, ystar) <= 1e-3
 
 
-@pytest.mark.parametrize("m", [1, 4, 8])
+@pytest.mark.parametrize("m", [1, 4, 8, 11, 16])
 @pytest.mark.parametrize("ns", [(1024, 256, 256), (4096, 1024), (40, 17, 1000), (5000,)])
 def test_grouped_launch_equals_separate_launches(m, ns):
     k = 1024
