@@ -295,7 +295,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t* gen = smem_raw + (base - raw);            // generic pointer to the aligned base
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;   // provably warp-uniform
     const uint32_t n0 = blockIdx.x * C::BN, m0 = blockIdx.y * C::BM;
     // split K: grid.z CTAs share an output tile, each takes a run of K steps (an even number, so
     // scale pairs and format bytes stay aligned) and stores fp32 partial sums
@@ -618,7 +618,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_pair_kernel(const __grid_con
     const uint32_t base = (raw + 1023u) & ~1023u;      // same offset in both CTAs of the pair
     uint8_t* gen = smem_raw + (base - raw);
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;   // provably warp-uniform
     const uint32_t rank = cluster_ctarank();           // 0 = leader
     const uint32_t m0 = blockIdx.x * C::BM;            // this CTA's token rows
     const uint32_t n0 = blockIdx.y * C::BN;            // the pair's weight rows; this CTA decodes n0 + rank*128 ...

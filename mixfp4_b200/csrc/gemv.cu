@@ -123,7 +123,7 @@ __global__ void __launch_bounds__(kWarps * 32, kMinCtas) gemv_kernel(const GemvA
                                (kKL ? 0u : (uint32_t)kRowsPerCta * (uint32_t)(a.kpad >> 7)) + 15u) & ~15u;
     const uint32_t xres_rs = xres_row_bytes(a.kpad);
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;   // provably warp-uniform
     const int g = lane >> 2, t = lane & 3;
     const uint32_t ld_codes = (uint32_t)(a.kpad >> 1), ld_scales = (uint32_t)(a.kpad >> 4);
     const uint32_t ld_fmt = (uint32_t)(a.kpad >> 7);
@@ -468,7 +468,9 @@ template <int kGroups, int kGW, int kDepth, bool kAR = false, int kNT = 1, int k
 __global__ void __launch_bounds__(kGroups * kGW * 32, 1) gemv_sm_kernel(const GemvSmArgs a) {
     extern __shared__ __align__(16) uint8_t smem[];
     constexpr int kThreadsSm = kGroups * kGW * 32;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // the warp index through a shuffle: the compiler then knows it is warp-uniform and keeps the loop
+    // and ring bookkeeping that derives from it on the uniform datapath, off the (saturated) ALU pipe
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
     const int grp = warp / kGW, gw = warp % kGW;
     const int g = lane >> 2, t = lane & 3;
     const int m = a.m;
