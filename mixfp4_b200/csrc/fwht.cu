@@ -48,7 +48,7 @@ __global__ void __launch_bounds__(kThreads) fwht_kernel(const T* __restrict__ x,
                                                         int64_t k, int64_t ldx, int64_t ldy, int size, float root,
                                                         const float* __restrict__ signs, bool vec, int64_t chunks) {
     const int lane = threadIdx.x & 31;
-    const int64_t warp = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+    const int64_t warp = (int64_t)blockIdx.x * (kThreads / 32) + __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);   // provably warp-uniform
     const int64_t row = warp / chunks;
     if (row >= rows) return;
     const int64_t chunk = warp - row * chunks;

@@ -185,7 +185,7 @@ __global__ void selftest_division_kernel(unsigned long long* mismatches) {
 template <typename T>
 __global__ void __launch_bounds__(kThreads) quantize_kernel(const QuantArgs a) {
     const int lane = threadIdx.x & 31;
-    const int64_t warp = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+    const int64_t warp = (int64_t)blockIdx.x * kWarpsPerCta + __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);   // provably warp-uniform
     const int64_t row = warp / a.chunks;
     const float amax = *a.amax;
     const float gs = amax > 0.0f ? __fdiv_rn(amax, 2688.0f) : 1.0f;
@@ -359,7 +359,7 @@ __global__ void __launch_bounds__(kThreads) repack_kernel(const uint8_t* __restr
                                                           uint8_t* __restrict__ scales_out,
                                                           uint8_t* __restrict__ fmt_out) {
     const int lane = threadIdx.x & 31;
-    const int64_t warp = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+    const int64_t warp = (int64_t)blockIdx.x * kWarpsPerCta + __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);   // provably warp-uniform
     const int64_t row = warp / chunks;
     if (row >= rows) return;
     const int64_t chunk = warp - row * chunks;
