@@ -29,6 +29,21 @@ inline int check_launch(const char* where) {
     return err == cudaSuccess ? MIXFP4_OK : record_cuda_error(err, where);
 }
 
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per kernel instantiation AND device: the
+// attribute belongs to the device's copy of the function, and a process may drive several GPUs.
+// `done` is the instantiation's own bit mask (one bit per device ordinal, up to 64 devices).
+template <typename Kernel>
+inline int ensure_dynamic_smem(Kernel kernel, int bytes, unsigned long long& done) {
+    int dev = 0;
+    MIXFP4_CUDA_CHECK(cudaGetDevice(&dev));
+    const unsigned long long bit = 1ull << (dev & 63);
+    if (!(done & bit)) {
+        MIXFP4_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+        done |= bit;
+    }
+    return MIXFP4_OK;
+}
+
 __host__ __device__ inline int64_t padded_k(int64_t k) { return (k + 127) / 128 * 128; }
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }

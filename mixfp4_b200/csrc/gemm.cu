@@ -845,12 +845,8 @@ int launch_gemm(const void* xa, int64_t lda, const GemmArgs& a, cudaStream_t st)
                                wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cw != CUDA_SUCCESS) return record_error_text("cuTensorMapEncodeTiled failed for the code matrix");
-    static bool configured = false;          // one per instantiation
-    if (!configured) {
-        MIXFP4_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel<kMT, kBN, kKL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               (int)C::kSmemBytes));
-        configured = true;
-    }
+    static unsigned long long configured = 0;          // one per instantiation, one bit per device
+    if (const int rc = ensure_dynamic_smem(gemm_kernel<kMT, kBN, kKL>, (int)C::kSmemBytes, configured)) return rc;
     const int total_kt = static_cast<int>(a.kpad / BK);
     const int splits = (total_kt + a.kt_per_split - 1) / a.kt_per_split;
     const dim3 grid((unsigned)((a.n + C::BN - 1) / C::BN), (unsigned)((a.m + C::BM - 1) / C::BM), (unsigned)splits);
@@ -920,12 +916,8 @@ int launch_gemm_pair(const void* xa, int64_t lda, const GemmArgs& a, cudaStream_
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return record_error_text("cuTensorMapEncodeTiled failed for the code matrix");
-    static bool configured = false;          // one per instantiation
-    if (!configured) {
-        MIXFP4_CUDA_CHECK(cudaFuncSetAttribute(gemm_pair_kernel<kMT, kKL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               (int)C::kSmemBytes));
-        configured = true;
-    }
+    static unsigned long long configured = 0;          // one per instantiation, one bit per device
+    if (const int rc = ensure_dynamic_smem(gemm_pair_kernel<kMT, kKL>, (int)C::kSmemBytes, configured)) return rc;
     const int64_t pairs = (a.m + 2 * C::BM - 1) / (2 * C::BM);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(2 * pairs), (unsigned)((a.n + C::BN - 1) / C::BN));

@@ -373,12 +373,9 @@ int launch(const GemvArgs& a, int flags, cudaStream_t st) {
                         (kKL ? 0 : (size_t)kRowsPerCta * (a.kpad / 128)) + 16 +
                         (kXRes ? (size_t)a.m * xres_row_bytes(a.kpad) : 0);
     if (smem > 200 * 1024 || ctas > 0x7fffffffLL) return MIXFP4_E_SHAPE;
-    static bool configured = false;          // one per instantiation
-    if (!configured) {
-        MIXFP4_CUDA_CHECK(cudaFuncSetAttribute(gemv_kernel<kWarps, kNTiles, kKL, kU, kDepth, kXRes, kMinCtas>,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        configured = true;
-    }
+    static unsigned long long configured = 0;          // one per instantiation, one bit per device
+    if (const int rc = ensure_dynamic_smem(gemv_kernel<kWarps, kNTiles, kKL, kU, kDepth, kXRes, kMinCtas>, 200 * 1024, configured))
+        return rc;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)ctas);
     cfg.blockDim = dim3(kWarps * 32);
@@ -714,12 +711,9 @@ int launch_sm(const GemvSmArgs& a, int flags, cudaStream_t st) {
     const size_t smem = (size_t)a.nseg * 256 * 16 * kLutRep + (((size_t)a.m * xres_row_bytes(a.kpad) + 15) & ~(size_t)15) +
                         red_bytes_sm(kGroups, kGW, a.m) + (size_t)kGroups * kGW * kDepth * kStageSm;
     if (smem > 227 * 1024) return MIXFP4_E_SHAPE;
-    static bool configured = false;          // one per instantiation
-    if (!configured) {
-        MIXFP4_CUDA_CHECK(cudaFuncSetAttribute(gemv_sm_kernel<kGroups, kGW, kDepth, kAR, kNT, kLutRep>,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        configured = true;
-    }
+    static unsigned long long configured = 0;          // one per instantiation, one bit per device
+    if (const int rc = ensure_dynamic_smem(gemv_sm_kernel<kGroups, kGW, kDepth, kAR, kNT, kLutRep>, 227 * 1024, configured))
+        return rc;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)ctas);
     cfg.blockDim = dim3(kGroups * kGW * 32);
