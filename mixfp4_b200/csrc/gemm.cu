@@ -50,6 +50,7 @@ constexpr int BK = 64;                     // K elements per pipeline stage (one
 constexpr int kDecodeWarps = 8;             // more transcoder warps were measured: no gain alone, a loss in CTA pairs           // two warps per scheduler were too few to hide the decode latency
 constexpr int kThreads = (3 + kDecodeWarps) * 32;   // x producer, MMA issuer, transcoders, code producer
 constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s: far beyond any legitimate wait
+constexpr uint32_t kMinSpins = 1u << 20;            // ... and at least this many polls
 
 // Tile configuration: kMT sub-tiles of 128 rows of x (each its own TMEM accumulator, all
 // sharing the transcoded weight tile) by kBN weight rows.
@@ -152,7 +153,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 63u) == 0) {
             if (*ctx.abort_flag) return false;
-            if (global_timer_ns() - t0 > kWaitLimitNs) {
+            // both a long time and many polls: a discontinuity of the timer alone never aborts a wait
+            if (spins > kMinSpins && global_timer_ns() - t0 > kWaitLimitNs) {
                 *ctx.abort_flag = 1;
                 if (ctx.status) atomicCAS(ctx.status, 0, code);
                 return false;
@@ -568,7 +570,8 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
     while (!mbar_try_wait_cluster(bar, parity)) {
         if ((++spins & 63u) == 0) {
             if (*ctx.abort_flag) return false;
-            if (global_timer_ns() - t0 > kWaitLimitNs) {
+            // both a long time and many polls: a discontinuity of the timer alone never aborts a wait
+            if (spins > kMinSpins && global_timer_ns() - t0 > kWaitLimitNs) {
                 *ctx.abort_flag = 1;
                 if (ctx.status) atomicCAS(ctx.status, 0, code);
                 return false;
