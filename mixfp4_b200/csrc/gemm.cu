@@ -50,7 +50,7 @@ constexpr int BK = 64;                     // K elements per pipeline stage (one
 constexpr int kDecodeWarps = 8;             // more transcoder warps were measured: no gain alone, a loss in CTA pairs           // two warps per scheduler were too few to hide the decode latency
 constexpr int kThreads = (3 + kDecodeWarps) * 32;   // x producer, MMA issuer, transcoders, code producer
 constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s: far beyond any legitimate wait
-constexpr uint32_t kMinSpins = 1u << 20;            // ... and at least this many polls
+constexpr uint32_t kMinSpins = 1u << 16;            // ... and at least this many polls
 
 // Tile configuration: kMT sub-tiles of 128 rows of x (each its own TMEM accumulator, all
 // sharing the transcoded weight tile) by kBN weight rows.

@@ -429,7 +429,7 @@ struct AllReduceArgs {
     uint32_t* words;             // [0] sequence number, [1] finished-CTA counter
     int* status;                 // optional device word: nonzero after an expired wait
 };
-constexpr uint64_t kPeerWaitLimitNs = 2000000000ull;   // 2 s (and at least 2^20 polls): far beyond any legitimate wait
+constexpr uint64_t kPeerWaitLimitNs = 2000000000ull;   // 2 s (and at least 2^16 polls): far beyond any legitimate wait
 
 struct GemvSmArgs {
     const __nv_bfloat16* x;
@@ -674,7 +674,7 @@ __global__ void __launch_bounds__(kGroups * kGW * 32, 1) gemv_sm_kernel(const Ge
                             const uint64_t t0 = gemv_timer_ns();
                             uint32_t spins = 0;
                             while ((pk = ld_packet(q)).y != flag) {
-                                if ((++spins & 63u) == 0 && spins > (1u << 20) && gemv_timer_ns() - t0 > kPeerWaitLimitNs) {
+                                if ((++spins & 63u) == 0 && spins > (1u << 16) && gemv_timer_ns() - t0 > kPeerWaitLimitNs) {
                                     if (a.ar.status) atomicCAS(a.ar.status, 0, 100 + src);
                                     break;
                                 }
