@@ -92,6 +92,7 @@ struct GemmArgs {
     int out_dtype;
     int64_t ldy;
     int* status;
+    int tma_store;              // pair kernel: epilogue through shared memory and TMA stores
     int kt_per_split;           // K steps per CTA along grid.z (all of them without split K)
     float* partial;             // split K: fp32 partial sums [splits][m][ld_partial]
     int64_t ld_partial;
@@ -503,6 +504,73 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     }
 }
 
+// Epilogue through shared memory and TMA stores (bf16 output with 16-byte aligned rows): every
+// lane owns one accumulator row, so direct stores touch 32 different lines per instruction and
+// cost about a tenth of a tile's time.  Here the warps write their bf16 values into boxes of
+// 128 rows x 64 columns in the 128-byte swizzle (conflict-free), and one thread hands the boxes
+// to the TMA unit, which also clips them at the edges of y.  `stage` is operand memory that is
+// free once the accumulator barrier has completed (1024-byte aligned, kMT * kBN / 64 * 16 KB).
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1) : "memory");
+}
+// AND over the epilogue warps (named barrier 1): they take the shared-memory epilogue together or not at all.
+__device__ __forceinline__ bool epilogue_warps_all(bool pred) {
+    uint32_t out;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 q, %1, 0;\n\t"
+        "bar.red.and.pred p, 1, %2, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(out)
+        : "r"((uint32_t)pred), "n"(kDecodeWarps * 32)
+        : "memory");
+    return out != 0;
+}
+template <int kMT, int kBN>
+__device__ __forceinline__ void store_accumulators_tma(const GemmArgs& a, const CUtensorMap* tmap_y, uint32_t stage,
+                                                       uint32_t tmem_base, uint32_t m0, uint32_t n0, int warp, int lane) {
+    tcgen05_fence_after();
+    constexpr int kColGroups = kDecodeWarps / 4;
+    const int q = warp & 3, ch = (warp - 2) >> 2;
+    constexpr int kChunks = kBN / (32 * kColGroups);
+    constexpr int kBoxesPerSub = kBN / 64;
+    const uint32_t row = q * 32 + lane;                       // row inside a 128-row box
+#pragma unroll 1
+    for (int it = 0; it < kMT * kChunks; ++it) {
+        const int mt = it / kChunks, c = it % kChunks;
+        const int col0 = ch * (kBN / kColGroups) + c * 32;
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(mt * kBN + col0), r);
+        uint32_t pk[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+            pk[j] = *reinterpret_cast<const uint32_t*>(&v);
+        }
+        const uint32_t box = stage + (uint32_t)(mt * kBoxesPerSub + col0 / 64) * 16384u + row * 128u;
+        const uint32_t chunk0 = (uint32_t)(col0 % 64) / 8;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            sts128(box + (((chunk0 + j) ^ (row & 7u)) * 16u), pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+    }
+    fence_async_proxy();
+    asm volatile("bar.sync 1, %0;" ::"n"(kDecodeWarps * 32) : "memory");      // the epilogue warps only
+    if (warp == 2 && lane == 0) {
+#pragma unroll
+        for (int mt = 0; mt < kMT; ++mt) {
+#pragma unroll
+            for (int bx = 0; bx < kBoxesPerSub; ++bx) {
+                const int64_t r0 = (int64_t)m0 + mt * 128, c0 = (int64_t)n0 + bx * 64;
+                if (r0 < a.m && c0 < a.n)
+                    tma_store_2d(tmap_y, stage + (uint32_t)(mt * kBoxesPerSub + bx) * 16384u, (int)c0, (int)r0);
+            }
+        }
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");    // the boxes are read before the CTA leaves
+    }
+}
+
 // ------------------------------------------------------------------- CTA-pair kernel
 // The single-CTA kernel above is bound by the shared-memory data path: per K step the
 // transcoders store and the tensor core re-reads the whole decoded 256-row weight tile, once
@@ -613,6 +681,7 @@ __device__ __forceinline__ void umma_pair_commit(uint32_t bar) {
 template <int kMT, bool kKL>
 __global__ void __launch_bounds__(kThreads, 1) gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_x,
                                                                 const __grid_constant__ CUtensorMap tmap_w,
+                                                                const __grid_constant__ CUtensorMap tmap_y,
                                                                 const GemmArgs a) {
     using C = PairCfg<kMT>;
     constexpr int kStages = C::kStages, kWStages = C::kWStages;
@@ -791,8 +860,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_pair_kernel(const __grid_con
             fb = nfb;
         }
 
-        if (ok && mbar_wait_cluster(accum_bar, 0, ctx, 6))
+        // a.tma_store is the same for every thread, so the named barrier inside is reached by all or none
+        const bool done = ok && mbar_wait_cluster(accum_bar, 0, ctx, 6);
+        if (a.tma_store) {
+            if (epilogue_warps_all(done))
+                store_accumulators_tma<kMT, C::BN>(a, &tmap_y, base + C::kOffA, tmem_base, m0, n0, warp, lane);
+        } else if (done) {
             store_accumulators<kMT, C::BN>(a, tmem_base, m0, n0, warp, lane);
+        }
     }
 
     // Both CTAs stay until the pair is done: the leader's MMAs read the peer's shared memory and
@@ -899,12 +974,25 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k) {
 int64_t partial_ld(int64_t n) { return (n + 3) / 4 * 4; }
 
 template <int kMT, bool kKL>
-int launch_gemm_pair(const void* xa, int64_t lda, const GemmArgs& a, cudaStream_t st) {
+int launch_gemm_pair(const void* xa, int64_t lda, const GemmArgs& args, cudaStream_t st) {
     using C = PairCfg<kMT>;
+    GemmArgs a = args;
     EncodeTiledFn encode = encode_tiled_fn();
     if (!encode) return record_error_text("cuTensorMapEncodeTiled is not available from the driver");
-    CUtensorMap tmap, tmap_w;
+    CUtensorMap tmap, tmap_w, tmap_y;
     const cuuint32_t estr[2] = {1, 1};
+    // bf16 output with 16-byte aligned rows: boxes of 128 rows x 64 columns leave through TMA stores
+    a.tma_store = a.out_dtype == MIXFP4_BF16 && aligned(a.y, 16) && (a.ldy * 2) % 16 == 0;
+    {
+        const cuuint64_t ydims[2] = {(cuuint64_t)a.n, (cuuint64_t)a.m};
+        const cuuint64_t ystrides[1] = {(cuuint64_t)a.ldy * 2};
+        const cuuint32_t ybox[2] = {64, 128};
+        if (a.tma_store &&
+            encode(&tmap_y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.y, ydims, ystrides, ybox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            a.tma_store = 0;
+        if (!a.tma_store) memset(&tmap_y, 0, sizeof(tmap_y));
+    }
     const cuuint64_t dims[2] = {(cuuint64_t)a.k, (cuuint64_t)a.m};
     const cuuint64_t strides[1] = {(cuuint64_t)lda * 2};
     const cuuint32_t box[2] = {BK, (cuuint32_t)C::BM};
@@ -935,7 +1023,7 @@ int launch_gemm_pair(const void* xa, int64_t lda, const GemmArgs& a, cudaStream_
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    MIXFP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_pair_kernel<kMT, kKL>, tmap, tmap_w, a));
+    MIXFP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_pair_kernel<kMT, kKL>, tmap, tmap_w, tmap_y, a));
     return check_launch("gemm_pair_kernel");
 }
 
@@ -992,7 +1080,7 @@ extern "C" int mixfp4_gemm(const void* x, int64_t m, int64_t ldx, const uint8_t*
     a.lut = static_cast<const uint4*>(lut);
     a.m = m; a.n = n; a.k = k; a.kpad = padded_k(k);
     a.y = y; a.out_dtype = out_dtype; a.ldy = ldy; a.status = status;
-    a.kt_per_split = static_cast<int>(a.kpad / BK); a.partial = nullptr; a.ld_partial = 0;
+    a.kt_per_split = static_cast<int>(a.kpad / BK); a.partial = nullptr; a.ld_partial = 0; a.tma_store = 0;
     const GemmPlan plan = plan_gemm(m, n, k);
     const int mt = plan.mt, bn = plan.bn;
     if (plan.splits > 1) {     // split K needs room for the partial sums after the staging area; without it: one CTA per tile
