@@ -3,15 +3,21 @@
 // (project_quant/modeling.py:629 + nn.Linear.forward).  HBM-bound by design: the packed
 // weight (0.5703 B/element) is read exactly once, x stays in L1/L2.
 //
-// Work split.  A row tile is 16 consecutive weight rows; the warps of a CTA split its K range
-// in interleaved 128-element steps and their partial sums are added in a fixed order through
-// shared memory (deterministic).  With the kernel layout the CTAs are persistent (two or three
-// per SM) and walk over row tiles blockIdx.x, blockIdx.x + gridDim.x, ...  Inside a warp a
-// 16 x 128 step is laid over the mma.sync.m16n8k16 A-fragment: lane (g, t) = (lane/4, lane%4)
-// owns rows g and g+8 and the 32 consecutive K elements starting at 32*t.  The k index of an
-// MMA is only a summation label, so the 16 k-slots of every MMA are filled with whatever 4
-// consecutive elements each lane decodes next; the B fragment takes the same 4 elements of x
-// (batch row g).  Two accumulator sets alternate to shorten the MMA dependency chain.
+// Two kernels share the work split below.  gemv_sm_kernel (further down) is the main one: one
+// persistent CTA per SM, kernel layout, x resident in shared memory, an eightfold decode table;
+// it also carries the grouped launch (several weights that share x) and the row-parallel form
+// with the all-reduce in its epilogue.  gemv_kernel (first) serves the canonical layout and
+// activations too large for shared memory, with two or three CTAs per SM.
+//
+// Work split.  A row tile is 16 consecutive weight rows; the warps of a CTA (or of a warp group)
+// split its K range in interleaved 128-element steps and their partial sums are added in a fixed
+// order through shared memory (deterministic).  CTAs are persistent and walk over row tiles.
+// Inside a warp a 16 x 128 step is laid over the mma.sync.m16n8k16 A-fragment: lane (g, t) =
+// (lane/4, lane%4) owns rows g and g+8 and the 32 consecutive K elements starting at 32*t.  The
+// k index of an MMA is only a summation label, so the 16 k-slots of every MMA are filled with
+// whatever 4 consecutive elements each lane decodes next; the B fragment takes the same 4
+// elements of x (batch row g).  Two accumulator sets alternate to shorten the MMA dependency
+// chain.  The limiter is the ALU pipe (the byte-permute decode), then the shared-memory data path.
 //
 // Data movement.  Every warp runs its own ring of cp.async stages: per step a lane copies its
 // 2 x 16 B of codes and (two lanes of each quad) the 8 scale bytes of a row, a few steps ahead
