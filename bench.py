@@ -380,6 +380,11 @@ def secondary_numbers(dev) -> dict:
             rot = mx.quantize_packed(mx.apply_transform(w, "H128"), rotation="H128")[0].to_kernel_layout()
             t = timeit(lambda: mx.mixfp4_linear(x, rot), 8)
             out["gemm_tflops_m4096_q_4096x4096_h128_rotation"] = round(2.0 * 4096 * gn * gk / t / 1e12, 1)
+            # W4A4 in the reference's sense: rotation, activation fake-quantization and GEMM in one call
+            t = timeit(lambda: mx.mixfp4_linear(x, rot, activation_mode="oracle16"), 8)
+            out["gemm_tflops_m4096_q_4096x4096_h128_w4a4"] = round(2.0 * 4096 * gn * gk / t / 1e12, 1)
+            t = timeit(lambda: mx.fake_quantize_activations(x, "oracle16"), 8)
+            out["fake_quantize_gbs_4096x4096"] = round(4.0 * 4096 * gk / t / 1e9, 1)     # bf16 in + bf16 out
         del w, packed, x
     out["bf16_peak_tflops"] = peak_tf
     out["decode_tokens_per_s_linears_only"] = None   # filled by the caller from ms_per_step

@@ -108,6 +108,17 @@ MIXFP4_API int mixfp4_quantize(const void* x, int dtype, int64_t rows, int64_t k
                     float* e2_err, float* e0_err, float* e2_scale, float* e0_scale,
                     void* dequant, int64_t ld_dequant, void* stream);
 
+/* Fake-quantization of an activation tensor: y = dequantized mixed-FP4 form of x, in x's dtype
+ * (what the reference's forward-pre-hook feeds the linear in its W4A4 modes,
+ * project_quant/modeling.py:662-705: quant_mixfp4_granularity(x, operand_role="activation_a")
+ * with the global scale taken over the whole tensor of this call, scale.py:28-36).  One call =
+ * mixfp4_amax into *amax (device float[1] scratch, left holding max|x|) followed by the
+ * quantizer with no packed outputs.  mode: ORACLE16, ALL_E2M1 or ALL_E0M3 (coarse activation
+ * regions take the three-pass route: mixfp4_quantize, mixfp4_select_regions, mixfp4_quantize).
+ * y may be x itself (same pointer and row stride); any other overlap is not allowed. */
+MIXFP4_API int mixfp4_fake_quantize(const void* x, int dtype, int64_t rows, int64_t k, int64_t ldx, int mode,
+                         float* amax, void* y, int64_t ldy, void* stream);
+
 /* Coarse format regions (project_quant/region.py:42-86 region_shape / aggregate_regions and
  * selector.py:28-33 mse_selection): one format per region of region_rows x region_groups K16
  * blocks, E0M3 iff the region's summed E0M3 error is smaller (ties keep E2M1), summed in the
@@ -215,7 +226,7 @@ MIXFP4_API int mixfp4_gemv_allreduce(const mixfp4_comm* comm, const void* x, int
  * 128 or an x that TMA cannot address: MIXFP4_E_WORKSPACE without it) followed by room for
  * split-K partial sums (problems with few output tiles and a long K run several CTAs per tile;
  * optional: with a smaller or NULL workspace one CTA per tile does the whole K range, the result
- * then differs in fp32 summation order only).
+ * then differs in fp32 summation order only) and a 256-byte slot used by mixfp4_gemm_a4.
  * status: optional device int[1]; non-zero after completion if a bounded device-side
  * wait gave up (the output is then invalid). */
 MIXFP4_API int64_t mixfp4_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k);
@@ -223,6 +234,20 @@ MIXFP4_API int mixfp4_gemm(const void* x, int64_t m, int64_t ldx,
                 const uint8_t* codes, const uint8_t* scales, const uint8_t* fmt,
                 const float* global_scale, int64_t n, int64_t k, int layout, const void* lut,
                 int rotation_block, void* y, int out_dtype, int64_t ldy,
+                void* workspace, int64_t workspace_bytes, int* status, int flags, void* stream);
+
+/* W4A4 in the reference's sense: the activations are rotated (rotation_block 0 or 128; every
+ * butterfly stage rounded to bf16, which is what the reference's hook computes on a bf16 tensor,
+ * rotation.py:47-58), fake-quantized with mixfp4_fake_quantize(mode = act_mode) and then multiplied
+ * with the packed weight by mixfp4_gemm -- ActivationHooks._hook followed by nn.Linear.forward
+ * (modeling.py:662-705, :629).  The operand the tensor cores read is the reference's dequantized
+ * bf16 activation, bit for bit; an FP4 x FP4 MMA on the codes would not reproduce the bf16 rounding
+ * of either operand.  workspace: at least mixfp4_gemm_workspace_bytes(m, n, k) bytes, required
+ * (staging area, split-K partial sums, amax word).  Other arguments as mixfp4_gemm. */
+MIXFP4_API int mixfp4_gemm_a4(const void* x, int64_t m, int64_t ldx,
+                const uint8_t* codes, const uint8_t* scales, const uint8_t* fmt,
+                const float* global_scale, int64_t n, int64_t k, int layout, const void* lut,
+                int rotation_block, int act_mode, void* y, int out_dtype, int64_t ldy,
                 void* workspace, int64_t workspace_bytes, int* status, int flags, void* stream);
 
 /* Allocation-free form of the H128-rotated prefill linear.  No counterpart in the

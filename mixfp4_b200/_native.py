@@ -15,7 +15,7 @@ import torch
 from . import build as _build
 
 OK = 0
-E_SHAPE = -2
+E_NULL, E_SHAPE, E_ALIGN, E_DTYPE, E_MODE, E_CUDA, E_WORKSPACE = -1, -2, -3, -4, -5, -6, -7
 BF16, F16, F32 = 0, 1, 2
 MODE_ORACLE16, MODE_ALL_E2M1, MODE_ALL_E0M3, MODE_GIVEN = 0, 1, 2, 3
 LAYOUT_CANONICAL, LAYOUT_KERNEL = 0, 1
@@ -57,6 +57,8 @@ def _declare(h: ctypes.CDLL) -> None:
     h.mixfp4_amax.argtypes = [p, i32, i64, i64, i64, p, p]
     h.mixfp4_quantize.restype = i32
     h.mixfp4_quantize.argtypes = [p, i32, i64, i64, i64, i32, p, p, p, p, p, p, p, p, p, p, i64, p]
+    h.mixfp4_fake_quantize.restype = i32
+    h.mixfp4_fake_quantize.argtypes = [p, i32, i64, i64, i64, i32, p, p, i64, p]
     h.mixfp4_select_regions.restype = i32
     h.mixfp4_select_regions.argtypes = [p, p, i64, i64, i32, i32, p, p]
     h.mixfp4_selftest_division.restype = i32
@@ -90,6 +92,8 @@ def _declare(h: ctypes.CDLL) -> None:
     h.mixfp4_gemm_workspace_bytes.argtypes = [i64, i64, i64]
     h.mixfp4_gemm.restype = i32
     h.mixfp4_gemm.argtypes = [p, i64, i64, p, p, p, p, i64, i64, i32, p, i32, p, i32, i64, p, i64, p, i32, p]
+    h.mixfp4_gemm_a4.restype = i32
+    h.mixfp4_gemm_a4.argtypes = [p, i64, i64, p, p, p, p, i64, i64, i32, p, i32, i32, p, i32, i64, p, i64, p, i32, p]
     h.mixfp4_gemm_h128_static_max_bytes.restype = i64
     h.mixfp4_gemm_h128_static_max_bytes.argtypes = []
     h.mixfp4_gemm_h128_static.restype = i32
@@ -99,11 +103,11 @@ def _declare(h: ctypes.CDLL) -> None:
 # every symbol include/mixfp4_b200.h declares
 EXPORTED = (
     "mixfp4_abi_version", "mixfp4_status_string", "mixfp4_last_cuda_error", "mixfp4_padded_k",
-    "mixfp4_amax", "mixfp4_quantize", "mixfp4_select_regions", "mixfp4_selftest_division", "mixfp4_dequant", "mixfp4_repack", "mixfp4_decode_table", "mixfp4_fwht",
+    "mixfp4_amax", "mixfp4_quantize", "mixfp4_fake_quantize", "mixfp4_select_regions", "mixfp4_selftest_division", "mixfp4_dequant", "mixfp4_repack", "mixfp4_decode_table", "mixfp4_fwht",
     "mixfp4_gemv", "mixfp4_gemv_grouped",
     "mixfp4_comm_create", "mixfp4_comm_handle_bytes", "mixfp4_comm_handle", "mixfp4_comm_open", "mixfp4_comm_destroy",
     "mixfp4_gemv_allreduce",
-    "mixfp4_gemm_workspace_bytes", "mixfp4_gemm", "mixfp4_gemm_h128_static_max_bytes", "mixfp4_gemm_h128_static",
+    "mixfp4_gemm_workspace_bytes", "mixfp4_gemm", "mixfp4_gemm_a4", "mixfp4_gemm_h128_static_max_bytes", "mixfp4_gemm_h128_static",
 )
 
 

@@ -12,7 +12,7 @@ Checkpoint format (`torch.save` of plain tensors and python scalars, no code obj
     {"format": "mixfp4_b200.packed", "version": 1, "layers": {module name: {
         "codes": u8 [n, kpad/2], "scales": u8 [n, kpad/16], "fmt": u8 [n, kpad/128],
         "global_scale": f32 [1], "n": int, "k": int, "rotation": str | None, "mode": str,
-        "bias": tensor | None}}}
+        "activation_mode": str | None, "bias": tensor | None}}}
 The bytes are the canonical layout of include/mixfp4_b200.h (the one the parity tests hash);
 the kernel layout and the decode tables are rebuilt at load time.
 """
@@ -60,13 +60,17 @@ def _set_submodule(model: nn.Module, name: str, new: nn.Module) -> None:
 
 @torch.no_grad()
 def quantize_model_weights(model: nn.Module, weight_mode: str = "oracle16", *, rotation: str = "identity",
-                           per_module_rotation: dict[str, str] | None = None, device=None) -> list[dict[str, Any]]:
+                           per_module_rotation: dict[str, str] | None = None, device=None,
+                           activation_mode: str | None = None) -> list[dict[str, Any]]:
     """Replace every linear of ``model`` (heads excluded) by a packed MixFP4Linear, in place.
 
     weight_mode: a format region of `quant_mixfp4_granularity` ("oracle16", "n8k64", ...);
     "high_precision" / "fp16" / "bf16" leave the model untouched, as in the reference.
     rotation / per_module_rotation: name of a K-side transform ("H128", ...) folded into the
     weight before quantization; the layer then rotates its input with the same transform.
+    activation_mode: format region of the activation fake-quantization each converted layer
+    applies to its (rotated) input, as the reference's ActivationHooks do (modeling.py:640-705);
+    None / "bf16" leaves the activations in bf16.
     Returns one row per converted layer (name, type, layer index, shape, share of E0M3 blocks,
     packed bytes)."""
     if weight_mode in {"high_precision", "fp16", "bf16"}:
@@ -75,7 +79,8 @@ def quantize_model_weights(model: nn.Module, weight_mode: str = "oracle16", *, r
     for name, linear in list(named_linears(model)):
         chosen = per_module_rotation.get(name, rotation) if per_module_rotation else rotation
         chosen = None if chosen in (None, "identity") else chosen
-        layer = MixFP4Linear.from_linear(linear, rotation=chosen, mode=weight_mode, device=device)
+        layer = MixFP4Linear.from_linear(linear, rotation=chosen, mode=weight_mode, device=device,
+                                         activation_mode=activation_mode)
         layer.weight_mode = weight_mode
         _set_submodule(model, name, layer)
         scales = layer.scales[:, : (layer.in_features + 15) // 16]
@@ -99,6 +104,7 @@ def packed_state(model: nn.Module) -> dict[str, Any]:
                 "codes": p.codes.cpu(), "scales": p.scales.cpu(), "fmt": p.fmt.cpu(),
                 "global_scale": p.global_scale.cpu(), "n": p.n, "k": p.k, "rotation": p.rotation,
                 "mode": getattr(module, "weight_mode", "oracle16"),
+                "activation_mode": module.activation_mode,
                 "bias": None if module.bias is None else module.bias.detach().cpu(),
             }
     return {"format": FORMAT_NAME, "version": FORMAT_VERSION, "layers": layers}
@@ -132,7 +138,7 @@ def load_packed(model: nn.Module, path_or_state, *, device=None, strict: bool = 
         packed = PackedWeight(entry["codes"].to(device), entry["scales"].to(device), entry["fmt"].to(device),
                               entry["global_scale"].to(device), entry["n"], entry["k"], entry["rotation"])
         bias = None if entry["bias"] is None else entry["bias"].to(device)
-        layer = MixFP4Linear(packed, bias)
+        layer = MixFP4Linear(packed, bias, entry.get("activation_mode"))
         layer.weight_mode = entry.get("mode", "oracle16")
         _set_submodule(model, name, layer)
         done.append(name)

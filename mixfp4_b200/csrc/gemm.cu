@@ -899,6 +899,7 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 int64_t x_staging_bytes(int64_t m, int64_t k) { return m * ((k + 7) / 8 * 8) * 2; }
+constexpr int64_t kAmaxSlotBytes = 256;
 
 template <int kMT, int kBN, bool kKL>
 int launch_gemm(const void* xa, int64_t lda, const GemmArgs& a, cudaStream_t st) {
@@ -1039,7 +1040,7 @@ extern "C" int64_t mixfp4_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k) 
         const GemmPlan p = plan_gemm(m, n, k);
         if (p.splits > 1) bytes += (int64_t)p.splits * m * partial_ld(n) * 4;
     }
-    return bytes;
+    return bytes + kAmaxSlotBytes;      // last: the activation amax word of mixfp4_gemm_a4
 }
 
 extern "C" int mixfp4_gemm(const void* x, int64_t m, int64_t ldx, const uint8_t* codes, const uint8_t* scales,
@@ -1105,6 +1106,35 @@ extern "C" int mixfp4_gemm(const void* x, int64_t m, int64_t ldx, const uint8_t*
     if (mt == 1 && bn == 256) return kl ? launch_gemm<1, 256, true>(xa, lda, a, st) : launch_gemm<1, 256, false>(xa, lda, a, st);
     if (mt == 2 && bn == 128) return kl ? launch_gemm<2, 128, true>(xa, lda, a, st) : launch_gemm<2, 128, false>(xa, lda, a, st);
     return kl ? launch_gemm<2, 256, true>(xa, lda, a, st) : launch_gemm<2, 256, false>(xa, lda, a, st);
+}
+
+extern "C" int mixfp4_gemm_a4(const void* x, int64_t m, int64_t ldx, const uint8_t* codes, const uint8_t* scales,
+                              const uint8_t* fmt, const float* global_scale, int64_t n, int64_t k, int layout,
+                              const void* lut, int rotation_block, int act_mode, void* y, int out_dtype, int64_t ldy,
+                              void* workspace, int64_t workspace_bytes, int* status, int flags, void* stream) {
+    if (!x || !codes || !scales || !global_scale || !y) return MIXFP4_E_NULL;
+    if (m <= 0 || n <= 0 || k <= 0 || ldx < k || ldy < n) return MIXFP4_E_SHAPE;
+    if (m > 0x7fffffffLL || n > 0x7fffffffLL || k > 0x7fffffffLL) return MIXFP4_E_SHAPE;
+    if (rotation_block != 0 && rotation_block != 128) return MIXFP4_E_MODE;
+    const int64_t total = mixfp4_gemm_workspace_bytes(m, n, k);
+    if (!workspace || workspace_bytes < total) return MIXFP4_E_WORKSPACE;
+    if (!aligned(workspace, 16)) return MIXFP4_E_ALIGN;
+    // staging area: the rotated (every stage rounded to bf16, as the reference's hook computes it on
+    // a bf16 tensor), then fake-quantized activations; the amax word sits in the workspace's last slot
+    const int64_t lda = (k + 7) / 8 * 8;
+    float* amax = reinterpret_cast<float*>(static_cast<char*>(workspace) + total - kAmaxSlotBytes);
+    const void* src = x;
+    int64_t lds = ldx;
+    if (rotation_block == 128) {
+        const int rc = mixfp4_fwht(x, workspace, MIXFP4_BF16, m, k, ldx, lda, 128, nullptr, 1, stream);
+        if (rc != MIXFP4_OK) return rc;
+        src = workspace;
+        lds = lda;
+    }
+    const int rc = mixfp4_fake_quantize(src, MIXFP4_BF16, m, k, lds, act_mode, amax, workspace, lda, stream);
+    if (rc != MIXFP4_OK) return rc;
+    return mixfp4_gemm(workspace, m, lda, codes, scales, fmt, global_scale, n, k, layout, lut, 0, y, out_dtype, ldy,
+                       workspace, total - kAmaxSlotBytes, status, flags, stream);
 }
 
 

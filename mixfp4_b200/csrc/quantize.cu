@@ -75,6 +75,7 @@ struct QuantArgs {
     int64_t chunks;       // ceil(blocks_pad / 32): warps per row
     int mode;
     bool vec_in, vec_out;
+    bool in_place;        // dequant aliases x: the input is read with ordinary (coherent) loads
     const float* amax;
     uint8_t* codes;
     uint8_t* scales;
@@ -209,7 +210,7 @@ __global__ void __launch_bounds__(kThreads) quantize_kernel(const QuantArgs a) {
     const bool stored = blk < a.blocks_pad;
     const bool real = blk < a.groups;
 
-    if (warp == 0 && lane == 0) *a.global_scale = gs;
+    if (warp == 0 && lane == 0 && a.global_scale) *a.global_scale = gs;
 
     uint32_t lo = 0, hi = 0, scale_byte = 0x01;    // what an all-zero block quantizes to
     bool use_e0 = false;
@@ -222,7 +223,10 @@ __global__ void __launch_bounds__(kThreads) quantize_kernel(const QuantArgs a) {
             constexpr int kWords = kGroup * sizeof(T) / 16;
             uint4 w[kWords];
 #pragma unroll
-            for (int j = 0; j < kWords; ++j) w[j] = __ldg(reinterpret_cast<const uint4*>(xr + c0) + j);
+            for (int j = 0; j < kWords; ++j) {
+                const uint4* src = reinterpret_cast<const uint4*>(xr + c0) + j;
+                w[j] = a.in_place ? *src : __ldg(src);
+            }
             const T* e = reinterpret_cast<const T*>(w);
 #pragma unroll
             for (int i = 0; i < kGroup; ++i) x[i] = Elem<T>::load(e + i);
@@ -291,6 +295,7 @@ __global__ void __launch_bounds__(kThreads) quantize_kernel(const QuantArgs a) {
         }
     }
 
+    if (!a.codes) return;                          // fake-quantization only: no packed outputs
     if (stored) {
         const int64_t ld_codes = a.blocks_pad * 8, ld_scales = a.blocks_pad;
         *reinterpret_cast<uint2*>(a.codes + row * ld_codes + blk * 8) = make_uint2(lo, hi);
@@ -469,6 +474,36 @@ __global__ void __launch_bounds__(kThreads) select_regions_kernel(const float* _
     for (int r = 0; r < region_rows && r0 + r < rows; ++r) fmt[(r0 + r) * fmt_cols + col] = static_cast<uint8_t>(byte);
 }
 
+namespace mixfp4 {
+namespace {
+int launch_quantize(const void* x, int dtype, int64_t rows, int64_t k, int64_t ldx, int mode, const float* amax,
+                    uint8_t* codes, uint8_t* scales, uint8_t* fmt, float* global_scale, float* e2_err, float* e0_err,
+                    float* e2_scale, float* e0_scale, void* dequant, int64_t ld_dequant, cudaStream_t st) {
+    QuantArgs a;
+    a.x = x; a.rows = rows; a.k = k; a.ldx = ldx;
+    a.groups = (k + kGroup - 1) / kGroup;
+    a.blocks_pad = padded_k(k) / kGroup;
+    a.chunks = (a.blocks_pad + 31) / 32;
+    a.mode = mode;
+    a.vec_in = rows_vectorizable(x, ldx, dtype);
+    a.vec_out = dequant && rows_vectorizable(dequant, ld_dequant, dtype);
+    a.in_place = dequant == x;
+    a.amax = amax; a.codes = codes; a.scales = scales; a.fmt = fmt; a.global_scale = global_scale;
+    a.e2_err = e2_err; a.e0_err = e0_err; a.e2_scale = e2_scale; a.e0_scale = e0_scale;
+    a.dequant = dequant; a.ld_dequant = ld_dequant;
+    const int64_t warps = rows * a.chunks;
+    const int64_t ctas = (warps + kWarpsPerCta - 1) / kWarpsPerCta;
+    if (ctas > 0x7fffffffLL) return MIXFP4_E_SHAPE;
+    switch (dtype) {
+        case MIXFP4_BF16: quantize_kernel<__nv_bfloat16><<<(unsigned)ctas, kThreads, 0, st>>>(a); break;
+        case MIXFP4_F16: quantize_kernel<__half><<<(unsigned)ctas, kThreads, 0, st>>>(a); break;
+        default: quantize_kernel<float><<<(unsigned)ctas, kThreads, 0, st>>>(a);
+    }
+    return check_launch("quantize_kernel");
+}
+}  // namespace
+}  // namespace mixfp4
+
 extern "C" int mixfp4_quantize(const void* x, int dtype, int64_t rows, int64_t k, int64_t ldx, int mode,
                                const float* amax, uint8_t* codes, uint8_t* scales, uint8_t* fmt,
                                float* global_scale, float* e2_err, float* e0_err, float* e2_scale,
@@ -478,27 +513,22 @@ extern "C" int mixfp4_quantize(const void* x, int dtype, int64_t rows, int64_t k
     if (dtype < MIXFP4_BF16 || dtype > MIXFP4_F32) return MIXFP4_E_DTYPE;
     if (mode < MIXFP4_MODE_ORACLE16 || mode > MIXFP4_MODE_GIVEN) return MIXFP4_E_MODE;
     if (!aligned(codes, 8)) return MIXFP4_E_ALIGN;
-    QuantArgs a;
-    a.x = x; a.rows = rows; a.k = k; a.ldx = ldx;
-    a.groups = (k + kGroup - 1) / kGroup;
-    a.blocks_pad = padded_k(k) / kGroup;
-    a.chunks = (a.blocks_pad + 31) / 32;
-    a.mode = mode;
-    a.vec_in = rows_vectorizable(x, ldx, dtype);
-    a.vec_out = dequant && rows_vectorizable(dequant, ld_dequant, dtype);
-    a.amax = amax; a.codes = codes; a.scales = scales; a.fmt = fmt; a.global_scale = global_scale;
-    a.e2_err = e2_err; a.e0_err = e0_err; a.e2_scale = e2_scale; a.e0_scale = e0_scale;
-    a.dequant = dequant; a.ld_dequant = ld_dequant;
-    const int64_t warps = rows * a.chunks;
-    const int64_t ctas = (warps + kWarpsPerCta - 1) / kWarpsPerCta;
-    if (ctas > 0x7fffffffLL) return MIXFP4_E_SHAPE;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    switch (dtype) {
-        case MIXFP4_BF16: quantize_kernel<__nv_bfloat16><<<(unsigned)ctas, kThreads, 0, st>>>(a); break;
-        case MIXFP4_F16: quantize_kernel<__half><<<(unsigned)ctas, kThreads, 0, st>>>(a); break;
-        default: quantize_kernel<float><<<(unsigned)ctas, kThreads, 0, st>>>(a);
-    }
-    return check_launch("quantize_kernel");
+    return launch_quantize(x, dtype, rows, k, ldx, mode, amax, codes, scales, fmt, global_scale, e2_err, e0_err,
+                           e2_scale, e0_scale, dequant, ld_dequant, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int mixfp4_fake_quantize(const void* x, int dtype, int64_t rows, int64_t k, int64_t ldx, int mode,
+                                    float* amax, void* y, int64_t ldy, void* stream) {
+    if (!x || !amax || !y) return MIXFP4_E_NULL;
+    if (rows <= 0 || k <= 0 || ldx < k || ldy < k) return MIXFP4_E_SHAPE;
+    if (dtype < MIXFP4_BF16 || dtype > MIXFP4_F32) return MIXFP4_E_DTYPE;
+    if (mode < MIXFP4_MODE_ORACLE16 || mode > MIXFP4_MODE_ALL_E0M3) return MIXFP4_E_MODE;
+    // in place is allowed when the two views coincide exactly; any other overlap is not
+    if (y == x && ldy != ldx) return MIXFP4_E_SHAPE;
+    const int rc = mixfp4_amax(x, dtype, rows, k, ldx, amax, stream);
+    if (rc != MIXFP4_OK) return rc;
+    return launch_quantize(x, dtype, rows, k, ldx, mode, amax, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
+                           nullptr, nullptr, y, ldy, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int mixfp4_dequant(const uint8_t* codes, const uint8_t* scales, const uint8_t* fmt,

@@ -15,7 +15,8 @@ from torch import nn
 
 from . import _native as nat
 from . import rotation as _rotation
-from .quant import PackedWeight, quantize_packed
+from .quant import (HIGH_PRECISION_MODES, PackedWeight, _MODE_CODE, fake_quantize_activations, normalize_region,
+                    quantize_packed, region_shape)
 
 GEMV_MAX_M = 16
 _workspaces: dict[tuple, torch.Tensor] = {}
@@ -49,8 +50,15 @@ def gemm_status(device=None) -> int:
 
 def mixfp4_linear(x: torch.Tensor, packed: PackedWeight, *, bias: torch.Tensor | None = None,
                   rotate: bool | None = None, out_dtype: torch.dtype | None = None,
-                  overlap_previous: bool = False) -> torch.Tensor:
+                  overlap_previous: bool = False, activation_mode: str | None = None) -> torch.Tensor:
     """y = x @ W^T (+ bias) with W packed; x bf16 [..., K] on the GPU.
+
+    activation_mode: None / "bf16" keeps x as it is (W4A16).  A format region ("oracle16",
+    "all_e2m1", "m8k64", ...) makes this the reference's W4A4 forward (ActivationHooks._hook,
+    project_quant/modeling.py:662-705): x is rotated with every stage rounded to bf16 (what the
+    hook's apply_transform computes on a bf16 tensor), fake-quantized with its own global scale,
+    and the dequantized bf16 tensor goes into the same kernels.  Prefill shapes with a per-block
+    or whole-tensor mode run as one ``mixfp4_gemm_a4`` call.
 
     rotate: apply the weight's folded K-transform to x first (default: yes when the packed
     weight records one).  H128 is fused into the GEMM prologue; the GEMV path and other
@@ -86,6 +94,31 @@ def mixfp4_linear(x: torch.Tensor, packed: PackedWeight, *, bias: torch.Tensor |
     if m == 0:
         return y.reshape(*lead, packed.n)
     lib = nat.lib()
+    act = None
+    if activation_mode is not None:
+        act = normalize_region(activation_mode, "activation_a")
+        act = None if act in HIGH_PRECISION_MODES else act
+    if act is not None:
+        fusable = (m > GEMV_MAX_M and region_shape(act, "activation_a") is None
+                   and (spec is None or (spec.block_size == 128 and spec.seed is None)))
+        if fusable:
+            nbytes = lib.mixfp4_gemm_workspace_bytes(m, packed.n, packed.k)
+            ws = _workspace(x.device, nbytes)
+            with torch.cuda.device(x.device):
+                st = lib.mixfp4_gemm_a4(x2.data_ptr(), m, x2.stride(0), packed.codes.data_ptr(), packed.scales.data_ptr(),
+                                        nat.ptr(packed.fmt), packed.global_scale.data_ptr(), packed.n, packed.k,
+                                        packed.layout_code, nat.ptr(packed.lut), 128 if spec is not None else 0,
+                                        _MODE_CODE[act], y.data_ptr(), nat.DTYPE_CODE[out_dtype], y.stride(0),
+                                        nat.ptr(ws), nbytes, _status_word(x.device).data_ptr(), 0,
+                                        nat.stream_ptr(x.device))
+            nat.check("mixfp4_gemm_a4", st)
+            if bias is not None:
+                y += bias.to(y.dtype)
+            return y.reshape(*lead, packed.n)
+        if spec is not None:
+            x2 = _rotation.apply_transform(x2, spec, rounding="reference")
+            spec = None
+        x2 = fake_quantize_activations(x2, act)
     with torch.cuda.device(x.device):
         stream = nat.stream_ptr(x.device)
         if m <= GEMV_MAX_M:
@@ -158,9 +191,10 @@ def mixfp4_linear_grouped(x: torch.Tensor, packs: list[PackedWeight], *, out_dty
 class MixFP4Linear(nn.Module):
     """nn.Linear whose weight lives in the packed mixed-FP4 layout."""
 
-    def __init__(self, packed: PackedWeight, bias: torch.Tensor | None = None):
+    def __init__(self, packed: PackedWeight, bias: torch.Tensor | None = None, activation_mode: str | None = None):
         super().__init__()
         self.in_features, self.out_features = packed.k, packed.n
+        self.activation_mode = activation_mode      # None: W4A16; a format region: the reference's W4A4 forward
         packed = packed.to_kernel_layout()          # the layers keep the layout the kernels decode fastest
         self.rotation = packed.rotation
         self.register_buffer("codes", packed.codes)
@@ -177,7 +211,7 @@ class MixFP4Linear(nn.Module):
     @classmethod
     @torch.no_grad()
     def from_linear(cls, linear: nn.Linear, *, rotation: str | None = None, mode: str = "oracle16",
-                    device=None) -> "MixFP4Linear":
+                    device=None, activation_mode: str | None = None) -> "MixFP4Linear":
         """Quantize ``linear.weight`` (optionally rotated along K first, as the reference's
         apply_rotations does offline, modeling.py:323-344) and wrap it."""
         device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
@@ -188,11 +222,13 @@ class MixFP4Linear(nn.Module):
             w = _rotation.apply_transform(w, rotation)
         packed, _, _ = quantize_packed(w, mode=mode, rotation=rotation)
         bias = None if linear.bias is None else linear.bias.detach().to(device)
-        return cls(packed, bias)
+        return cls(packed, bias, activation_mode)
 
     def forward(self, x: torch.Tensor, out_dtype: torch.dtype | None = None,
                 overlap_previous: bool = False) -> torch.Tensor:
-        return mixfp4_linear(x, self.packed, bias=self.bias, out_dtype=out_dtype, overlap_previous=overlap_previous)
+        return mixfp4_linear(x, self.packed, bias=self.bias, out_dtype=out_dtype, overlap_previous=overlap_previous,
+                             activation_mode=self.activation_mode)
 
     def extra_repr(self) -> str:
-        return f"in_features={self.in_features}, out_features={self.out_features}, rotation={self.rotation}"
+        return (f"in_features={self.in_features}, out_features={self.out_features}, rotation={self.rotation}, "
+                f"activation_mode={self.activation_mode}")

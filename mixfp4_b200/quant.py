@@ -296,6 +296,43 @@ def quantize_packed(x: torch.Tensor, *, mode: str = "oracle16", amax: torch.Tens
     return PackedWeight(codes, scales, fmt, gs, rows, k, rotation), dq, stats
 
 
+HIGH_PRECISION_MODES = ("high_precision", "fp16", "bf16")
+
+
+@torch.no_grad()
+def fake_quantize_activations(x: torch.Tensor, mode: str = "oracle16", *, in_place: bool = False) -> torch.Tensor:
+    """The tensor the reference's forward-pre-hook hands to a linear in its W4A4 modes
+    (project_quant/modeling.py:669-705): ``quant_mixfp4_granularity(x, format_region=mode,
+    operand_role="activation_a")`` -- x's own global scale, K16 block scales, one format per
+    block or per activation region (m4k64 ...), dequantized back to x.dtype.  x: CUDA tensor
+    [..., K].  Per-block and whole-tensor modes run as one amax and one quantizer launch with
+    no packed outputs (``mixfp4_fake_quantize``); region modes take the three-pass route.
+    in_place=True overwrites x (it must then be contiguous along K with a dense row stride)."""
+    mode = normalize_region(mode, "activation_a")
+    if mode in HIGH_PRECISION_MODES:
+        return x
+    region = region_shape(mode, "activation_a")
+    x2 = _as_rows(x)
+    if region is not None:
+        dq = quantize_packed(x2, mode=mode, want_dequant=True, region=region)[1]
+        if in_place:
+            x.copy_(dq.reshape(x.shape))
+            return x
+        return dq.reshape(x.shape)
+    aliases_input = x2.data_ptr() == x.data_ptr() and x2.stride(-1) == 1
+    out = x2 if in_place and aliases_input else torch.empty_like(x2, memory_format=torch.contiguous_format)
+    amax = torch.empty(1, dtype=torch.float32, device=x2.device)
+    with torch.cuda.device(x2.device):
+        st = nat.lib().mixfp4_fake_quantize(x2.data_ptr(), nat.DTYPE_CODE[x2.dtype], x2.shape[0], x2.shape[1],
+                                            x2.stride(0), _MODE_CODE[mode], amax.data_ptr(), out.data_ptr(),
+                                            out.stride(0), nat.stream_ptr(x2.device))
+    nat.check("mixfp4_fake_quantize", st)
+    if in_place and not aliases_input:
+        x.copy_(out.reshape(x.shape))
+        return x
+    return out.reshape(x.shape)
+
+
 def dequantize(packed: PackedWeight, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
     """Dense [n, k] tensor with exactly the values the reference's dequantized weight holds."""
     if dtype not in nat.DTYPE_CODE:

@@ -68,6 +68,17 @@ def test_c_abi_argument_validation_needs_no_gpu():
     assert h.mixfp4_select_regions(one, one, 0, 64, 1, 4, one, None) == -2
     bad = list(args); bad[5] = 4
     assert h.mixfp4_quantize(*bad) == -5          # modes are 0..3
+    assert h.mixfp4_fake_quantize(one, nat.BF16, 4, 64, 64, 0, one, None, 64, None) == -1
+    assert h.mixfp4_fake_quantize(one, nat.BF16, 4, 64, 64, 0, one, one, 32, None) == -2      # ldy < k
+    assert h.mixfp4_fake_quantize(one, nat.BF16, 4, 64, 64, 3, one, one, 64, None) == -5      # no format bits to be given
+    assert h.mixfp4_fake_quantize(one, nat.BF16, 4, 64, 96, 0, one, one, 64, None) == -2      # in place needs equal strides
+    a4 = [one, 64, 64, one, one, one, one, 64, 64, 0, None, 0, 0, one, nat.F32, 64, None, 0, None, 0, None]
+    assert h.mixfp4_gemm_a4(*a4) == -7                                                          # workspace is required
+    bad = list(a4); bad[11] = 64
+    assert h.mixfp4_gemm_a4(*bad) == -5                                                         # rotation 0 or 128
+    bad = list(a4); bad[0] = None
+    assert h.mixfp4_gemm_a4(*bad) == -1
+    assert h.mixfp4_gemm_workspace_bytes(64, 64, 64) >= 64 * 64 * 2 + 4
     assert h.mixfp4_repack(one, one, None, 4, 64, 1, one, one, None, None) == -1
     assert h.mixfp4_decode_table(None, one, None) == -1
     assert h.mixfp4_status_string(-3).decode().startswith("pointer or stride")
@@ -147,3 +158,16 @@ def test_model_walk_helpers_follow_the_reference_rules():
     assert convert.quantize_model_weights(Net(), "fp16") == []          # high-precision modes convert nothing
     with pytest.raises(ValueError, match="packed checkpoint"):
         convert.load_packed(Net(), {"format": "something else", "version": 1, "layers": {}})
+
+
+def test_activation_modes_follow_the_reference_tables():
+    import torch
+    from mixfp4_b200 import quant
+    x = torch.zeros(4, 64, dtype=torch.bfloat16)
+    for mode in ("bf16", "fp16", "high_precision"):
+        assert quant.fake_quantize_activations(x, mode) is x          # the hook leaves these alone (modeling.py:669)
+    with pytest.raises(ValueError):
+        quant.fake_quantize_activations(x, "n8k64")                   # a weight region (region.py:42-70)
+    with pytest.raises(NotImplementedError):
+        quant.fake_quantize_activations(x, "m16k16")
+    assert quant.region_shape("m8k64", "activation_a") == (8, 4)
