@@ -37,13 +37,23 @@ __global__ void __launch_bounds__(kThreads) amax_kernel(const T* __restrict__ x,
         constexpr int kPer = 16 / sizeof(T);
         const int64_t words_per_row = k / kPer;
         const int64_t total = rows * words_per_row;
-        for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
-             i += (int64_t)gridDim.x * blockDim.x) {
-            const int64_t r = i / words_per_row, w = i - r * words_per_row;
-            const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + r * ldx) + w);
-            const T* e = reinterpret_cast<const T*>(&v);
+        // four independent 16-byte loads in flight per thread and trip
+        const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+        for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += 4 * stride) {
+            uint4 v[4];
 #pragma unroll
-            for (int j = 0; j < kPer; ++j) m = fmaxf(m, fabsf(Elem<T>::load(e + j)));
+            for (int u = 0; u < 4; ++u) {
+                const int64_t iu = i + u * stride;
+                const uint4* src = reinterpret_cast<const uint4*>(x) + iu;         // dense rows: one flat array
+                if (ldx != k) {
+                    const int64_t r = iu / words_per_row, w = iu - r * words_per_row;
+                    src = reinterpret_cast<const uint4*>(x + r * ldx) + w;
+                }
+                v[u] = iu < total ? __ldg(src) : make_uint4(0u, 0u, 0u, 0u);
+            }
+            const T* e = reinterpret_cast<const T*>(v);
+#pragma unroll
+            for (int j = 0; j < 4 * kPer; ++j) m = fmaxf(m, fabsf(Elem<T>::load(e + j)));
         }
     } else {
         const int64_t total = rows * k;
@@ -112,26 +122,34 @@ __device__ __forceinline__ float div_exact(float a, float b, float r) {
 
 // E2M1 rounding of |n| exactly as codebook.py:12-25 computes it: exponent floor(log2 |n|)
 // clamped at 0, floor(mantissa * 2 + 0.5), saturate at 6.  For |n| >= 1 that is round-half-up
-// to one mantissa bit, done on the bit pattern (the level index is then the float's exponent
-// and top mantissa bit: index = (bits >> 22) - 252); below 1 the grid is {0, 0.5, 1} with
+// to one mantissa bit, done on the bit pattern; below 1 the grid is {0, 0.5, 1} with
 // thresholds 0.75 and -- because the reference adds 0.5 in fp32 -- the float just below 0.25.
-__device__ __forceinline__ void e2m1_quantize(float mag, float& q, uint32_t& idx) {
+// Returns the level value.
+__device__ __forceinline__ float e2m1_round(float mag) {
     const uint32_t b = __float_as_uint(mag);
     const uint32_t rb = (b + 0x00200000u) & 0xffc00000u;               // |n| >= 1
-    const uint32_t lo_idx = (b >= 0x3f400000u ? 1u : 0u) + (b >= 0x3e7fffffu ? 1u : 0u);   // |n| < 1
-    const bool big = b >= 0x3f800000u;
-    q = big ? fminf(__uint_as_float(rb), 6.0f) : 0.5f * static_cast<float>(lo_idx);
-    idx = big ? min((rb >> 22) - 252u, 7u) : lo_idx;
+    const float q_big = fminf(__uint_as_float(rb), 6.0f);
+    const float q_small = b >= 0x3f400000u ? 1.0f : (b >= 0x3e7fffffu ? 0.5f : 0.0f);
+    return b >= 0x3f800000u ? q_big : q_small;
+}
+// The 3-bit code of an E2M1 level, left in bits 22..24: scaled by 2^-126 the level's fp32 bit
+// pattern is the E2M1 encoding itself (0.5 becomes the subnormal with only the top mantissa bit,
+// 1 the smallest normal, ...), and nothing else is set.
+__device__ __forceinline__ uint32_t e2m1_code_at_22(float q) {
+    return __float_as_uint(__fmul_rn(q, 1.1754943508222875e-38f));
 }
 
-// E0M3 rounding of |n|: round-half-even then saturate at 7 (codebook.py:41-43); |n| < 2^22.
-__device__ __forceinline__ void e0m3_quantize(float mag, float& q, uint32_t& idx) {
-    const float t = __fadd_rn(mag, 8388608.0f);           // the sum's low mantissa bits are RNE(mag)
-    q = fminf(__fsub_rn(t, 8388608.0f), 7.0f);
-    idx = min(__float_as_uint(t) & 0x3fffffu, 7u);
+// E0M3 rounding of |n|: round-half-even then saturate at 7 (codebook.py:41-43).  Clamping at 7.25
+// first changes nothing (everything above rounds to 7 or saturates) and keeps the sum's low
+// mantissa bits equal to the level: t = 2^23 + level.
+__device__ __forceinline__ float e0m3_round(float mag) {
+    const float t = __fadd_rn(fminf(mag, 7.25f), 8388608.0f);
+    return __fsub_rn(t, 8388608.0f);
 }
-
-template <bool kE0, bool kFast>
+// One candidate format of one block.  ax = |x|, s = x / gs.  Produces the block's scale, its
+// squared error in the reference's summation order, the magnitudes of the dequantized values
+// (kKeep) and the eight-per-word 3-bit level codes without signs (kPack).
+template <bool kE0, bool kFast, bool kPack, bool kKeep>
 __device__ __forceinline__ void candidate(const float (&ax)[kGroup], const float (&s)[kGroup], float amax_s,
                                           float gs, uint32_t& lo, uint32_t& hi, uint32_t& scale_byte,
                                           float& scale_val, float& err, float (&dmag)[kGroup]) {
@@ -142,22 +160,27 @@ __device__ __forceinline__ void candidate(const float (&ax)[kGroup], const float
     const float rsc = __frcp_rn(sc);
     scale_val = sc;
     float sq[kGroup];
+    float p4[4] = {0.0f, 0.0f, 0.0f, 0.0f};         // E0M3: four levels per float, 16^j weights (exact)
     lo = 0;
     hi = 0;
 #pragma unroll
     for (int i = 0; i < kGroup; ++i) {
-        const float n = div_exact<kFast>(s[i], sc, rsc);
-        const float mag = fabsf(n);
-        float q;
-        uint32_t idx;
-        if constexpr (kE0) e0m3_quantize(mag, q, idx);
-        else e2m1_quantize(mag, q, idx);
-        const uint32_t nib = idx | (n < 0.0f ? 8u : 0u);
-        if (i < 8) lo |= nib << (4 * i);
-        else hi |= nib << (4 * (i - 8));
+        const float mag = fabsf(div_exact<kFast>(s[i], sc, rsc));
+        const float q = kE0 ? e0m3_round(mag) : e2m1_round(mag);
+        if constexpr (kPack && kE0) {
+            const float weight = (i & 3) == 0 ? 1.0f : (i & 3) == 1 ? 16.0f : (i & 3) == 2 ? 256.0f : 4096.0f;
+            p4[i >> 2] = (i & 3) == 0 ? q : __fmaf_rn(q, weight, p4[i >> 2]);
+        }
+        if constexpr (kPack && !kE0) {
+            const uint32_t c = e2m1_code_at_22(q);
+            const int j = i & 7;                                       // constants once unrolled
+            const int right = 22 - 4 * j > 0 ? 22 - 4 * j : 0, left = 4 * j - 22 > 0 ? 4 * j - 22 : 0;
+            if (i < 8) lo |= (c >> right) << left;
+            else hi |= (c >> right) << left;
+        }
         // (d - x)^2 == (|d| - |x|)^2 bit for bit: d and x never have opposite signs
         const float d = __fmul_rn(__fmul_rn(q, sc), gs);
-        dmag[i] = d;
+        if constexpr (kKeep) dmag[i] = d;
         const float e = __fsub_rn(d, ax[i]);
         sq[i] = __fmul_rn(e, e);
     }
@@ -165,6 +188,11 @@ __device__ __forceinline__ void candidate(const float (&ax)[kGroup], const float
 #pragma unroll
     for (int j = 1; j < 8; ++j) acc = __fadd_rn(acc, __fadd_rn(sq[j], sq[j + 8]));
     err = acc;
+    if constexpr (kPack && kE0) {
+        // 2^23 + p has p in its low mantissa bits; the low halves of two such words make one code word
+        lo = __byte_perm(__float_as_uint(__fadd_rn(p4[0], 8388608.0f)), __float_as_uint(__fadd_rn(p4[1], 8388608.0f)), 0x5410);
+        hi = __byte_perm(__float_as_uint(__fadd_rn(p4[2], 8388608.0f)), __float_as_uint(__fadd_rn(p4[3], 8388608.0f)), 0x5410);
+    }
 }
 
 // Exhaustive check of div_rcp against IEEE division: all 2^23 significands of the dividend
@@ -183,11 +211,12 @@ __global__ void selftest_division_kernel(unsigned long long* mismatches) {
     if (bad) atomicAdd(mismatches, bad);
 }
 
-template <typename T>
-__global__ void __launch_bounds__(kThreads) quantize_kernel(const QuantArgs a) {
+// kPack: write codes / scales / format bits; kDequant: write the dequantized tensor.  Each warp
+// walks over (row, 32-block chunk) items with the grid's stride.
+template <typename T, bool kPack, bool kDequant>
+__global__ void __launch_bounds__(kThreads, 3) quantize_kernel(const QuantArgs a) {
     const int lane = threadIdx.x & 31;
-    const int64_t warp = (int64_t)blockIdx.x * kWarpsPerCta + __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);   // provably warp-uniform
-    const int64_t row = warp / a.chunks;
+    const int warp_in_cta = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);   // provably warp-uniform
     const float amax = *a.amax;
     const float gs = amax > 0.0f ? __fdiv_rn(amax, 2688.0f) : 1.0f;
     const float rgs = __frcp_rn(gs);
@@ -204,110 +233,124 @@ __global__ void __launch_bounds__(kThreads) quantize_kernel(const QuantArgs a) {
         }
         fast = __syncthreads_and(ok) && fast;
     }
-    if (row >= a.rows) return;                     // whole warp leaves together
-    const int64_t chunk = warp - row * a.chunks;
-    const int64_t blk = chunk * 32 + lane;         // block index inside the row
-    const bool stored = blk < a.blocks_pad;
-    const bool real = blk < a.groups;
+    if (blockIdx.x == 0 && threadIdx.x == 0 && a.global_scale) *a.global_scale = gs;
 
-    if (warp == 0 && lane == 0 && a.global_scale) *a.global_scale = gs;
+    const int64_t items = a.rows * a.chunks;
+    for (int64_t item = (int64_t)blockIdx.x * kWarpsPerCta + warp_in_cta; item < items;
+         item += (int64_t)gridDim.x * kWarpsPerCta) {
+        const int64_t row = item / a.chunks;
+        const int64_t chunk = item - row * a.chunks;
+        const int64_t blk = chunk * 32 + lane;         // block index inside the row
+        const bool stored = blk < a.blocks_pad;
+        const bool real = blk < a.groups;
 
-    uint32_t lo = 0, hi = 0, scale_byte = 0x01;    // what an all-zero block quantizes to
-    bool use_e0 = false;
-
-    if (real) {
-        const T* xr = static_cast<const T*>(a.x) + row * a.ldx;
-        const int64_t c0 = blk * kGroup;
-        float x[kGroup];
-        if (a.vec_in && c0 + kGroup <= a.k) {
-            constexpr int kWords = kGroup * sizeof(T) / 16;
-            uint4 w[kWords];
-#pragma unroll
-            for (int j = 0; j < kWords; ++j) {
-                const uint4* src = reinterpret_cast<const uint4*>(xr + c0) + j;
-                w[j] = a.in_place ? *src : __ldg(src);
-            }
-            const T* e = reinterpret_cast<const T*>(w);
-#pragma unroll
-            for (int i = 0; i < kGroup; ++i) x[i] = Elem<T>::load(e + i);
-        } else {
-#pragma unroll
-            for (int i = 0; i < kGroup; ++i) x[i] = c0 + i < a.k ? Elem<T>::load(xr + c0 + i) : 0.0f;
-        }
-
-        float s[kGroup], ax[kGroup];
-        float amax_s = 0.0f;
-        uint32_t lo2, hi2, b2, lo0, hi0, b0;
-        float sc2, sc0, err2, err0;
-        float d2[kGroup], d0[kGroup];
-        if (fast) {
-#pragma unroll
-            for (int i = 0; i < kGroup; ++i) {
-                s[i] = div_exact<true>(x[i], gs, rgs);
-                ax[i] = fabsf(x[i]);
-                amax_s = fmaxf(amax_s, fabsf(s[i]));
-            }
-            candidate<false, true>(ax, s, amax_s, gs, lo2, hi2, b2, sc2, err2, d2);
-            candidate<true, true>(ax, s, amax_s, gs, lo0, hi0, b0, sc0, err0, d0);
-        } else {
-#pragma unroll
-            for (int i = 0; i < kGroup; ++i) {
-                s[i] = __fdiv_rn(x[i], gs);
-                ax[i] = fabsf(x[i]);
-                amax_s = fmaxf(amax_s, fabsf(s[i]));
-            }
-            candidate<false, false>(ax, s, amax_s, gs, lo2, hi2, b2, sc2, err2, d2);
-            candidate<true, false>(ax, s, amax_s, gs, lo0, hi0, b0, sc0, err0, d0);
-        }
-        if (a.mode == MIXFP4_MODE_GIVEN)   // the caller's format bits (read before this warp rewrites the byte below)
+        uint32_t lo = 0, hi = 0, scale_byte = 0x01;    // what an all-zero block quantizes to
+        bool use_e0 = false;
+        if (kPack && a.mode == MIXFP4_MODE_GIVEN && real)   // the caller's format bits (read before the byte is rewritten below)
             use_e0 = (a.fmt[row * (a.blocks_pad / 8) + (blk >> 3)] >> (blk & 7)) & 1;
-        else
-            use_e0 = a.mode == MIXFP4_MODE_ORACLE16 ? (err0 < err2) : (a.mode == MIXFP4_MODE_ALL_E0M3);
-        lo = use_e0 ? lo0 : lo2;
-        hi = use_e0 ? hi0 : hi2;
-        scale_byte = use_e0 ? b0 : b2;
 
-        const int64_t g = row * a.groups + blk;
-        if (a.e2_err) a.e2_err[g] = err2;
-        if (a.e0_err) a.e0_err[g] = err0;
-        if (a.e2_scale) a.e2_scale[g] = sc2;
-        if (a.e0_scale) a.e0_scale[g] = sc0;
-
-        if (a.dequant) {
-            T* out = static_cast<T*>(a.dequant) + row * a.ld_dequant + c0;
-            T vals[kGroup];
-#pragma unroll
-            for (int i = 0; i < kGroup; ++i) {
-                const uint32_t nib = ((i < 8 ? lo : hi) >> (4 * (i & 7))) & 15u;
-                const float mag = use_e0 ? d0[i] : d2[i];
-                vals[i] = Elem<T>::round((nib & 8u) ? -mag : mag);
-            }
-            if (a.vec_out && c0 + kGroup <= a.k) {
+        if (real) {
+            const T* xr = static_cast<const T*>(a.x) + row * a.ldx;
+            const int64_t c0 = blk * kGroup;
+            float x[kGroup];
+            if (a.vec_in && c0 + kGroup <= a.k) {
                 constexpr int kWords = kGroup * sizeof(T) / 16;
+                uint4 w[kWords];
 #pragma unroll
-                for (int j = 0; j < kWords; ++j)
-                    reinterpret_cast<uint4*>(out)[j] = reinterpret_cast<const uint4*>(vals)[j];
+                for (int j = 0; j < kWords; ++j) {
+                    const uint4* src = reinterpret_cast<const uint4*>(xr + c0) + j;
+                    w[j] = a.in_place ? *src : __ldg(src);
+                }
+                const T* e = reinterpret_cast<const T*>(w);
+#pragma unroll
+                for (int i = 0; i < kGroup; ++i) x[i] = Elem<T>::load(e + i);
             } else {
 #pragma unroll
-                for (int i = 0; i < kGroup; ++i)
-                    if (c0 + i < a.k) out[i] = vals[i];
+                for (int i = 0; i < kGroup; ++i) x[i] = c0 + i < a.k ? Elem<T>::load(xr + c0 + i) : 0.0f;
+            }
+
+            float s[kGroup], ax[kGroup];
+            float amax_s = 0.0f;
+            uint32_t lo2, hi2, b2, lo0, hi0, b0;
+            float sc2, sc0, err2, err0;
+            float d2[kGroup], d0[kGroup];
+            if (fast) {
+#pragma unroll
+                for (int i = 0; i < kGroup; ++i) {
+                    s[i] = div_exact<true>(x[i], gs, rgs);
+                    ax[i] = fabsf(x[i]);
+                    amax_s = fmaxf(amax_s, fabsf(s[i]));
+                }
+                candidate<false, true, kPack, kDequant>(ax, s, amax_s, gs, lo2, hi2, b2, sc2, err2, d2);
+                candidate<true, true, kPack, kDequant>(ax, s, amax_s, gs, lo0, hi0, b0, sc0, err0, d0);
+            } else {
+#pragma unroll
+                for (int i = 0; i < kGroup; ++i) {
+                    s[i] = __fdiv_rn(x[i], gs);
+                    ax[i] = fabsf(x[i]);
+                    amax_s = fmaxf(amax_s, fabsf(s[i]));
+                }
+                candidate<false, false, kPack, kDequant>(ax, s, amax_s, gs, lo2, hi2, b2, sc2, err2, d2);
+                candidate<true, false, kPack, kDequant>(ax, s, amax_s, gs, lo0, hi0, b0, sc0, err0, d0);
+            }
+            if (a.mode != MIXFP4_MODE_GIVEN)
+                use_e0 = a.mode == MIXFP4_MODE_ORACLE16 ? (err0 < err2) : (a.mode == MIXFP4_MODE_ALL_E0M3);
+
+            const int64_t g = row * a.groups + blk;
+            if (a.e2_err) a.e2_err[g] = err2;
+            if (a.e0_err) a.e0_err[g] = err0;
+            if (a.e2_scale) a.e2_scale[g] = sc2;
+            if (a.e0_scale) a.e0_scale[g] = sc0;
+
+            if constexpr (kPack) {
+                // Sign bit of a nibble = (n < 0) = (x < 0): dividing by the positive scales keeps the sign and
+                // never reaches zero from a nonzero x; x = -0 gives n = -0, which is not below zero.
+                uint32_t sl = 0, sh = 0;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    if (x[i] < 0.0f) sl |= 8u << (4 * i);
+                    if (x[i + 8] < 0.0f) sh |= 8u << (4 * i);
+                }
+                lo = (use_e0 ? lo0 : lo2) | sl;
+                hi = (use_e0 ? hi0 : hi2) | sh;
+                scale_byte = use_e0 ? b0 : b2;
+            }
+
+            if constexpr (kDequant) {
+                T* out = static_cast<T*>(a.dequant) + row * a.ld_dequant + c0;
+                T vals[kGroup];
+#pragma unroll
+                for (int i = 0; i < kGroup; ++i) {
+                    const float mag = use_e0 ? d0[i] : d2[i];
+                    vals[i] = Elem<T>::round(x[i] < 0.0f ? -mag : mag);
+                }
+                if (a.vec_out && c0 + kGroup <= a.k) {
+                    constexpr int kWords = kGroup * sizeof(T) / 16;
+#pragma unroll
+                    for (int j = 0; j < kWords; ++j)
+                        reinterpret_cast<uint4*>(out)[j] = reinterpret_cast<const uint4*>(vals)[j];
+                } else {
+#pragma unroll
+                    for (int i = 0; i < kGroup; ++i)
+                        if (c0 + i < a.k) out[i] = vals[i];
+                }
             }
         }
-    }
 
-    if (!a.codes) return;                          // fake-quantization only: no packed outputs
-    if (stored) {
-        const int64_t ld_codes = a.blocks_pad * 8, ld_scales = a.blocks_pad;
-        *reinterpret_cast<uint2*>(a.codes + row * ld_codes + blk * 8) = make_uint2(lo, hi);
-        a.scales[row * ld_scales + blk] = static_cast<uint8_t>(scale_byte);
+        if constexpr (kPack) {
+            if (stored) {
+                const int64_t ld_codes = a.blocks_pad * 8, ld_scales = a.blocks_pad;
+                *reinterpret_cast<uint2*>(a.codes + row * ld_codes + blk * 8) = make_uint2(lo, hi);
+                a.scales[row * ld_scales + blk] = static_cast<uint8_t>(scale_byte);
+            }
+            const uint32_t bits = __ballot_sync(0xffffffffu, use_e0);
+            const int64_t fmt_col = chunk * 4 + lane;      // lanes 0..3 write one format byte each
+            if (lane < 4 && fmt_col < a.blocks_pad / 8)
+                a.fmt[row * (a.blocks_pad / 8) + fmt_col] = static_cast<uint8_t>(bits >> (8 * lane));
+        }
     }
-    const uint32_t bits = __ballot_sync(0xffffffffu, use_e0);
-    const int64_t fmt_col = chunk * 4 + lane;      // lanes 0..3 write one format byte each
-    if (lane < 4 && fmt_col < a.blocks_pad / 8)
-        a.fmt[row * (a.blocks_pad / 8) + fmt_col] = static_cast<uint8_t>(bits >> (8 * lane));
 }
 
-// --------------------------------------------------------------------------- dequant
 template <typename T, bool kKL>
 __global__ void __launch_bounds__(kThreads) dequant_kernel(const uint8_t* __restrict__ codes,
                                                            const uint8_t* __restrict__ scales,
@@ -492,13 +535,20 @@ int launch_quantize(const void* x, int dtype, int64_t rows, int64_t k, int64_t l
     a.e2_err = e2_err; a.e0_err = e0_err; a.e2_scale = e2_scale; a.e0_scale = e0_scale;
     a.dequant = dequant; a.ld_dequant = ld_dequant;
     const int64_t warps = rows * a.chunks;
-    const int64_t ctas = (warps + kWarpsPerCta - 1) / kWarpsPerCta;
-    if (ctas > 0x7fffffffLL) return MIXFP4_E_SHAPE;
+    int64_t ctas = (warps + kWarpsPerCta - 1) / kWarpsPerCta;
+    if (ctas > 148 * 6) ctas = 148 * 6;            // the warps stride over the (row, chunk) items
+#define MIXFP4_LAUNCH_QUANTIZE(T)                                                                       \
+    do {                                                                                                \
+        if (codes && dequant) quantize_kernel<T, true, true><<<(unsigned)ctas, kThreads, 0, st>>>(a);    \
+        else if (codes) quantize_kernel<T, true, false><<<(unsigned)ctas, kThreads, 0, st>>>(a);         \
+        else quantize_kernel<T, false, true><<<(unsigned)ctas, kThreads, 0, st>>>(a);                    \
+    } while (0)
     switch (dtype) {
-        case MIXFP4_BF16: quantize_kernel<__nv_bfloat16><<<(unsigned)ctas, kThreads, 0, st>>>(a); break;
-        case MIXFP4_F16: quantize_kernel<__half><<<(unsigned)ctas, kThreads, 0, st>>>(a); break;
-        default: quantize_kernel<float><<<(unsigned)ctas, kThreads, 0, st>>>(a);
+        case MIXFP4_BF16: MIXFP4_LAUNCH_QUANTIZE(__nv_bfloat16); break;
+        case MIXFP4_F16: MIXFP4_LAUNCH_QUANTIZE(__half); break;
+        default: MIXFP4_LAUNCH_QUANTIZE(float);
     }
+#undef MIXFP4_LAUNCH_QUANTIZE
     return check_launch("quantize_kernel");
 }
 }  // namespace
