@@ -18,6 +18,8 @@
 // owns 32 consecutive blocks of one row, so its loads cover 1 KB of contiguous bf16 and
 // its stores 256 B of codes, 32 B of scales and one 32-bit word of format bits.
 
+#include <cuda_fp4.h>
+
 #include "common.cuh"
 #include "decode.cuh"
 
@@ -146,6 +148,25 @@ __device__ __forceinline__ float e0m3_round(float mag) {
     const float t = __fadd_rn(fminf(mag, 7.25f), 8388608.0f);
     return __fsub_rn(t, 8388608.0f);
 }
+// The same rounding on the FP4 conversion unit.  The hardware rounds to nearest even, the reference
+// half up: setting the last mantissa bit lifts an exact tie (whose low bits are zero) above the
+// midpoint and leaves every other value on its side of it (the float below a tie already has the
+// bit set); the one input the reference's own fp32 addition lifts, the float just below 0.25, is
+// replaced by the float just above 0.25.  Two magnitudes -> one byte (first in the low nibble, the canonical code order),
+// and the byte back to the two level values.  mixfp4_selftest_division sweeps every fp32 input
+// against e2m1_round.
+__device__ __forceinline__ float e2m1_nudge(float mag) {
+    const uint32_t b = __float_as_uint(mag);
+    return __uint_as_float(b == 0x3e7fffffu ? 0x3e800001u : (b | 1u));
+}
+__device__ __forceinline__ uint32_t e2m1_pair_codes(float mag0, float mag1) {
+    return __nv_cvt_float2_to_fp4x2(make_float2(e2m1_nudge(mag0), e2m1_nudge(mag1)), __NV_E2M1, cudaRoundNearest);
+}
+__device__ __forceinline__ float2 e2m1_pair_levels(uint32_t byte) {
+    const __half2_raw h = __nv_cvt_fp4x2_to_halfraw2(static_cast<__nv_fp4x2_storage_t>(byte), __NV_E2M1);
+    return __half22float2(__half2(h));
+}
+
 // One candidate format of one block.  ax = |x|, s = x / gs.  Produces the block's scale, its
 // squared error in the reference's summation order, the magnitudes of the dequantized values
 // (kKeep) and the eight-per-word 3-bit level codes without signs (kPack).
@@ -161,37 +182,48 @@ __device__ __forceinline__ void candidate(const float (&ax)[kGroup], const float
     scale_val = sc;
     float sq[kGroup];
     float p4[4] = {0.0f, 0.0f, 0.0f, 0.0f};         // E0M3: four levels per float, 16^j weights (exact)
-    lo = 0;
-    hi = 0;
+    uint32_t byte[8];                               // E2M1: code bytes of the eight element pairs
 #pragma unroll
-    for (int i = 0; i < kGroup; ++i) {
-        const float mag = fabsf(div_exact<kFast>(s[i], sc, rsc));
-        const float q = kE0 ? e0m3_round(mag) : e2m1_round(mag);
-        if constexpr (kPack && kE0) {
-            const float weight = (i & 3) == 0 ? 1.0f : (i & 3) == 1 ? 16.0f : (i & 3) == 2 ? 256.0f : 4096.0f;
-            p4[i >> 2] = (i & 3) == 0 ? q : __fmaf_rn(q, weight, p4[i >> 2]);
+    for (int i = 0; i < kGroup; i += 2) {
+        const float mag0 = fabsf(div_exact<kFast>(s[i], sc, rsc)), mag1 = fabsf(div_exact<kFast>(s[i + 1], sc, rsc));
+        float q[2];
+        if constexpr (kE0) {
+            q[0] = e0m3_round(mag0);
+            q[1] = e0m3_round(mag1);
+            if constexpr (kPack) {
+                const int w = (i >> 1) & 1;                                // pair 0 or 1 of its group of four
+                p4[i >> 2] = w == 0 ? __fmaf_rn(q[1], 16.0f, q[0])
+                                    : __fmaf_rn(q[1], 4096.0f, __fmaf_rn(q[0], 256.0f, p4[i >> 2]));
+            }
+        } else {
+            byte[i >> 1] = e2m1_pair_codes(mag0, mag1);
+            const float2 lv = e2m1_pair_levels(byte[i >> 1]);
+            q[0] = lv.x;
+            q[1] = lv.y;
         }
-        if constexpr (kPack && !kE0) {
-            const uint32_t c = e2m1_code_at_22(q);
-            const int j = i & 7;                                       // constants once unrolled
-            const int right = 22 - 4 * j > 0 ? 22 - 4 * j : 0, left = 4 * j - 22 > 0 ? 4 * j - 22 : 0;
-            if (i < 8) lo |= (c >> right) << left;
-            else hi |= (c >> right) << left;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            // (d - x)^2 == (|d| - |x|)^2 bit for bit: d and x never have opposite signs
+            const float d = __fmul_rn(__fmul_rn(q[j], sc), gs);
+            if constexpr (kKeep) dmag[i + j] = d;
+            const float e = __fsub_rn(d, ax[i + j]);
+            sq[i + j] = __fmul_rn(e, e);
         }
-        // (d - x)^2 == (|d| - |x|)^2 bit for bit: d and x never have opposite signs
-        const float d = __fmul_rn(__fmul_rn(q, sc), gs);
-        if constexpr (kKeep) dmag[i] = d;
-        const float e = __fsub_rn(d, ax[i]);
-        sq[i] = __fmul_rn(e, e);
     }
     float acc = __fadd_rn(sq[0], sq[8]);
 #pragma unroll
     for (int j = 1; j < 8; ++j) acc = __fadd_rn(acc, __fadd_rn(sq[j], sq[j + 8]));
     err = acc;
+    lo = 0;
+    hi = 0;
     if constexpr (kPack && kE0) {
         // 2^23 + p has p in its low mantissa bits; the low halves of two such words make one code word
         lo = __byte_perm(__float_as_uint(__fadd_rn(p4[0], 8388608.0f)), __float_as_uint(__fadd_rn(p4[1], 8388608.0f)), 0x5410);
         hi = __byte_perm(__float_as_uint(__fadd_rn(p4[2], 8388608.0f)), __float_as_uint(__fadd_rn(p4[3], 8388608.0f)), 0x5410);
+    }
+    if constexpr (kPack && !kE0) {
+        lo = __byte_perm(__byte_perm(byte[0], byte[1], 0x0040), __byte_perm(byte[2], byte[3], 0x0040), 0x5410);
+        hi = __byte_perm(__byte_perm(byte[4], byte[5], 0x0040), __byte_perm(byte[6], byte[7], 0x0040), 0x5410);
     }
 }
 
@@ -208,6 +240,24 @@ __global__ void selftest_division_kernel(unsigned long long* mismatches) {
         bad += __float_as_uint(div_rcp(a, b, r)) != __float_as_uint(__fdiv_rn(a, b));
         bad += __float_as_uint(div_rcp(a * 0.001f, b * 6.0f, __frcp_rn(b * 6.0f))) != __float_as_uint(__fdiv_rn(a * 0.001f, b * 6.0f));
     }
+    if (bad) atomicAdd(mismatches, bad);
+}
+
+// Exhaustive check of the FP4-unit E2M1 rounding against e2m1_round: every fp32 magnitude from 0
+// to 16 (pairs of neighbouring bit patterns), level value and 3-bit code.
+constexpr uint32_t kE2m1SweepPairs = 0x41800000u / 2 + 1;
+__global__ void selftest_e2m1_kernel(unsigned long long* mismatches) {
+    const uint32_t pair = blockIdx.x * blockDim.x + threadIdx.x;
+    if (pair >= kE2m1SweepPairs) return;
+    const float m0 = __uint_as_float(2 * pair), m1 = __uint_as_float(2 * pair + 1);
+    const uint32_t byte = e2m1_pair_codes(m0, m1);
+    const float2 lv = e2m1_pair_levels(byte);
+    const float q0 = e2m1_round(m0), q1 = e2m1_round(m1);
+    unsigned long long bad = 0;
+    bad += __float_as_uint(lv.x) != __float_as_uint(q0);
+    bad += __float_as_uint(lv.y) != __float_as_uint(q1);
+    bad += (byte & 15u) != (e2m1_code_at_22(q0) >> 22);
+    bad += (byte >> 4) != (e2m1_code_at_22(q1) >> 22);
     if (bad) atomicAdd(mismatches, bad);
 }
 
@@ -235,11 +285,15 @@ __global__ void __launch_bounds__(kThreads, 3) quantize_kernel(const QuantArgs a
     }
     if (blockIdx.x == 0 && threadIdx.x == 0 && a.global_scale) *a.global_scale = gs;
 
-    const int64_t items = a.rows * a.chunks;
-    for (int64_t item = (int64_t)blockIdx.x * kWarpsPerCta + warp_in_cta; item < items;
-         item += (int64_t)gridDim.x * kWarpsPerCta) {
-        const int64_t row = item / a.chunks;
-        const int64_t chunk = item - row * a.chunks;
+    // (row, chunk) of this warp's items: one division here, carries in the loop
+    const int64_t first = (int64_t)blockIdx.x * kWarpsPerCta + warp_in_cta, step = (int64_t)gridDim.x * kWarpsPerCta;
+    const int64_t step_rows = step / a.chunks, step_chunks = step - step_rows * a.chunks;
+    int64_t row = first / a.chunks, chunk = first - row * a.chunks;
+    for (; row < a.rows; row += step_rows, chunk += step_chunks) {
+        if (chunk >= a.chunks) {
+            chunk -= a.chunks;
+            if (++row >= a.rows) break;
+        }
         const int64_t blk = chunk * 32 + lane;         // block index inside the row
         const bool stored = blk < a.blocks_pad;
         const bool real = blk < a.groups;
@@ -644,7 +698,10 @@ extern "C" int mixfp4_selftest_division(unsigned long long* mismatches, void* st
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     MIXFP4_CUDA_CHECK(cudaMemsetAsync(mismatches, 0, sizeof(unsigned long long), st));
     selftest_division_kernel<<<(1u << 23) / 256, 256, 0, st>>>(mismatches);
-    const int rc = check_launch("selftest_division_kernel");
+    int rc = check_launch("selftest_division_kernel");
+    if (rc != MIXFP4_OK) return rc;
+    selftest_e2m1_kernel<<<(kE2m1SweepPairs + 255) / 256, 256, 0, st>>>(mismatches);
+    rc = check_launch("selftest_e2m1_kernel");
     return rc != MIXFP4_OK ? rc : fwht_selftest_division(mismatches, st);
 }
 
