@@ -132,8 +132,10 @@ MIXFP4_API int mixfp4_select_regions(const float* e2_err, const float* e0_err, i
 /* Diagnostic: the quantizer divides by block scales with a reciprocal-and-residual sequence
  * instead of a full IEEE division.  This runs the exhaustive proof that the two agree (all 2^23
  * dividend significands x the 8 significands an E4M3 scale or the constants 6 and 7 can have;
- * likewise for the Hadamard kernel's division by sqrt(32) and sqrt(128))
- * and leaves the number of disagreements (expected 0) in *mismatches (device memory). */
+ * likewise for the Hadamard kernel's division by sqrt(32) and sqrt(128)), and the proof that the
+ * E2M1 rounding done on the FP4 conversion unit equals the reference's round-half-up
+ * (project_quant/codebook.py:12-25) for every fp32 magnitude from 0 to 16, level and code;
+ * it leaves the number of disagreements (expected 0) in *mismatches (device memory). */
 MIXFP4_API int mixfp4_selftest_division(unsigned long long* mismatches, void* stream);
 
 /* Packed -> dense weight in out_dtype (the tensor the reference stores back into

@@ -13,8 +13,8 @@
 // into an FMA, and the 16 squared errors are added in the order the reference's CPU
 // reduction uses (lane j + lane j+8 first, then the eight sums left to right).
 //
-// Work split: one thread owns one 16-element block (two candidates, ~40 fp32
-// instructions per element -- the kernel is bound by the fp32 pipes, not by HBM); a warp
+// Work split: one thread owns one 16-element block (two candidates, ~50
+// instructions per element -- the kernel is bound by instruction issue, not by HBM); a warp
 // owns 32 consecutive blocks of one row, so its loads cover 1 KB of contiguous bf16 and
 // its stores 256 B of codes, 32 B of scales and one 32-bit word of format bits.
 
