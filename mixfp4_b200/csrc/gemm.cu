@@ -1094,14 +1094,19 @@ extern "C" int mixfp4_gemm(const void* x, int64_t m, int64_t ldx, const uint8_t*
         }
     }
     const bool kl = layout == MIXFP4_LAYOUT_KERNEL;
-    // Enough 256 x 256 tiles to occupy most SMs: CTA pairs (two SMs share each decoded weight tile;
-    // measured 1.25-1.3 x the single-CTA kernel at M >= 2048, slower below about 100 CTAs).
-    const int64_t pair_ctas = 2 * ((m + 511) / 512) * ((n + 255) / 256);
-    if (pair_ctas >= 112) return kl ? launch_gemm_pair<2, true>(xa, lda, a, st) : launch_gemm_pair<2, false>(xa, lda, a, st);
-    // fewer tokens: pairs of 128-row CTAs (the pair still shares a 256-row weight tile)
-    const int64_t pair_ctas_small = 2 * ((m + 255) / 256) * ((n + 255) / 256);
-    if (pair_ctas_small >= 112 && m > 256)
-        return kl ? launch_gemm_pair<1, true>(xa, lda, a, st) : launch_gemm_pair<1, false>(xa, lda, a, st);
+    // More than 256 tokens and enough tiles to occupy most SMs: CTA pairs (two SMs share each decoded
+    // weight tile; measured 1.25-1.3 x the single-CTA kernel at M >= 2048, slower below about 100 CTAs).
+    // Pairs of 256-row CTAs unless pairs of 128-row CTAs pad the token rows noticeably less.  With at
+    // most 256 tokens a pair's second CTA would hold no rows and still decode: measured 88 us against 51
+    // for the single-CTA kernel at M = 17 .. 128 on a 28672 x 4096 weight.
+    if (m > 256) {
+        const int64_t tiles_n = (n + 255) / 256;
+        const int64_t rows2 = (m + 511) / 512 * 512, rows1 = (m + 255) / 256 * 256;
+        if (rows2 * 100 <= rows1 * 108 && 2 * (rows2 / 512) * tiles_n >= 112)
+            return kl ? launch_gemm_pair<2, true>(xa, lda, a, st) : launch_gemm_pair<2, false>(xa, lda, a, st);
+        if (2 * (rows1 / 256) * tiles_n >= 112)
+            return kl ? launch_gemm_pair<1, true>(xa, lda, a, st) : launch_gemm_pair<1, false>(xa, lda, a, st);
+    }
     if (mt == 1 && bn == 128) return kl ? launch_gemm<1, 128, true>(xa, lda, a, st) : launch_gemm<1, 128, false>(xa, lda, a, st);
     if (mt == 1 && bn == 256) return kl ? launch_gemm<1, 256, true>(xa, lda, a, st) : launch_gemm<1, 256, false>(xa, lda, a, st);
     if (mt == 2 && bn == 128) return kl ? launch_gemm<2, 128, true>(xa, lda, a, st) : launch_gemm<2, 128, false>(xa, lda, a, st);
