@@ -122,7 +122,11 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- GPU arm
-def build_model(device, rank: int, world: int, m: int):
+def to_layout(packed, layout: str):
+    return packed.to_stream_layout() if layout == "stream" else packed.to_kernel_layout()
+
+
+def build_model(device, rank: int, world: int, m: int, layout: str = "stream"):
     """Quantize the (sharded) synthetic 8B linear stack on the device.  Returns a list of
     layers, each a dict name -> (PackedWeight, kind)."""
     import mixfp4_b200 as mx
@@ -151,7 +155,7 @@ def build_model(device, rank: int, world: int, m: int):
                     step = n // world
                     w = w[rank * step:(rank + 1) * step].contiguous()
             packed, _, _ = mx.quantize_packed(w, amax=amax)
-            entry[name] = packed.to_kernel_layout()
+            entry[name] = to_layout(packed, layout)
             del w
         model.append(entry)
     torch.cuda.synchronize(device)
@@ -207,7 +211,7 @@ def run_ours(args):
     global TRAFFIC_BYTES_PER_LAUNCH
     TRAFFIC_BYTES_PER_LAUNCH = int(TRAFFIC_OVER_ALGORITHMIC * total_bytes / launches_per_step / world)
 
-    model = build_model(dev, rank, world, m)
+    model = build_model(dev, rank, world, m, args.layout)
     x_host = torch.randn((m, 4096), generator=torch.Generator().manual_seed(7)).to(torch.bfloat16).pin_memory()
     x_dev = x_host.to(dev)
     out_host = torch.empty((m, 4096), dtype=torch.bfloat16).pin_memory()
@@ -301,7 +305,7 @@ def run_ours(args):
                     "d2h_bytes_per_step": out_host.numel() * 2},
             "gpu_launches": launches_per_step * args.steps,
             "roofline": {"bound": "hbm", "achieved": round(per_gpu, 1), "peak": peak, "unit": "GB/s",
-                         "frac": round(per_gpu / peak, 4), "peak_kind": peak_kind, "kernel": "gemv_sm_kernel",
+                         "frac": round(per_gpu / peak, 4), "peak_kind": peak_kind, "kernel": "gemv_stream_kernel" if args.layout == "stream" else "gemv_sm_kernel",
                          "traffic": TRAFFIC_BYTES_PER_LAUNCH,
                          "note": "achieved = algorithmic bytes of the %d GEMV launches of a step / CUDA-event time" % launches_per_step},
             "peer_wait_status": int(comm.status.item()) if comm is not None else None,
@@ -351,7 +355,7 @@ def secondary_numbers(dev) -> dict:
     out["quantize_ms_14336x4096"] = round(t * 1e3, 4)
 
     # decode GEMV at larger batch, gate/up shape, cycling over distinct weights (> L2)
-    packs = [mx.quantize_packed(w)[0].to_kernel_layout() for w in ws]
+    packs = [mx.quantize_packed(w)[0].to_stream_layout() for w in ws]
     for m in (4, 16):
         x = torch.randn((m, k), device=dev).to(torch.bfloat16)
 
@@ -359,7 +363,18 @@ def secondary_numbers(dev) -> dict:
             for p in packs:
                 mx.mixfp4_linear(x, p, overlap_previous=True)
 
-        t = timeit(gemv_pass, 10) / len(packs)
+        # as a CUDA graph of dependent launches, like the headline (a Python call per launch costs
+        # more than the kernel)
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            gemv_pass()
+            torch.cuda.synchronize(dev)
+            with torch.cuda.graph(g, stream=side):
+                gemv_pass()
+        torch.cuda.synchronize(dev)
+        t = timeit(g.replay, 10) / len(packs)
         out["gemv_gbs_m%d_14336x4096" % m] = round(algorithmic_bytes(n, k, m) / t / 1e9, 1)
 
     peak_tf = None
@@ -465,6 +480,78 @@ def run_reference(args):
     }))
 
 
+# ------------------------------------------------------------------ single-kernel timing
+def run_kernel(args):
+    """One kernel alone on one shape (the command the profiler summaries under profiles/ were
+    captured with): prints one line with the kernel's algorithmic bytes or flops per second.
+    Weights are seeded N(0, 0.02^2) bf16 tensors quantized on the device; the GEMV cycles over
+    enough distinct packed weights to exceed the L2 and runs as a CUDA graph of dependent launches."""
+    import mixfp4_b200 as mx
+    torch.cuda.set_device(0)
+    n, k, m = args.shape
+
+    def timed(fn, iters, warm=3):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / iters * 1e-3
+
+    def weight(seed):
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        return (torch.randn((n, k), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+
+    if args.kernel == "gemv":
+        per = mx.packed_nbytes(n, k)
+        buffers = args.buffers or max(2, int(600e6 // per))
+        packs = [to_layout(mx.quantize_packed(weight(i))[0], args.layout) for i in range(buffers)]
+        x = torch.randn((m, k), device="cuda").to(torch.bfloat16)
+
+        def run():
+            for p in packs:
+                mx.mixfp4_linear(x, p, overlap_previous=True)
+
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            run()
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                run()
+        t = timed(graph.replay, args.steps) / buffers
+        algo = per + 2 * m * k + 2 * m * n
+        print(json.dumps({"kernel": "gemv", "layout": args.layout, "n": n, "k": k, "m": m, "us_per_launch": round(t * 1e6, 2),
+                          "gbs": round(algo / t / 1e9, 1), "buffers": buffers, "decode_status": mx.decode_status()}))
+    elif args.kernel == "gemm":
+        w = weight(0)
+        if args.rotate:
+            packed = to_layout(mx.quantize_packed(mx.apply_transform(w, "H128"), rotation="H128")[0], args.layout)
+        else:
+            packed = to_layout(mx.quantize_packed(w)[0], args.layout)
+        x = torch.randn((m, k), device="cuda").to(torch.bfloat16)
+        t = timed(lambda: mx.mixfp4_linear(x, packed), args.steps)
+        print(json.dumps({"kernel": "gemm", "layout": args.layout, "n": n, "k": k, "m": m, "h128": bool(args.rotate),
+                          "us": round(t * 1e6, 1), "tflops": round(2.0 * m * n * k / t / 1e12, 1),
+                          "gemm_status": mx.gemm_status()}))
+    else:
+        ws = [weight(i) for i in range(max(2, int(400e6 // (2 * n * k))))]
+        state = {"i": 0}
+
+        def run():
+            state["i"] = (state["i"] + 1) % len(ws)
+            mx.quantize_packed(ws[state["i"]])
+
+        t = timed(run, args.steps)
+        algo = 2 * n * k + mx.packed_nbytes(n, k)
+        print(json.dumps({"kernel": "quantize", "n": n, "k": k, "us": round(t * 1e6, 1), "gbs": round(algo / t / 1e9, 1)}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -476,8 +563,17 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary kernel numbers")
     ap.add_argument("--nccl-allreduce", action="store_true",
                     help="multi-GPU: GEMV + NCCL all-reduce instead of the fused GEMV + all-reduce kernel")
+    ap.add_argument("--layout", default="stream", choices=["stream", "kernel"],
+                    help="packed layout of the weights the linears read (stream: 1152-byte chunks; kernel: row-major)")
+    ap.add_argument("--kernel", default=None, choices=["gemv", "gemm", "quantize"],
+                    help="time one kernel alone on --shape N K M instead of the decode workload")
+    ap.add_argument("--shape", type=int, nargs=3, default=[14336, 4096, 1], metavar=("N", "K", "M"))
+    ap.add_argument("--buffers", type=int, default=None, help="--kernel gemv: distinct weights to cycle over")
+    ap.add_argument("--rotate", action="store_true", help="--kernel gemm: H128 rotation of x inside the call")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.kernel:
+        run_kernel(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -32,7 +32,7 @@
 extern "C" {
 #endif
 
-#define MIXFP4_ABI_VERSION 2
+#define MIXFP4_ABI_VERSION 3
 
 #if defined(__GNUC__)
 #define MIXFP4_API __attribute__((visibility("default")))
@@ -62,8 +62,15 @@ enum { MIXFP4_BF16 = 0, MIXFP4_F16 = 1, MIXFP4_F32 = 2 };
  * with fewer instructions: same array shapes, but inside every 32-bit word of `codes`
  * (8 elements) bit 3 of nibble 2i+1 holds the sign of element i and bit 3 of nibble 2i the
  * sign of element 4+i (i = 0..3), and bit 7 of every scale byte holds the block's format
- * bit (the `fmt` array is not used).  mixfp4_repack converts either way. */
-enum { MIXFP4_LAYOUT_CANONICAL = 0, MIXFP4_LAYOUT_KERNEL = 1 };
+ * bit (the `fmt` array is not used).  mixfp4_repack converts either way.
+ * STREAM is what the decode kernels stream fastest: one buffer of mixfp4_stream_bytes(rows, k)
+ * bytes made of 1152-byte chunks, one per 16 rows x 128 K elements, chunk (tile, j) at
+ * (tile * kpad/128 + j) * 1152: first 16 x 64 bytes of codes (row-major, code words in the KERNEL
+ * bit order), then 16 x 8 scale bytes (row-major, format bit in bit 7).  Rows that pad the last
+ * tile hold zero codes.  Entry points that take a layout accept the chunk buffer as `codes`;
+ * `scales` and `fmt` are then unused and may be NULL.  mixfp4_repack_stream /
+ * mixfp4_repack_from_stream convert from and to the canonical layout. */
+enum { MIXFP4_LAYOUT_CANONICAL = 0, MIXFP4_LAYOUT_KERNEL = 1, MIXFP4_LAYOUT_STREAM = 2 };
 
 /* flags of the linear entry points */
 enum {
@@ -152,6 +159,15 @@ MIXFP4_API int mixfp4_repack(const uint8_t* codes, const uint8_t* scales, const 
                   int64_t rows, int64_t k, int to_layout,
                   uint8_t* codes_out, uint8_t* scales_out, uint8_t* fmt_out, void* stream);
 
+/* Stream layout (no reference counterpart).  mixfp4_stream_bytes: size of the chunk buffer of a
+ * [rows, k] weight.  mixfp4_repack_stream: canonical codes/scales/fmt -> chunks.
+ * mixfp4_repack_from_stream: chunks -> canonical codes_out/scales_out/fmt_out.  Pure permutations. */
+MIXFP4_API int64_t mixfp4_stream_bytes(int64_t rows, int64_t k);
+MIXFP4_API int mixfp4_repack_stream(const uint8_t* codes, const uint8_t* scales, const uint8_t* fmt,
+                         int64_t rows, int64_t k, uint8_t* chunks, void* stream);
+MIXFP4_API int mixfp4_repack_from_stream(const uint8_t* chunks, int64_t rows, int64_t k,
+                              uint8_t* codes_out, uint8_t* scales_out, uint8_t* fmt_out, void* stream);
+
 /* Decode table of a packed weight: 256 entries x 16 B indexed by (format << 7 | E4M3 scale
  * byte) holding the block's eight bf16 magnitudes bf16((level * scale) * global).  Optional
  * input of the linear kernels (they build it per launch when given NULL). */
@@ -180,29 +196,37 @@ MIXFP4_API int mixfp4_gemv(const void* x, int64_t m, int64_t ldx,
 /* Several weights that take the same x in one launch (q/k/v, gate/up of a decoder layer; no
  * single counterpart in the reference, which calls nn.Linear.forward once per projection,
  * modeling.py:629): y_i[M,n_i] = x[M,K] * W_i[n_i,K]^T for i < count, 1 <= count <= 3,
- * 1 <= M <= 16, all weights in MIXFP4_LAYOUT_KERNEL with the same K.  Saves the per-launch
- * ramp of the small projections.  Returns MIXFP4_E_SHAPE when x (M * (2 * padded K + 16)
- * bytes) or the tables do not fit in shared memory: call mixfp4_gemv per weight then. */
+ * 1 <= M <= 16, all weights in the same layout (MIXFP4_LAYOUT_KERNEL or MIXFP4_LAYOUT_STREAM)
+ * with the same K.  Saves the per-launch ramp of the small projections.  Returns MIXFP4_E_SHAPE
+ * when x (M * (2 * padded K + 16) bytes) or the tables do not fit in shared memory: call
+ * mixfp4_gemv per weight then. */
 typedef struct mixfp4_gemv_segment {
-    const uint8_t* codes;          /* kernel layout [n, kpad/2] */
-    const uint8_t* scales;         /* kernel layout [n, kpad/16] */
+    const uint8_t* codes;          /* kernel layout [n, kpad/2], or the stream layout's chunk buffer */
+    const uint8_t* scales;         /* kernel layout [n, kpad/16]; unused (NULL) for the stream layout */
     const float* global_scale;     /* device f32[1] */
     const void* lut;               /* optional table from mixfp4_decode_table, else NULL */
     void* y;                       /* [M, n] in out_dtype */
     int64_t ldy;
     int64_t n;
 } mixfp4_gemv_segment;
+/* 1 if the stream-layout decode kernel can keep x resident for `count` weights of this K (the
+ * fused all-reduce and the grouped launch need that), else 0.  Host-only arithmetic; ranks of a
+ * tensor-parallel group call it with the largest K shard so that all take the same branch. */
+MIXFP4_API int mixfp4_gemv_x_fits(int64_t m, int64_t k, int count);
 MIXFP4_API int mixfp4_gemv_grouped(const void* x, int64_t m, int64_t ldx, int64_t k,
-                        const mixfp4_gemv_segment* segments, int count,
+                        const mixfp4_gemv_segment* segments, int count, int layout,
                         int out_dtype, int flags, void* stream);
 
 /* Row-parallel decode linear with the all-reduce fused into the kernel (tensor parallelism over
  * the GPUs of one node, one process per GPU; replaces F.linear on a K shard of the weight,
  * modeling.py:629, followed by the sum over ranks that a row-parallel split needs -- the reference
- * itself is single-device).  Every rank calls with its own K shard (x [M, k_shard], kernel-layout
- * weight [n, k_shard]) and receives the same y = sum over ranks, added in rank order.  Partial sums
- * travel as 8-byte {value, sequence} packets stored directly into the peers' buffers; every wait
- * is bounded (2 s) and reports through *status (device int, optional).  1 <= M <= 8.
+ * itself is single-device).  Every rank calls with its own K shard (x [M, k_shard], weight
+ * [n, k_shard] in MIXFP4_LAYOUT_KERNEL or MIXFP4_LAYOUT_STREAM) and receives the same y = sum over
+ * ranks, added in rank order.  Partial sums travel as 8-byte {value, sequence} packets stored
+ * directly into the peers' buffers; every wait is bounded (2 s unless mixfp4_set_wait_limit_ns
+ * changed it) and reports through *status (device int, optional: 100 + the rank whose packet did
+ * not arrive; the output is then invalid, the kernel still returns and later launches work).
+ * 1 <= M <= 8.
  *
  * Communicator: mixfp4_comm_create allocates this rank's receive buffer (slot_floats >= M * n of
  * the largest call) on the current device; mixfp4_comm_handle exports it (mixfp4_comm_handle_bytes
@@ -214,11 +238,29 @@ MIXFP4_API int mixfp4_comm_create(int rank, int world, int64_t slot_floats, mixf
 MIXFP4_API int mixfp4_comm_handle_bytes(void);
 MIXFP4_API int mixfp4_comm_handle(const mixfp4_comm* comm, void* handle);
 MIXFP4_API int mixfp4_comm_open(mixfp4_comm* comm, const void* handles);
+/* Same for a process that drives several GPUs itself (or a test): buffers = world device pointers
+ * in rank order, each at least mixfp4_comm_buffer_bytes(world, slot_floats) bytes, zeroed, and
+ * reachable from this GPU (peer access enabled by the caller); this rank's own entry is ignored. */
+MIXFP4_API int64_t mixfp4_comm_buffer_bytes(int world, int64_t slot_floats);
+/* This rank's receive buffer (device pointer): [2 parities][world source ranks][slot_floats] packets
+ * of {fp32 bits, sequence number + 1}, the pointer the other GPUs' communicators are opened with. */
+MIXFP4_API int mixfp4_comm_buffer(const mixfp4_comm* comm, void** buffer);
+MIXFP4_API int mixfp4_comm_open_local(mixfp4_comm* comm, void* const* buffers);
 MIXFP4_API int mixfp4_comm_destroy(mixfp4_comm* comm);
 MIXFP4_API int mixfp4_gemv_allreduce(const mixfp4_comm* comm, const void* x, int64_t m, int64_t ldx,
                           const uint8_t* codes, const uint8_t* scales, const float* global_scale,
-                          const void* lut, int64_t n, int64_t k, void* y, int out_dtype, int64_t ldy,
-                          int* status, int flags, void* stream);
+                          const void* lut, int64_t n, int64_t k, int layout, void* y, int out_dtype,
+                          int64_t ldy, int* status, int flags, void* stream);
+
+/* Bounded device-side waits.  Every spin in the kernels (on a weight chunk, a tensor-core stage, a
+ * peer's packet) gives up after a time limit, records a code in a status word and lets the kernel
+ * finish.  mixfp4_set_wait_limit_ns changes the limit of the decode kernels' waits for later
+ * launches (default 2 s; meant for tests and for hosts with their own watchdog).
+ * mixfp4_check_status synchronises `stream`, reads the device word `dev_status` (NULL: the decode
+ * kernels' own word for weight chunks on the current device), stores it in *value (optional) and
+ * returns MIXFP4_E_DEVICE_WAIT if it is non-zero, else MIXFP4_OK. */
+MIXFP4_API int mixfp4_set_wait_limit_ns(uint64_t ns);
+MIXFP4_API int mixfp4_check_status(const int* dev_status, int* value, void* stream);
 
 /* Prefill-shape dequant-linear on the tcgen05 tensor cores (any M >= 1, meant for
  * M >= 128).  rotation_block: 0, or 128 to apply the block-Hadamard H128 to x on the

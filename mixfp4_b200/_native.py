@@ -16,9 +16,10 @@ from . import build as _build
 
 OK = 0
 E_NULL, E_SHAPE, E_ALIGN, E_DTYPE, E_MODE, E_CUDA, E_WORKSPACE = -1, -2, -3, -4, -5, -6, -7
+E_UNSUPPORTED, E_DEVICE_WAIT, E_TOO_LARGE = -8, -9, -10
 BF16, F16, F32 = 0, 1, 2
 MODE_ORACLE16, MODE_ALL_E2M1, MODE_ALL_E0M3, MODE_GIVEN = 0, 1, 2, 3
-LAYOUT_CANONICAL, LAYOUT_KERNEL = 0, 1
+LAYOUT_CANONICAL, LAYOUT_KERNEL, LAYOUT_STREAM = 0, 1, 2
 FLAG_OVERLAP_PREVIOUS = 1
 
 DTYPE_CODE = {torch.bfloat16: BF16, torch.float16: F16, torch.float32: F32}
@@ -45,6 +46,7 @@ class GemvSegment(ctypes.Structure):
 
 def _declare(h: ctypes.CDLL) -> None:
     p, i64, i32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int
+    pp = ctypes.POINTER(ctypes.c_void_p)
     h.mixfp4_abi_version.restype = i32
     h.mixfp4_abi_version.argtypes = []
     h.mixfp4_status_string.restype = ctypes.c_char_p
@@ -74,8 +76,25 @@ def _declare(h: ctypes.CDLL) -> None:
     h.mixfp4_gemv.restype = i32
     h.mixfp4_gemv.argtypes = [p, i64, i64, p, p, p, p, i64, i64, i32, p, p, i32, i64, i32, p]
     h.mixfp4_gemv_grouped.restype = i32
-    h.mixfp4_gemv_grouped.argtypes = [p, i64, i64, i64, ctypes.POINTER(GemvSegment), i32, i32, i32, p]
-    pp = ctypes.POINTER(ctypes.c_void_p)
+    h.mixfp4_gemv_grouped.argtypes = [p, i64, i64, i64, ctypes.POINTER(GemvSegment), i32, i32, i32, i32, p]
+    h.mixfp4_gemv_x_fits.restype = i32
+    h.mixfp4_gemv_x_fits.argtypes = [i64, i64, i32]
+    h.mixfp4_stream_bytes.restype = i64
+    h.mixfp4_stream_bytes.argtypes = [i64, i64]
+    h.mixfp4_repack_stream.restype = i32
+    h.mixfp4_repack_stream.argtypes = [p, p, p, i64, i64, p, p]
+    h.mixfp4_repack_from_stream.restype = i32
+    h.mixfp4_repack_from_stream.argtypes = [p, i64, i64, p, p, p, p]
+    h.mixfp4_set_wait_limit_ns.restype = i32
+    h.mixfp4_set_wait_limit_ns.argtypes = [ctypes.c_uint64]
+    h.mixfp4_check_status.restype = i32
+    h.mixfp4_check_status.argtypes = [p, ctypes.POINTER(ctypes.c_int), p]
+    h.mixfp4_comm_buffer_bytes.restype = i64
+    h.mixfp4_comm_buffer_bytes.argtypes = [i32, i64]
+    h.mixfp4_comm_buffer.restype = i32
+    h.mixfp4_comm_buffer.argtypes = [p, pp]
+    h.mixfp4_comm_open_local.restype = i32
+    h.mixfp4_comm_open_local.argtypes = [p, ctypes.POINTER(ctypes.c_void_p)]
     h.mixfp4_comm_create.restype = i32
     h.mixfp4_comm_create.argtypes = [i32, i32, i64, pp]
     h.mixfp4_comm_handle_bytes.restype = i32
@@ -87,7 +106,7 @@ def _declare(h: ctypes.CDLL) -> None:
     h.mixfp4_comm_destroy.restype = i32
     h.mixfp4_comm_destroy.argtypes = [p]
     h.mixfp4_gemv_allreduce.restype = i32
-    h.mixfp4_gemv_allreduce.argtypes = [p, p, i64, i64, p, p, p, p, i64, i64, p, i32, i64, p, i32, p]
+    h.mixfp4_gemv_allreduce.argtypes = [p, p, i64, i64, p, p, p, p, i64, i64, i32, p, i32, i64, p, i32, p]
     h.mixfp4_gemm_workspace_bytes.restype = i64
     h.mixfp4_gemm_workspace_bytes.argtypes = [i64, i64, i64]
     h.mixfp4_gemm.restype = i32
@@ -104,9 +123,11 @@ def _declare(h: ctypes.CDLL) -> None:
 EXPORTED = (
     "mixfp4_abi_version", "mixfp4_status_string", "mixfp4_last_cuda_error", "mixfp4_padded_k",
     "mixfp4_amax", "mixfp4_quantize", "mixfp4_fake_quantize", "mixfp4_select_regions", "mixfp4_selftest_division", "mixfp4_dequant", "mixfp4_repack", "mixfp4_decode_table", "mixfp4_fwht",
-    "mixfp4_gemv", "mixfp4_gemv_grouped",
-    "mixfp4_comm_create", "mixfp4_comm_handle_bytes", "mixfp4_comm_handle", "mixfp4_comm_open", "mixfp4_comm_destroy",
-    "mixfp4_gemv_allreduce",
+    "mixfp4_stream_bytes", "mixfp4_repack_stream", "mixfp4_repack_from_stream",
+    "mixfp4_gemv", "mixfp4_gemv_x_fits", "mixfp4_gemv_grouped",
+    "mixfp4_comm_create", "mixfp4_comm_handle_bytes", "mixfp4_comm_handle", "mixfp4_comm_open",
+    "mixfp4_comm_buffer_bytes", "mixfp4_comm_buffer", "mixfp4_comm_open_local", "mixfp4_comm_destroy",
+    "mixfp4_gemv_allreduce", "mixfp4_set_wait_limit_ns", "mixfp4_check_status",
     "mixfp4_gemm_workspace_bytes", "mixfp4_gemm", "mixfp4_gemm_a4", "mixfp4_gemm_h128_static_max_bytes", "mixfp4_gemm_h128_static",
 )
 
@@ -122,7 +143,7 @@ def lib() -> ctypes.CDLL:
                 "(run `python -m mixfp4_b200.build`); mixfp4_b200 has no fallback path")
         handle = ctypes.CDLL(path)
         _declare(handle)
-        if handle.mixfp4_abi_version() != 2:
+        if handle.mixfp4_abi_version() != 3:
             raise RuntimeError("libmixfp4_b200.so ABI version mismatch; rebuild it")
         _lib = handle
     return _lib

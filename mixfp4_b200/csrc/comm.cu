@@ -25,6 +25,7 @@ struct mixfp4_comm {
     uint2* peer[8];              // every rank's buffer as seen from this GPU (peer[rank] == recv)
     uint32_t* words;             // [0] sequence number of the next launch, [1] finished-CTA counter
     bool opened;
+    bool local;                  // peers are plain pointers of this process (mixfp4_comm_open_local)
 };
 
 using namespace mixfp4;
@@ -34,7 +35,7 @@ extern "C" int mixfp4_comm_create(int rank, int world, int64_t slot_floats, mixf
     if (world < 1 || world > 8 || rank < 0 || rank >= world || slot_floats <= 0) return MIXFP4_E_SHAPE;
     mixfp4_comm* c = new (std::nothrow) mixfp4_comm();
     if (!c) return MIXFP4_E_CUDA;
-    c->rank = rank; c->world = world; c->slot_packets = slot_floats; c->opened = world == 1;
+    c->rank = rank; c->world = world; c->slot_packets = slot_floats; c->opened = world == 1; c->local = false;
     for (int i = 0; i < 8; ++i) c->peer[i] = nullptr;
     const size_t bytes = (size_t)2 * world * slot_floats * sizeof(uint2);
     cudaError_t err = cudaGetDevice(&c->device);
@@ -80,10 +81,34 @@ extern "C" int mixfp4_comm_open(mixfp4_comm* c, const void* handles) {
     return MIXFP4_OK;
 }
 
+extern "C" int64_t mixfp4_comm_buffer_bytes(int world, int64_t slot_floats) {
+    return world >= 1 && world <= 8 && slot_floats > 0 ? (int64_t)2 * world * slot_floats * (int64_t)sizeof(uint2) : 0;
+}
+
+extern "C" int mixfp4_comm_buffer(const mixfp4_comm* c, void** buffer) {
+    if (!c || !buffer) return MIXFP4_E_NULL;
+    *buffer = c->recv;
+    return MIXFP4_OK;
+}
+
+extern "C" int mixfp4_comm_open_local(mixfp4_comm* c, void* const* buffers) {
+    if (!c || !buffers) return MIXFP4_E_NULL;
+    if (c->opened) return MIXFP4_OK;
+    for (int r = 0; r < c->world; ++r) {
+        if (r == c->rank) continue;
+        if (!buffers[r]) return MIXFP4_E_NULL;
+        if (!aligned(buffers[r], 8)) return MIXFP4_E_ALIGN;
+        c->peer[r] = static_cast<uint2*>(buffers[r]);
+    }
+    c->opened = true;
+    c->local = true;
+    return MIXFP4_OK;
+}
+
 extern "C" int mixfp4_comm_destroy(mixfp4_comm* c) {
     if (!c) return MIXFP4_OK;
     for (int r = 0; r < c->world; ++r)
-        if (r != c->rank && c->peer[r]) cudaIpcCloseMemHandle(c->peer[r]);
+        if (!c->local && r != c->rank && c->peer[r]) cudaIpcCloseMemHandle(c->peer[r]);
     cudaFree(c->recv);
     cudaFree(c->words);
     delete c;

@@ -93,6 +93,19 @@ __device__ __forceinline__ void decode8_kl(uint32_t w, const uint4& t, uint32_t 
     p[3] = prmt(lo_b, hi_b, 0x7362u);
 }
 
+// Stream layout of the packed weight -- what the decode-shape kernels read fastest.  The weight is
+// cut into chunks of 16 rows x 128 K elements, each chunk one contiguous run of kChunkBytes:
+//   bytes    0 .. 1023   codes, row-major [16 rows][64 B], code words in the kernel-layout bit order;
+//   bytes 1024 .. 1151   scale bytes, row-major [16 rows][8 blocks], format bit in bit 7.
+// Chunks follow each other along K, then by row tile: chunk (tile, sub) starts at
+// (tile * kpad/128 + sub) * kChunkBytes.  Rows past N in the last tile hold zero codes and the
+// scale byte 0x01.  One cp.async.bulk moves a chunk; a warp's 16 x 128 step is exactly one chunk.
+constexpr uint32_t kChunkBytes = 1152, kChunkCodeBytes = 1024, kChunkRows = 16, kChunkK = 128;
+__host__ __device__ inline int64_t stream_tiles(int64_t rows) { return (rows + kChunkRows - 1) / kChunkRows; }
+__host__ __device__ inline int64_t stream_bytes(int64_t rows, int64_t k) {
+    return stream_tiles(rows) * (padded_k(k) / kChunkK) * kChunkBytes;
+}
+
 template <bool kKernelLayout>
 __device__ __forceinline__ void decode_word(uint32_t w, const uint4& t, uint32_t (&p)[4]) {
     if constexpr (kKernelLayout) decode8_kl(w, t, p);

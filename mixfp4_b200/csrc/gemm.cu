@@ -47,7 +47,7 @@ namespace mixfp4 {
 namespace {
 
 constexpr int BK = 64;                     // K elements per pipeline stage (one 128-byte swizzle row)
-constexpr int kDecodeWarps = 8;             // more transcoder warps were measured: no gain alone, a loss in CTA pairs           // two warps per scheduler were too few to hide the decode latency
+constexpr int kDecodeWarps = 8;             // more transcoder warps were measured: no gain alone, a loss in CTA pairs
 constexpr int kThreads = (3 + kDecodeWarps) * 32;   // x producer, MMA issuer, transcoders, code producer
 constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s: far beyond any legitimate wait
 constexpr uint32_t kMinSpins = 1u << 16;            // ... and at least this many polls
@@ -96,6 +96,8 @@ struct GemmArgs {
     int kt_per_split;           // K steps per CTA along grid.z (all of them without split K)
     float* partial;             // split K: fp32 partial sums [splits][m][ld_partial]
     int64_t ld_partial;
+    int stream_layout;          // `codes` is the chunk buffer of the stream layout (decode.cuh), `scales` unused
+    int subs;                   // chunks per row tile (kpad / 128)
 };
 
 // Sum of the split-K partials in split order (deterministic), converted to the output type.
@@ -169,6 +171,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+
+// Box of the stream layout's code bytes: coordinates (byte in a row's 64, row in the tile, chunk along K, row tile).
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2,
+                                            int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
 
@@ -390,7 +401,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                 const uint32_t ph = (kt / kWStages) & 1;
                 if (!mbar_wait(empty_w(s), ph ^ 1, ctx, 7)) break;
                 mbar_arrive_expect_tx(full_w(s), C::kWBytes);
-                tma_load_2d(base + C::kOffW + s * C::kWBytes, &tmap_w, full_w(s), (kt0 + kt) * (BK / 2), (int)n0);
+                if (a.stream_layout)
+                    tma_load_4d(base + C::kOffW + s * C::kWBytes, &tmap_w, full_w(s), ((kt0 + kt) & 1) * (BK / 2), 0,
+                                (kt0 + kt) >> 1, (int)(n0 >> 4));
+                else
+                    tma_load_2d(base + C::kOffW + s * C::kWBytes, &tmap_w, full_w(s), (kt0 + kt) * (BK / 2), (int)n0);
                 issued = kt + 1;
             }
             for (int kt = max(0, issued - kWStages); kt < issued; ++kt)
@@ -406,7 +421,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         const int row = dt / kTPR, part = dt % kTPR;    // tile row, which part of the K step
         const uint32_t last_row = (uint32_t)a.n - 1;
         const uint32_t grow = min(n0 + row, last_row);  // rows past N re-read the last row; never stored
-        const uint8_t* srow = a.scales + (size_t)grow * (a.kpad / 16);
+        // a row's 8 scale bytes per 128 K elements: 8 bytes apart in a scale row, one chunk apart in the stream layout
+        const uint8_t* srow = a.stream_layout
+            ? a.codes + (size_t)(grow >> 4) * a.subs * kChunkBytes + kChunkCodeBytes + (grow & 15) * 8
+            : a.scales + (size_t)grow * (a.kpad / 16);
+        const size_t sstep = a.stream_layout ? kChunkBytes : 8;
         const uint8_t* fptr = kKL ? a.scales : a.fmt + (size_t)grow * (a.kpad / 128);   // unused for the kernel layout
         const uint32_t lut_base = base + C::kOffLut;
         // destination of this thread's 16-byte chunks: row r, logical chunk c -> c ^ (r & 7)
@@ -437,7 +456,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         };
         // Scales: 8 bytes of a row cover two K steps.
         auto load_scale_pair = [&](int pair) -> uint2 {
-            return __ldg(reinterpret_cast<const uint2*>(srow) + pair);
+            return __ldg(reinterpret_cast<const uint2*>(srow + (size_t)pair * sstep));
         };
 
         uint32_t codes[kWords], ncodes[kWords];
@@ -783,7 +802,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_pair_kernel(const __grid_con
                 const uint32_t ph = (kt / kWStages) & 1;
                 if (!mbar_wait(empty_w(s), ph ^ 1, ctx, 7)) break;
                 mbar_arrive_expect_tx(full_w(s), C::kWBytes);
-                tma_load_2d(base + C::kOffW + s * C::kWBytes, &tmap_w, full_w(s), kt * (BK / 2), (int)nh0);
+                if (a.stream_layout)
+                    tma_load_4d(base + C::kOffW + s * C::kWBytes, &tmap_w, full_w(s), (kt & 1) * (BK / 2), 0, kt >> 1,
+                                (int)(nh0 >> 4));
+                else
+                    tma_load_2d(base + C::kOffW + s * C::kWBytes, &tmap_w, full_w(s), kt * (BK / 2), (int)nh0);
                 issued = kt + 1;
             }
             for (int kt = max(0, issued - kWStages); kt < issued; ++kt)
@@ -796,7 +819,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_pair_kernel(const __grid_con
         const int row = dt / kTPR, part = dt % kTPR;    // row of this CTA's half tile, part of the K step
         const uint32_t last_row = (uint32_t)a.n - 1;
         const uint32_t grow = min(nh0 + row, last_row);
-        const uint8_t* srow = a.scales + (size_t)grow * (a.kpad / 16);
+        const uint8_t* srow = a.stream_layout
+            ? a.codes + (size_t)(grow >> 4) * a.subs * kChunkBytes + kChunkCodeBytes + (grow & 15) * 8
+            : a.scales + (size_t)grow * (a.kpad / 16);
+        const size_t sstep = a.stream_layout ? kChunkBytes : 8;
         const uint8_t* fptr = kKL ? a.scales : a.fmt + (size_t)grow * (a.kpad / 128);
         const uint32_t lut_base = base + C::kOffLut;
         const uint32_t row_off = (row >> 3) * 1024u + (row & 7) * 128u;
@@ -816,7 +842,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_pair_kernel(const __grid_con
             if (lane == 0) mbar_arrive(empty_w(ws));
             return true;
         };
-        auto load_scale_pair = [&](int pair) -> uint2 { return __ldg(reinterpret_cast<const uint2*>(srow) + pair); };
+        auto load_scale_pair = [&](int pair) -> uint2 { return __ldg(reinterpret_cast<const uint2*>(srow + (size_t)pair * sstep)); };
 
         uint32_t codes[kWords], ncodes[kWords];
         bool ok = load_codes(codes, 0);
@@ -898,6 +924,28 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
+// Tensor map of the packed codes; a box is one K step (32 bytes per row) of `box_rows` weight rows.
+// Row-major layouts: the byte matrix [n, kpad/2].  Stream layout: (64 code bytes of a row in a chunk,
+// 16 rows, chunks along K, row tiles), whose box of box_rows/16 tiles lands in shared memory in the
+// same row-major order.
+bool encode_code_map(EncodeTiledFn encode, CUtensorMap* map, const GemmArgs& a, int box_rows) {
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    if (a.stream_layout) {
+        const cuuint64_t dims[4] = {64, kChunkRows, (cuuint64_t)a.subs, (cuuint64_t)stream_tiles(a.n)};
+        const cuuint64_t strides[3] = {64, kChunkBytes, (cuuint64_t)a.subs * kChunkBytes};
+        const cuuint32_t box[4] = {BK / 2, kChunkRows, 1, (cuuint32_t)(box_rows / (int)kChunkRows)};
+        return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<uint8_t*>(a.codes), dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    }
+    const cuuint64_t dims[2] = {(cuuint64_t)(a.kpad / 2), (cuuint64_t)a.n};
+    const cuuint64_t strides[1] = {(cuuint64_t)(a.kpad / 2)};
+    const cuuint32_t box[2] = {BK / 2, (cuuint32_t)box_rows};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(a.codes), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 int64_t x_staging_bytes(int64_t m, int64_t k) { return m * ((k + 7) / 8 * 8) * 2; }
 constexpr int64_t kAmaxSlotBytes = 256;
 
@@ -917,13 +965,7 @@ int launch_gemm(const void* xa, int64_t lda, const GemmArgs& a, cudaStream_t st)
     if (cr != CUDA_SUCCESS) return record_error_text("cuTensorMapEncodeTiled failed");
     // the packed codes as a byte matrix [n, kpad/2]; a box is one K step (32 bytes) of BN rows
     CUtensorMap tmap_w;
-    const cuuint64_t wdims[2] = {(cuuint64_t)(a.kpad / 2), (cuuint64_t)a.n};
-    const cuuint64_t wstrides[1] = {(cuuint64_t)(a.kpad / 2)};
-    const cuuint32_t wbox[2] = {BK / 2, (cuuint32_t)C::BN};
-    const CUresult cw = encode(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(a.codes), wdims, wstrides,
-                               wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (cw != CUDA_SUCCESS) return record_error_text("cuTensorMapEncodeTiled failed for the code matrix");
+    if (!encode_code_map(encode, &tmap_w, a, C::BN)) return record_error_text("cuTensorMapEncodeTiled failed for the code matrix");
     static unsigned long long configured = 0;          // one per instantiation, one bit per device
     if (const int rc = ensure_dynamic_smem(gemm_kernel<kMT, kBN, kKL>, (int)C::kSmemBytes, configured)) return rc;
     const int total_kt = static_cast<int>(a.kpad / BK);
@@ -1001,13 +1043,7 @@ int launch_gemm_pair(const void* xa, int64_t lda, const GemmArgs& args, cudaStre
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return record_error_text("cuTensorMapEncodeTiled failed");
-    const cuuint64_t wdims[2] = {(cuuint64_t)(a.kpad / 2), (cuuint64_t)a.n};
-    const cuuint64_t wstrides[1] = {(cuuint64_t)(a.kpad / 2)};
-    const cuuint32_t wbox[2] = {BK / 2, (cuuint32_t)C::BNH};
-    if (encode(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(a.codes), wdims, wstrides, wbox, estr,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return record_error_text("cuTensorMapEncodeTiled failed for the code matrix");
+    if (!encode_code_map(encode, &tmap_w, a, C::BNH)) return record_error_text("cuTensorMapEncodeTiled failed for the code matrix");
     static unsigned long long configured = 0;          // one per instantiation, one bit per device
     if (const int rc = ensure_dynamic_smem(gemm_pair_kernel<kMT, kKL>, (int)C::kSmemBytes, configured)) return rc;
     const int64_t pairs = (a.m + 2 * C::BM - 1) / (2 * C::BM);
@@ -1033,6 +1069,23 @@ int launch_gemm_pair(const void* xa, int64_t lda, const GemmArgs& args, cudaStre
 
 using namespace mixfp4;
 
+// Argument checks shared by every GEMM entry point; they run before anything is enqueued.
+static int check_gemm_args(const void* x, int64_t m, int64_t ldx, const uint8_t* codes, const uint8_t* scales,
+                           const uint8_t* fmt, const float* global_scale, int64_t n, int64_t k, int layout,
+                           const void* lut, int rotation_block, const void* y, int out_dtype, int64_t ldy) {
+    if (layout != MIXFP4_LAYOUT_CANONICAL && layout != MIXFP4_LAYOUT_KERNEL && layout != MIXFP4_LAYOUT_STREAM)
+        return MIXFP4_E_MODE;
+    const bool streamed = layout == MIXFP4_LAYOUT_STREAM;
+    if (!x || !codes || (!scales && !streamed) || (!fmt && layout == MIXFP4_LAYOUT_CANONICAL) || !global_scale || !y)
+        return MIXFP4_E_NULL;
+    if (m <= 0 || n <= 0 || k <= 0 || ldx < k || ldy < n) return MIXFP4_E_SHAPE;
+    if (m > 0x7fffffffLL || n > 0x7fffffffLL || k > 0x7fffffffLL) return MIXFP4_E_SHAPE;
+    if (out_dtype != MIXFP4_F32 && out_dtype != MIXFP4_BF16) return MIXFP4_E_DTYPE;
+    if (rotation_block != 0 && rotation_block != 128) return MIXFP4_E_MODE;
+    if (!aligned(codes, 16) || (!streamed && !aligned(scales, 8)) || (lut && !aligned(lut, 16))) return MIXFP4_E_ALIGN;
+    return MIXFP4_OK;
+}
+
 extern "C" int64_t mixfp4_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k) {
     if (m <= 0 || k <= 0) return 0;
     int64_t bytes = (x_staging_bytes(m, k) + 255) / 256 * 256;
@@ -1048,13 +1101,9 @@ extern "C" int mixfp4_gemm(const void* x, int64_t m, int64_t ldx, const uint8_t*
                            const void* lut, int rotation_block, void* y, int out_dtype, int64_t ldy, void* workspace,
                            int64_t workspace_bytes, int* status, int flags, void* stream) {
     (void)flags;
-    if (layout != MIXFP4_LAYOUT_CANONICAL && layout != MIXFP4_LAYOUT_KERNEL) return MIXFP4_E_MODE;
-    if (!x || !codes || !scales || (!fmt && layout == MIXFP4_LAYOUT_CANONICAL) || !global_scale || !y) return MIXFP4_E_NULL;
-    if (m <= 0 || n <= 0 || k <= 0 || ldx < k || ldy < n) return MIXFP4_E_SHAPE;
-    if (m > 0x7fffffffLL || n > 0x7fffffffLL || k > 0x7fffffffLL) return MIXFP4_E_SHAPE;
-    if (out_dtype != MIXFP4_F32 && out_dtype != MIXFP4_BF16) return MIXFP4_E_DTYPE;
-    if (rotation_block != 0 && rotation_block != 128) return MIXFP4_E_MODE;
-    if (!aligned(codes, 16) || !aligned(scales, 8) || (lut && !aligned(lut, 16))) return MIXFP4_E_ALIGN;
+    if (const int rc = check_gemm_args(x, m, ldx, codes, scales, fmt, global_scale, n, k, layout, lut, rotation_block, y,
+                                       out_dtype, ldy))
+        return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 
     // The TMA descriptor needs a 16-byte aligned base and row pitch; the rotation needs a
@@ -1082,6 +1131,7 @@ extern "C" int mixfp4_gemm(const void* x, int64_t m, int64_t ldx, const uint8_t*
     a.m = m; a.n = n; a.k = k; a.kpad = padded_k(k);
     a.y = y; a.out_dtype = out_dtype; a.ldy = ldy; a.status = status;
     a.kt_per_split = static_cast<int>(a.kpad / BK); a.partial = nullptr; a.ld_partial = 0; a.tma_store = 0;
+    a.stream_layout = layout == MIXFP4_LAYOUT_STREAM; a.subs = static_cast<int>(a.kpad / kChunkK);
     const GemmPlan plan = plan_gemm(m, n, k);
     const int mt = plan.mt, bn = plan.bn;
     if (plan.splits > 1) {     // split K needs room for the partial sums after the staging area; without it: one CTA per tile
@@ -1093,7 +1143,7 @@ extern "C" int mixfp4_gemm(const void* x, int64_t m, int64_t ldx, const uint8_t*
             a.ld_partial = partial_ld(n);
         }
     }
-    const bool kl = layout == MIXFP4_LAYOUT_KERNEL;
+    const bool kl = layout != MIXFP4_LAYOUT_CANONICAL;       // the stream layout keeps the kernel layout's code words
     // More than 256 tokens and enough tiles to occupy most SMs: CTA pairs (two SMs share each decoded
     // weight tile; measured 1.25-1.3 x the single-CTA kernel at M >= 2048, slower below about 100 CTAs).
     // Pairs of 256-row CTAs unless pairs of 128-row CTAs pad the token rows noticeably less.  With at
@@ -1117,10 +1167,10 @@ extern "C" int mixfp4_gemm_a4(const void* x, int64_t m, int64_t ldx, const uint8
                               const uint8_t* fmt, const float* global_scale, int64_t n, int64_t k, int layout,
                               const void* lut, int rotation_block, int act_mode, void* y, int out_dtype, int64_t ldy,
                               void* workspace, int64_t workspace_bytes, int* status, int flags, void* stream) {
-    if (!x || !codes || !scales || !global_scale || !y) return MIXFP4_E_NULL;
-    if (m <= 0 || n <= 0 || k <= 0 || ldx < k || ldy < n) return MIXFP4_E_SHAPE;
-    if (m > 0x7fffffffLL || n > 0x7fffffffLL || k > 0x7fffffffLL) return MIXFP4_E_SHAPE;
-    if (rotation_block != 0 && rotation_block != 128) return MIXFP4_E_MODE;
+    if (const int rc = check_gemm_args(x, m, ldx, codes, scales, fmt, global_scale, n, k, layout, lut, rotation_block, y,
+                                       out_dtype, ldy))
+        return rc;
+    if (act_mode < MIXFP4_MODE_ORACLE16 || act_mode > MIXFP4_MODE_ALL_E0M3) return MIXFP4_E_MODE;
     const int64_t total = mixfp4_gemm_workspace_bytes(m, n, k);
     if (!workspace || workspace_bytes < total) return MIXFP4_E_WORKSPACE;
     if (!aligned(workspace, 16)) return MIXFP4_E_ALIGN;
@@ -1179,8 +1229,11 @@ extern "C" int mixfp4_gemm_h128_static(const void* x, int64_t m, int64_t ldx, co
                                        const uint8_t* scales, const uint8_t* fmt, const float* global_scale,
                                        int64_t n, int64_t k, int layout, const void* lut, void* y, int out_dtype,
                                        int64_t ldy, int* status, void* stream) {
-    if (!x || !codes || !scales || !global_scale || !y) return MIXFP4_E_NULL;
-    if (m <= 0 || n <= 0 || k <= 0 || ldx < k || ldy < n) return MIXFP4_E_SHAPE;
+    // every argument is checked before the first kernel is enqueued: a rejected call leaves the
+    // shared array untouched (the sizes are below 2^31 here, so the product cannot wrap)
+    if (const int rc = check_gemm_args(x, m, ldx, codes, scales, fmt, global_scale, n, k, layout, lut, 128, y, out_dtype,
+                                       ldy))
+        return rc;
     const int64_t lda = (k + 7) / 8 * 8;
     if (m * lda * 2 > kStaticScratchBytes) return MIXFP4_E_TOO_LARGE;
     void* scratch = nullptr;

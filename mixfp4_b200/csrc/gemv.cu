@@ -33,86 +33,10 @@
 // 4-bit codes (one 32-bit word) become four bf16x2 registers with byte permutes
 // (decode.cuh).  The accumulation is the tensor core's fp32.
 
-#include "common.cuh"
-#include "decode.cuh"
+#include "gemv_common.cuh"
 
 namespace mixfp4 {
 namespace {
-
-constexpr int kRowsPerCta = 16;
-constexpr int kStepK = 128;               // K elements one warp consumes per step
-// The decode table is kept kLutRep times in shared memory, lane t of a quad reading copy t: lanes
-// of a quad then never collide on a bank, which removes most conflicts of the random lookups.
-constexpr int kLutRep = 1;
-constexpr int kLutBytes = 4096 * kLutRep;
-
-struct GemvArgs {
-    const __nv_bfloat16* x;
-    int64_t m, ldx;
-    const uint8_t* codes;
-    const uint8_t* scales;
-    const uint8_t* fmt;
-    const float* global_scale;
-    const uint4* lut;                      // optional prebuilt decode table
-    int64_t n, k, kpad;
-    void* y;
-    int out_dtype;
-    int64_t ldy;
-    bool x_vec;                            // x rows are 16-byte aligned and K % 8 == 0
-};
-
-__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async16_stream(uint32_t dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int kPending>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory"); }
-
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-    return v;
-}
-// Predicated load: lanes with pred == false keep the previous contents of v.
-__device__ __forceinline__ void lds128_if(uint4& v, uint32_t addr, bool pred) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %5, 0;\n\t"
-        "@p ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n\t}"
-        : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)
-        : "r"(addr), "r"((uint32_t)pred));
-}
-__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
-    uint16_t v;
-    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ void sts128(uint32_t addr, const uint4& v) {
-    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-}
-
-// One ring stage of a warp: x [chunk 0..3][batch row][t] 16 B (m * 256 bytes), then the codes
-// [row half][lane] 16 B, then the scales [row 0..15] 8 B.
-__host__ __device__ inline uint32_t stage_bytes(int64_t m, bool x_resident) {
-    return (x_resident ? 0u : (uint32_t)m * 256u) + 1024u + 128u;
-}
-// With x resident in shared memory (small M*K) a row of x takes kpad*2 + 16 bytes (the pad
-// staggers the banks of different batch rows).
-__host__ __device__ inline uint32_t xres_row_bytes(int64_t kpad) { return (uint32_t)kpad * 2u + 16u; }
 
 template <int kWarps, int kNTiles, bool kKL, int kU, int kDepth, bool kXRes, int kMinCtas>
 __global__ void __launch_bounds__(kWarps * 32, kMinCtas) gemv_kernel(const GemvArgs a) {
@@ -161,6 +85,13 @@ __global__ void __launch_bounds__(kWarps * 32, kMinCtas) gemv_kernel(const GemvA
     const uint8_t* pc[2] = {a.codes, a.codes};
     const uint8_t* ps = a.scales;
     auto set_rows = [&]() {     // rows past N re-read the last row; their sums are never stored
+        if (a.stream) {         // chunk (tile, sub): codes [16 rows][64 B], then scales [16 rows][8 B]
+            const uint8_t* tb = a.codes + (size_t)p_tile * subs * kChunkBytes;
+            pc[0] = tb + lane * 16;
+            pc[1] = tb + 512 + lane * 16;
+            ps = tb + kChunkCodeBytes + (g + 8 * t) * 8;
+            return;
+        }
         const uint32_t row0 = (uint32_t)p_tile * kRowsPerCta;
         const uint32_t r0 = min(row0 + g, last_row), r1 = min(row0 + g + 8, last_row);
         pc[0] = a.codes + (size_t)r0 * ld_codes + t * 16;
@@ -176,8 +107,8 @@ __global__ void __launch_bounds__(kWarps * 32, kMinCtas) gemv_kernel(const GemvA
             const uint32_t base = ring + slot * slot_bytes + j * stage;
 #pragma unroll
             for (int h = 0; h < 2; ++h)
-                cp_async16_stream(base + off_codes + h * 512 + lane * 16, pc[h] + (size_t)sub * 64);
-            if (t < 2) cp_async8(base + off_scales + (g + 8 * t) * 8, ps + (size_t)sub * 8);
+                cp_async16_stream(base + off_codes + h * 512 + lane * 16, pc[h] + (size_t)sub * a.code_step);
+            if (t < 2) cp_async8(base + off_scales + (g + 8 * t) * 8, ps + (size_t)sub * a.scale_step);
         }
     };
     auto issue_x = [&](int step, uint32_t slot) {
@@ -423,20 +354,6 @@ struct GemvSegment {
     int n;
     int tile_end;                          // first tile index after this segment's tiles
 };
-// Fused all-reduce of a row-parallel GEMV (every rank holds a K shard of the same N rows): the
-// partial sums of a row tile go straight into every peer's receive buffer as 8-byte packets
-// {fp32 bits, sequence number}, the tile's owner threads then poll their own buffer and add the
-// world partials in rank order (identical bits on every rank).  See comm.cu for the buffers.
-struct AllReduceArgs {
-    int rank, world;
-    int64_t slot_packets;        // packets per source rank and parity
-    uint2* recv;                 // this rank's buffer
-    uint2* peer[8];              // every rank's buffer as seen from this GPU
-    uint32_t* words;             // [0] sequence number, [1] finished-CTA counter
-    int* status;                 // optional device word: nonzero after an expired wait
-};
-constexpr uint64_t kPeerWaitLimitNs = 2000000000ull;   // 2 s (and at least 2^16 polls): far beyond any legitimate wait
-
 struct GemvSmArgs {
     const __nv_bfloat16* x;
     int64_t ldx, k, kpad;
@@ -449,20 +366,6 @@ constexpr uint32_t kStageSm = 1024u + 128u;          // codes [row half][lane] 1
 
 __host__ __device__ inline uint32_t red_bytes_sm(int groups, int gw, int64_t m) {
     return (uint32_t)(groups * 2 * gw * kRowsPerCta * (int)m * 4);
-}
-
-__device__ __forceinline__ void st_packet(uint2* p, uint32_t value, uint32_t flag) {
-    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(value), "r"(flag) : "memory");
-}
-__device__ __forceinline__ uint2 ld_packet(const uint2* p) {
-    uint2 v;
-    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ uint64_t gemv_timer_ns() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
 }
 
 // kNT: MMA column tiles (8 batch rows each).  kLutRep: copies of the decode table (8: no bank
@@ -680,7 +583,7 @@ __global__ void __launch_bounds__(kGroups * kGW * 32, 1) gemv_sm_kernel(const Ge
                             const uint64_t t0 = gemv_timer_ns();
                             uint32_t spins = 0;
                             while ((pk = ld_packet(q)).y != flag) {
-                                if ((++spins & 63u) == 0 && spins > (1u << 16) && gemv_timer_ns() - t0 > kPeerWaitLimitNs) {
+                                if ((++spins & 63u) == 0 && spins > 4096u && gemv_timer_ns() - t0 > a.ar.wait_ns) {
                                     if (a.ar.status) atomicCAS(a.ar.status, 0, 100 + src);
                                     break;
                                 }
@@ -779,12 +682,22 @@ using namespace mixfp4;
 extern "C" int mixfp4_gemv(const void* x, int64_t m, int64_t ldx, const uint8_t* codes, const uint8_t* scales,
                            const uint8_t* fmt, const float* global_scale, int64_t n, int64_t k, int layout,
                            const void* lut, void* y, int out_dtype, int64_t ldy, int flags, void* stream) {
-    if (layout != MIXFP4_LAYOUT_CANONICAL && layout != MIXFP4_LAYOUT_KERNEL) return MIXFP4_E_MODE;
-    if (!x || !codes || !scales || (!fmt && layout == MIXFP4_LAYOUT_CANONICAL) || !global_scale || !y) return MIXFP4_E_NULL;
+    if (layout != MIXFP4_LAYOUT_CANONICAL && layout != MIXFP4_LAYOUT_KERNEL && layout != MIXFP4_LAYOUT_STREAM)
+        return MIXFP4_E_MODE;
+    const bool streamed = layout == MIXFP4_LAYOUT_STREAM;
+    if (!x || !codes || (!scales && !streamed) || (!fmt && layout == MIXFP4_LAYOUT_CANONICAL) || !global_scale || !y)
+        return MIXFP4_E_NULL;
     if (m < 1 || m > 16 || n <= 0 || k <= 0 || ldx < k || ldy < n) return MIXFP4_E_SHAPE;
     if (out_dtype != MIXFP4_F32 && out_dtype != MIXFP4_BF16) return MIXFP4_E_DTYPE;
-    if (!aligned(codes, 16) || !aligned(scales, 8) || !aligned(x, 2) || (lut && !aligned(lut, 16))) return MIXFP4_E_ALIGN;
+    if (!aligned(codes, 16) || (!streamed && !aligned(scales, 8)) || !aligned(x, 2) || (lut && !aligned(lut, 16)))
+        return MIXFP4_E_ALIGN;
     if (n > 0x7fffffffLL - 16) return MIXFP4_E_SHAPE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (streamed) {
+        const mixfp4_gemv_segment seg = {codes, nullptr, global_scale, lut, y, ldy, n};
+        const int rc = gemv_stream(x, m, ldx, k, &seg, 1, out_dtype, flags, nullptr, nullptr, st);
+        if (rc != MIXFP4_E_SHAPE) return rc;     // x too large for shared memory: the kernel below stages it
+    }
     GemvArgs a;
     a.x = static_cast<const __nv_bfloat16*>(x);
     a.m = m; a.ldx = ldx;
@@ -793,18 +706,28 @@ extern "C" int mixfp4_gemv(const void* x, int64_t m, int64_t ldx, const uint8_t*
     a.n = n; a.k = k; a.kpad = padded_k(k);
     a.y = y; a.out_dtype = out_dtype; a.ldy = ldy;
     a.x_vec = aligned(x, 16) && (ldx % 8 == 0) && (k % 8 == 0);
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    a.stream = streamed;
+    a.code_step = streamed ? kChunkBytes : 64u;
+    a.scale_step = streamed ? kChunkBytes : 8u;
+    if (streamed) {
+        if (a.m > 8) return launch<8, 2, true, 1, 3, false, 2>(a, flags, st);
+        return launch<8, 1, true, 1, 3, false, 2>(a, flags, st);
+    }
     return layout == MIXFP4_LAYOUT_KERNEL ? dispatch<true>(a, flags, st) : dispatch<false>(a, flags, st);
 }
 
 extern "C" int mixfp4_gemv_grouped(const void* x, int64_t m, int64_t ldx, int64_t k,
-                                   const mixfp4_gemv_segment* segments, int count, int out_dtype, int flags,
-                                   void* stream) {
+                                   const mixfp4_gemv_segment* segments, int count, int layout, int out_dtype,
+                                   int flags, void* stream) {
+    if (layout != MIXFP4_LAYOUT_KERNEL && layout != MIXFP4_LAYOUT_STREAM) return MIXFP4_E_MODE;
     if (!x || !segments) return MIXFP4_E_NULL;
     if (count < 1 || count > kMaxSegments) return MIXFP4_E_SHAPE;
     if (m < 1 || m > 16 || k <= 0 || ldx < k) return MIXFP4_E_SHAPE;
     if (out_dtype != MIXFP4_F32 && out_dtype != MIXFP4_BF16) return MIXFP4_E_DTYPE;
     if (!aligned(x, 2)) return MIXFP4_E_ALIGN;
+    if (layout == MIXFP4_LAYOUT_STREAM)
+        return gemv_stream(x, m, ldx, k, segments, count, out_dtype, flags, nullptr, nullptr,
+                           static_cast<cudaStream_t>(stream));   // MIXFP4_E_SHAPE: x does not fit
     GemvSmArgs g = {};
     g.x = static_cast<const __nv_bfloat16*>(x);
     g.ldx = ldx; g.k = k; g.kpad = padded_k(k);
@@ -829,12 +752,19 @@ extern "C" int mixfp4_gemv_grouped(const void* x, int64_t m, int64_t ldx, int64_
 
 extern "C" int mixfp4_gemv_allreduce(const mixfp4_comm* comm, const void* x, int64_t m, int64_t ldx,
                                      const uint8_t* codes, const uint8_t* scales, const float* global_scale,
-                                     const void* lut, int64_t n, int64_t k, void* y, int out_dtype, int64_t ldy,
-                                     int* status, int flags, void* stream) {
-    if (!comm || !x || !codes || !scales || !global_scale || !y) return MIXFP4_E_NULL;
+                                     const void* lut, int64_t n, int64_t k, int layout, void* y, int out_dtype,
+                                     int64_t ldy, int* status, int flags, void* stream) {
+    if (layout != MIXFP4_LAYOUT_KERNEL && layout != MIXFP4_LAYOUT_STREAM) return MIXFP4_E_MODE;
+    const bool streamed = layout == MIXFP4_LAYOUT_STREAM;
+    if (!comm || !x || !codes || (!scales && !streamed) || !global_scale || !y) return MIXFP4_E_NULL;
     if (m < 1 || m > 8 || n <= 0 || k <= 0 || ldx < k || ldy < n || n > 0x7fffffffLL - 16) return MIXFP4_E_SHAPE;
     if (out_dtype != MIXFP4_F32 && out_dtype != MIXFP4_BF16) return MIXFP4_E_DTYPE;
-    if (!aligned(codes, 16) || !aligned(scales, 8) || !aligned(x, 2) || (lut && !aligned(lut, 16))) return MIXFP4_E_ALIGN;
+    if (!aligned(codes, 16) || (!streamed && !aligned(scales, 8)) || !aligned(x, 2) || (lut && !aligned(lut, 16)))
+        return MIXFP4_E_ALIGN;
+    if (streamed) {
+        const mixfp4_gemv_segment seg = {codes, nullptr, global_scale, lut, y, ldy, n};
+        return gemv_stream(x, m, ldx, k, &seg, 1, out_dtype, flags, comm, status, static_cast<cudaStream_t>(stream));
+    }
     GemvSmArgs g = {};
     g.x = static_cast<const __nv_bfloat16*>(x);
     g.ldx = ldx; g.k = k; g.kpad = padded_k(k);
@@ -849,6 +779,7 @@ extern "C" int mixfp4_gemv_allreduce(const mixfp4_comm* comm, const void* x, int
     if (rc != MIXFP4_OK) return rc;
     if (m * n > g.ar.slot_packets) return MIXFP4_E_TOO_LARGE;
     g.ar.status = status;
+    g.ar.wait_ns = wait_limit_ns();
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return g.ntiles >= 2 * 148 ? launch_sm<3, 8, 4, true>(g, flags, st) : launch_sm<2, 16, 3, true>(g, flags, st);
 }

@@ -405,7 +405,8 @@ __global__ void __launch_bounds__(kThreads, 3) quantize_kernel(const QuantArgs a
     }
 }
 
-template <typename T, bool kKL>
+// kLayout: MIXFP4_LAYOUT_CANONICAL, _KERNEL or _STREAM (codes = the chunk buffer, scales unused).
+template <typename T, int kLayout>
 __global__ void __launch_bounds__(kThreads) dequant_kernel(const uint8_t* __restrict__ codes,
                                                            const uint8_t* __restrict__ scales,
                                                            const uint8_t* __restrict__ fmt,
@@ -417,8 +418,16 @@ __global__ void __launch_bounds__(kThreads) dequant_kernel(const uint8_t* __rest
     if (row >= rows) return;
     const int64_t blk = t - row * groups;
     const float gs = *global_scale;
-    uint2 c = __ldg(reinterpret_cast<const uint2*>(codes + row * blocks_pad * 8 + blk * 8));
-    const uint32_t sbyte = __ldg(scales + row * blocks_pad + blk);
+    constexpr bool kKL = kLayout != MIXFP4_LAYOUT_CANONICAL;
+    const uint8_t* cptr = codes + row * blocks_pad * 8 + blk * 8;
+    const uint8_t* sptr = scales + row * blocks_pad + blk;
+    if constexpr (kLayout == MIXFP4_LAYOUT_STREAM) {
+        const uint8_t* chunk = codes + ((row >> 4) * (blocks_pad >> 3) + (blk >> 3)) * kChunkBytes;
+        cptr = chunk + (row & 15) * 64 + (blk & 7) * 8;
+        sptr = chunk + kChunkCodeBytes + (row & 15) * 8 + (blk & 7);
+    }
+    uint2 c = __ldg(reinterpret_cast<const uint2*>(cptr));
+    const uint32_t sbyte = __ldg(sptr);
     bool e0;
     if constexpr (kKL) {
         c.x = codes_from_kernel_layout(c.x);
@@ -488,6 +497,58 @@ __global__ void __launch_bounds__(kThreads) repack_kernel(const uint8_t* __restr
     if constexpr (!kToKernel) {
         const uint32_t bits = __ballot_sync(0xffffffffu, fbit);
         const int64_t col = chunk * 4 + lane;
+        if (lane < 4 && col < blocks_pad / 8) fmt_out[row * (blocks_pad / 8) + col] = static_cast<uint8_t>(bits >> (8 * lane));
+    }
+}
+
+// canonical <-> stream layout (decode.cuh).  Same split as above; the grid also covers the rows that
+// pad the last 16-row tile, which are written as zero codes with the scale byte 0x01.
+template <bool kToStream>
+__global__ void __launch_bounds__(kThreads) repack_stream_kernel(const uint8_t* __restrict__ codes,
+                                                                 const uint8_t* __restrict__ scales,
+                                                                 const uint8_t* __restrict__ fmt,
+                                                                 uint8_t* __restrict__ chunks, int64_t rows,
+                                                                 int64_t rows_pad, int64_t blocks_pad, int64_t groups32,
+                                                                 uint8_t* __restrict__ codes_out,
+                                                                 uint8_t* __restrict__ scales_out,
+                                                                 uint8_t* __restrict__ fmt_out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t)blockIdx.x * kWarpsPerCta + __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);   // provably warp-uniform
+    const int64_t row = warp / groups32;
+    if (row >= (kToStream ? rows_pad : rows)) return;
+    const int64_t blk = (warp - row * groups32) * 32 + lane;
+    const bool stored = blk < blocks_pad;
+    uint8_t* chunk = chunks + ((row >> 4) * (blocks_pad >> 3) + (blk >> 3)) * kChunkBytes;
+    uint8_t* cptr = chunk + (row & 15) * 64 + (blk & 7) * 8;
+    uint8_t* sptr = chunk + kChunkCodeBytes + (row & 15) * 8 + (blk & 7);
+    bool fbit = false;
+    if (stored) {
+        if constexpr (kToStream) {
+            uint2 c = make_uint2(0u, 0u);
+            uint32_t sb = 0x01u;
+            if (row < rows) {
+                c = __ldg(reinterpret_cast<const uint2*>(codes + row * blocks_pad * 8 + blk * 8));
+                sb = __ldg(scales + row * blocks_pad + blk);
+                fbit = (__ldg(fmt + row * (blocks_pad / 8) + (blk >> 3)) >> (blk & 7)) & 1;
+                c.x = codes_to_kernel_layout(c.x);
+                c.y = codes_to_kernel_layout(c.y);
+                sb = (sb & 0x7fu) | (fbit ? 0x80u : 0u);
+            }
+            *reinterpret_cast<uint2*>(cptr) = c;
+            *sptr = static_cast<uint8_t>(sb);
+        } else {
+            uint2 c = *reinterpret_cast<const uint2*>(cptr);
+            const uint32_t sb = *sptr;
+            fbit = (sb >> 7) & 1;
+            c.x = codes_from_kernel_layout(c.x);
+            c.y = codes_from_kernel_layout(c.y);
+            *reinterpret_cast<uint2*>(codes_out + row * blocks_pad * 8 + blk * 8) = c;
+            scales_out[row * blocks_pad + blk] = static_cast<uint8_t>(sb & 0x7fu);
+        }
+    }
+    if constexpr (!kToStream) {
+        const uint32_t bits = __ballot_sync(0xffffffffu, fbit);
+        const int64_t col = (warp - row * groups32) * 4 + lane;
         if (lane < 4 && col < blocks_pad / 8) fmt_out[row * (blocks_pad / 8) + col] = static_cast<uint8_t>(bits >> (8 * lane));
     }
 }
@@ -638,8 +699,11 @@ extern "C" int mixfp4_fake_quantize(const void* x, int dtype, int64_t rows, int6
 extern "C" int mixfp4_dequant(const uint8_t* codes, const uint8_t* scales, const uint8_t* fmt,
                               const float* global_scale, int64_t rows, int64_t k, int layout, void* out,
                               int out_dtype, int64_t ldo, void* stream) {
-    if (layout != MIXFP4_LAYOUT_CANONICAL && layout != MIXFP4_LAYOUT_KERNEL) return MIXFP4_E_MODE;
-    if (!codes || !scales || (!fmt && layout == MIXFP4_LAYOUT_CANONICAL) || !global_scale || !out) return MIXFP4_E_NULL;
+    if (layout != MIXFP4_LAYOUT_CANONICAL && layout != MIXFP4_LAYOUT_KERNEL && layout != MIXFP4_LAYOUT_STREAM)
+        return MIXFP4_E_MODE;
+    if (!codes || (!scales && layout != MIXFP4_LAYOUT_STREAM) || (!fmt && layout == MIXFP4_LAYOUT_CANONICAL) ||
+        !global_scale || !out)
+        return MIXFP4_E_NULL;
     if (rows <= 0 || k <= 0 || ldo < k) return MIXFP4_E_SHAPE;
     if (out_dtype < MIXFP4_BF16 || out_dtype > MIXFP4_F32) return MIXFP4_E_DTYPE;
     if (!aligned(codes, 8)) return MIXFP4_E_ALIGN;
@@ -648,14 +712,14 @@ extern "C" int mixfp4_dequant(const uint8_t* codes, const uint8_t* scales, const
     if (ctas > 0x7fffffffLL) return MIXFP4_E_SHAPE;
     const bool vec = rows_vectorizable(out, ldo, out_dtype);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define MIXFP4_LAUNCH_DEQUANT_L(T, L)                                                                        \
+    dequant_kernel<T, L><<<(unsigned)ctas, kThreads, 0, st>>>(codes, scales, fmt, global_scale, rows, k, groups, \
+                                                              blocks_pad, static_cast<T*>(out), ldo, vec)
 #define MIXFP4_LAUNCH_DEQUANT(T)                                                                             \
     do {                                                                                                    \
-        if (layout == MIXFP4_LAYOUT_KERNEL)                                                                 \
-            dequant_kernel<T, true><<<(unsigned)ctas, kThreads, 0, st>>>(codes, scales, fmt, global_scale, rows, k, \
-                                                                         groups, blocks_pad, static_cast<T*>(out), ldo, vec); \
-        else                                                                                                \
-            dequant_kernel<T, false><<<(unsigned)ctas, kThreads, 0, st>>>(codes, scales, fmt, global_scale, rows, k, \
-                                                                          groups, blocks_pad, static_cast<T*>(out), ldo, vec); \
+        if (layout == MIXFP4_LAYOUT_STREAM) MIXFP4_LAUNCH_DEQUANT_L(T, MIXFP4_LAYOUT_STREAM);               \
+        else if (layout == MIXFP4_LAYOUT_KERNEL) MIXFP4_LAUNCH_DEQUANT_L(T, MIXFP4_LAYOUT_KERNEL);          \
+        else MIXFP4_LAUNCH_DEQUANT_L(T, MIXFP4_LAYOUT_CANONICAL);                                           \
     } while (0)
     switch (out_dtype) {
         case MIXFP4_BF16: MIXFP4_LAUNCH_DEQUANT(__nv_bfloat16); break;
@@ -663,7 +727,40 @@ extern "C" int mixfp4_dequant(const uint8_t* codes, const uint8_t* scales, const
         default: MIXFP4_LAUNCH_DEQUANT(float);
     }
 #undef MIXFP4_LAUNCH_DEQUANT
+#undef MIXFP4_LAUNCH_DEQUANT_L
     return check_launch("dequant_kernel");
+}
+
+extern "C" int64_t mixfp4_stream_bytes(int64_t rows, int64_t k) {
+    return rows > 0 && k > 0 ? stream_bytes(rows, k) : 0;
+}
+
+extern "C" int mixfp4_repack_stream(const uint8_t* codes, const uint8_t* scales, const uint8_t* fmt, int64_t rows,
+                                    int64_t k, uint8_t* chunks, void* stream) {
+    if (!codes || !scales || !fmt || !chunks) return MIXFP4_E_NULL;
+    if (rows <= 0 || k <= 0) return MIXFP4_E_SHAPE;
+    if (!aligned(codes, 8) || !aligned(chunks, 16)) return MIXFP4_E_ALIGN;
+    const int64_t blocks_pad = padded_k(k) / kGroup, groups32 = (blocks_pad + 31) / 32;
+    const int64_t rows_pad = stream_tiles(rows) * kChunkRows;
+    const int64_t ctas = (rows_pad * groups32 + kWarpsPerCta - 1) / kWarpsPerCta;
+    if (ctas > 0x7fffffffLL) return MIXFP4_E_SHAPE;
+    repack_stream_kernel<true><<<(unsigned)ctas, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        codes, scales, fmt, chunks, rows, rows_pad, blocks_pad, groups32, nullptr, nullptr, nullptr);
+    return check_launch("repack_stream_kernel");
+}
+
+extern "C" int mixfp4_repack_from_stream(const uint8_t* chunks, int64_t rows, int64_t k, uint8_t* codes_out,
+                                         uint8_t* scales_out, uint8_t* fmt_out, void* stream) {
+    if (!chunks || !codes_out || !scales_out || !fmt_out) return MIXFP4_E_NULL;
+    if (rows <= 0 || k <= 0) return MIXFP4_E_SHAPE;
+    if (!aligned(codes_out, 8) || !aligned(chunks, 16)) return MIXFP4_E_ALIGN;
+    const int64_t blocks_pad = padded_k(k) / kGroup, groups32 = (blocks_pad + 31) / 32;
+    const int64_t ctas = (rows * groups32 + kWarpsPerCta - 1) / kWarpsPerCta;
+    if (ctas > 0x7fffffffLL) return MIXFP4_E_SHAPE;
+    repack_stream_kernel<false><<<(unsigned)ctas, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        nullptr, nullptr, nullptr, const_cast<uint8_t*>(chunks), rows, stream_tiles(rows) * kChunkRows, blocks_pad,
+        groups32, codes_out, scales_out, fmt_out);
+    return check_launch("repack_stream_kernel");
 }
 
 extern "C" int mixfp4_repack(const uint8_t* codes, const uint8_t* scales, const uint8_t* fmt, int64_t rows, int64_t k,

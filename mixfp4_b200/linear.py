@@ -48,6 +48,19 @@ def gemm_status(device=None) -> int:
     return int(_status_word(device).item())
 
 
+def decode_status(device=None) -> int:
+    """Status word of the decode kernels on `device` (0 = every weight chunk arrived within the
+    wait limit).  Synchronises the current stream."""
+    import ctypes
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    value = ctypes.c_int(0)
+    with torch.cuda.device(device):
+        rc = nat.lib().mixfp4_check_status(None, ctypes.byref(value), nat.stream_ptr(device))
+    if rc not in (nat.OK, nat.E_DEVICE_WAIT):
+        nat.check("mixfp4_check_status", rc)
+    return int(value.value)
+
+
 def mixfp4_linear(x: torch.Tensor, packed: PackedWeight, *, bias: torch.Tensor | None = None,
                   rotate: bool | None = None, out_dtype: torch.dtype | None = None,
                   overlap_previous: bool = False, activation_mode: str | None = None) -> torch.Tensor:
@@ -153,7 +166,7 @@ def mixfp4_linear_grouped(x: torch.Tensor, packs: list[PackedWeight], *, out_dty
                           overlap_previous: bool = False) -> list[torch.Tensor]:
     """[x @ W_i^T for W_i in packs] for weights that take the same x (q/k/v, gate/up).
 
-    Decode shapes (at most 16 rows of x), up to three kernel-layout weights without a folded
+    Decode shapes (at most 16 rows of x), up to three kernel- or stream-layout weights without a folded
     rotation: one launch (``mixfp4_gemv_grouped``).  Anything else: one ``mixfp4_linear`` per
     weight, same results.
     """
@@ -163,7 +176,8 @@ def mixfp4_linear_grouped(x: torch.Tensor, packs: list[PackedWeight], *, out_dty
     lead = x.shape[:-1]
     m = x.numel() // max(1, x.shape[-1])
     grouped = (1 <= m <= 16 and 1 <= len(packs) <= 3 and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] == k
-               and all(p.k == k and p.layout == "kernel" and p.rotation is None for p in packs))
+               and packs[0].layout in ("kernel", "stream")
+               and all(p.k == k and p.layout == packs[0].layout and p.rotation is None for p in packs))
     if grouped:
         out_dtype = x.dtype if out_dtype is None else out_dtype
         if out_dtype not in (torch.float32, torch.bfloat16):
@@ -174,11 +188,11 @@ def mixfp4_linear_grouped(x: torch.Tensor, packs: list[PackedWeight], *, out_dty
         ys = [torch.empty((m, p.n), dtype=out_dtype, device=x.device) for p in packs]
         segs = (nat.GemvSegment * len(packs))()
         for seg, p, y in zip(segs, packs, ys):
-            seg.codes, seg.scales, seg.global_scale = p.codes.data_ptr(), p.scales.data_ptr(), p.global_scale.data_ptr()
+            seg.codes, seg.scales, seg.global_scale = p.codes.data_ptr(), nat.ptr(p.scales), p.global_scale.data_ptr()
             seg.lut, seg.y, seg.ldy, seg.n = nat.ptr(p.lut), y.data_ptr(), y.stride(0), p.n
         with torch.cuda.device(x.device):
             st = nat.lib().mixfp4_gemv_grouped(x2.data_ptr(), m, x2.stride(0), k, segs, len(packs),
-                                               nat.DTYPE_CODE[out_dtype],
+                                               packs[0].layout_code, nat.DTYPE_CODE[out_dtype],
                                                nat.FLAG_OVERLAP_PREVIOUS if overlap_previous else 0,
                                                nat.stream_ptr(x.device))
         if st != nat.E_SHAPE:
@@ -195,7 +209,7 @@ class MixFP4Linear(nn.Module):
         super().__init__()
         self.in_features, self.out_features = packed.k, packed.n
         self.activation_mode = activation_mode      # None: W4A16; a format region: the reference's W4A4 forward
-        packed = packed.to_kernel_layout()          # the layers keep the layout the kernels decode fastest
+        packed = packed.to_stream_layout()          # the layers keep the layout the kernels stream fastest
         self.rotation = packed.rotation
         self.register_buffer("codes", packed.codes)
         self.register_buffer("scales", packed.scales)
@@ -206,7 +220,7 @@ class MixFP4Linear(nn.Module):
     @property
     def packed(self) -> PackedWeight:
         return PackedWeight(self.codes, self.scales, None, self.global_scale, self.out_features,
-                            self.in_features, self.rotation, "kernel", self.lut)
+                            self.in_features, self.rotation, "stream", self.lut)
 
     @classmethod
     @torch.no_grad()

@@ -120,14 +120,23 @@ class PeerCommunicator:
             self._nat.lib().mixfp4_comm_destroy(self.handle)
             self.handle = None
 
+    def fused_ok(self, m: int, k_total: int, n: int, multiple: int = 128) -> bool:
+        """Whether a row-parallel layer of this shape runs the fused kernel.  Decided from global
+        quantities only (the largest K shard any rank holds), so every rank takes the same branch."""
+        blocks = -(-k_total // multiple)
+        largest = -(-blocks // self.world) * multiple
+        return (1 <= m <= 8 and m * n <= self.slot_floats
+                and bool(self._nat.lib().mixfp4_gemv_x_fits(m, min(largest, k_total), 1)))
+
     def linear(self, x_shard: torch.Tensor, packed_shard, *, out_dtype: torch.dtype | None = None,
                overlap_previous: bool = False) -> torch.Tensor | None:
         """sum over ranks of x_shard @ W_shard^T in one kernel per rank, or None when the shape does
-        not qualify (more than 8 rows of x, canonical layout, x too large for shared memory)."""
+        not qualify (more than 8 rows of x, canonical layout, x too large for shared memory).  Callers
+        whose ranks hold unequal shards decide with ``fused_ok`` first."""
         nat = self._nat
         k = packed_shard.k
         m = x_shard.numel() // max(1, x_shard.shape[-1])
-        if not (1 <= m <= 8 and packed_shard.layout == "kernel" and packed_shard.rotation is None
+        if not (1 <= m <= 8 and packed_shard.layout in ("kernel", "stream") and packed_shard.rotation is None
                 and x_shard.dtype == torch.bfloat16 and x_shard.shape[-1] == k and m * packed_shard.n <= self.slot_floats):
             return None
         out_dtype = x_shard.dtype if out_dtype is None else out_dtype
@@ -137,9 +146,9 @@ class PeerCommunicator:
         y = torch.empty((m, packed_shard.n), dtype=out_dtype, device=x_shard.device)
         with torch.cuda.device(x_shard.device):
             st = nat.lib().mixfp4_gemv_allreduce(
-                self.handle, x2.data_ptr(), m, x2.stride(0), packed_shard.codes.data_ptr(), packed_shard.scales.data_ptr(),
-                packed_shard.global_scale.data_ptr(), nat.ptr(packed_shard.lut), packed_shard.n, k, y.data_ptr(),
-                nat.DTYPE_CODE[out_dtype], y.stride(0), self.status.data_ptr(),
+                self.handle, x2.data_ptr(), m, x2.stride(0), packed_shard.codes.data_ptr(), nat.ptr(packed_shard.scales),
+                packed_shard.global_scale.data_ptr(), nat.ptr(packed_shard.lut), packed_shard.n, k,
+                packed_shard.layout_code, y.data_ptr(), nat.DTYPE_CODE[out_dtype], y.stride(0), self.status.data_ptr(),
                 nat.FLAG_OVERLAP_PREVIOUS if overlap_previous else 0, nat.stream_ptr(x_shard.device))
         if st == nat.E_SHAPE:
             return None
@@ -149,22 +158,31 @@ class PeerCommunicator:
 
 class RowParallelMixFP4Linear(torch.nn.Module):
     """y = sum over ranks of x[:, k0:k1] @ W[:, k0:k1]^T.  With a PeerCommunicator decode shapes run
-    the GEMV with the all-reduce fused in; otherwise the partials are summed by torch.distributed."""
+    the GEMV with the all-reduce fused in; otherwise fp32 partial sums are added by torch.distributed
+    and rounded to the output type afterwards.  `k_total` is the unsharded K: the choice between the
+    two forms is made from it (not from this rank's shard), so all ranks agree even when the shards
+    are unequal."""
 
-    def __init__(self, packed_shard, group=None, comm: PeerCommunicator | None = None):
+    def __init__(self, packed_shard, group=None, comm: PeerCommunicator | None = None, k_total: int | None = None):
         super().__init__()
         from .linear import MixFP4Linear
         self.inner = MixFP4Linear(packed_shard)
         self.group = group
         self.comm = comm
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.k_total = int(k_total) if k_total is not None else packed_shard.k * world
 
     def forward(self, x_shard, **kw):
-        if self.comm is not None and self.comm.world > 1:
+        m = x_shard.numel() // max(1, x_shard.shape[-1])
+        if (self.comm is not None and self.comm.world > 1 and self.inner.rotation is None
+                and self.comm.fused_ok(m, self.k_total, self.inner.out_features)):
             y = self.comm.linear(x_shard, self.inner.packed, out_dtype=kw.get("out_dtype"),
                                  overlap_previous=kw.get("overlap_previous", False))
-            if y is not None:
-                return y
-        y = self.inner(x_shard, **kw)
+            if y is None:
+                raise RuntimeError("the fused row-parallel kernel refused a shape fused_ok accepted")
+            return y
+        out_dtype = kw.get("out_dtype") or x_shard.dtype
+        y = self.inner(x_shard, **{**kw, "out_dtype": torch.float32})
         if dist.is_initialized() and dist.get_world_size(self.group) > 1:
             dist.all_reduce(y, group=self.group)
-        return y
+        return y.to(out_dtype)

@@ -73,7 +73,9 @@ class PackedWeight:
     n: int
     k: int
     rotation: str | None = None  # transform folded into the weight along K before quantization
-    layout: str = "canonical"    # "canonical" (parity-hashed) or "kernel" (bit-permuted for the linear kernels)
+    # "canonical" (parity-hashed), "kernel" (bit-permuted code words, format bit in the scale byte) or
+    # "stream" (1152-byte chunks of 16 rows x 128 K: `codes` is the flat chunk buffer, `scales` is empty)
+    layout: str = "canonical"
     lut: torch.Tensor | None = None   # optional decode table (uint8 [4096]) from mixfp4_decode_table
 
     @property
@@ -93,10 +95,12 @@ class PackedWeight:
 
     @property
     def layout_code(self) -> int:
-        return nat.LAYOUT_KERNEL if self.layout == "kernel" else nat.LAYOUT_CANONICAL
+        return {"canonical": nat.LAYOUT_CANONICAL, "kernel": nat.LAYOUT_KERNEL, "stream": nat.LAYOUT_STREAM}[self.layout]
 
     def format_ids(self) -> torch.Tensor:
         """uint8 [n, ceil(k/16)], 1 = E0M3 (GranularityResult.format_ids of the reference)."""
+        if self.layout == "stream":
+            return self.to_canonical().format_ids()
         if self.layout == "kernel":
             return (self.scales[:, : self.groups] >> 7).contiguous()
         shifts = torch.arange(8, device=self.fmt.device, dtype=torch.uint8)
@@ -105,6 +109,8 @@ class PackedWeight:
 
     def selected_scales(self) -> torch.Tensor:
         """float32 [n, ceil(k/16)] decoded block scales."""
+        if self.layout == "stream":
+            return self.to_canonical().selected_scales()
         return (self.scales[:, : self.groups] & 0x7F).contiguous().view(torch.float8_e4m3fn).float()
 
     def dequantize(self, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
@@ -138,6 +144,26 @@ class PackedWeight:
     def _repack(self, to: str) -> "PackedWeight":
         if self.layout == to:
             return self
+        if to == "stream":
+            src = self if self.layout == "canonical" else self._repack("canonical")
+            lib = nat.lib()
+            chunks = torch.empty(lib.mixfp4_stream_bytes(self.n, self.k), dtype=torch.uint8, device=self.device)
+            with torch.cuda.device(self.device):
+                st = lib.mixfp4_repack_stream(src.codes.data_ptr(), src.scales.data_ptr(), src.fmt.data_ptr(), self.n,
+                                              self.k, chunks.data_ptr(), nat.stream_ptr(self.device))
+            nat.check("mixfp4_repack_stream", st)
+            empty = torch.empty(0, dtype=torch.uint8, device=self.device)
+            return PackedWeight(chunks, empty, None, self.global_scale, self.n, self.k, self.rotation, "stream", self.lut)
+        if self.layout == "stream":
+            codes = torch.empty((self.n, self.kpad // 2), dtype=torch.uint8, device=self.device)
+            scales = torch.empty((self.n, self.kpad // 16), dtype=torch.uint8, device=self.device)
+            fmt = torch.empty((self.n, self.kpad // 128), dtype=torch.uint8, device=self.device)
+            with torch.cuda.device(self.device):
+                st = nat.lib().mixfp4_repack_from_stream(self.codes.data_ptr(), self.n, self.k, codes.data_ptr(),
+                                                         scales.data_ptr(), fmt.data_ptr(), nat.stream_ptr(self.device))
+            nat.check("mixfp4_repack_from_stream", st)
+            canon = PackedWeight(codes, scales, fmt, self.global_scale, self.n, self.k, self.rotation, "canonical", self.lut)
+            return canon if to == "canonical" else canon._repack(to)
         codes, scales = torch.empty_like(self.codes), torch.empty_like(self.scales)
         fmt = None if to == "kernel" else torch.empty((self.n, self.kpad // 128), dtype=torch.uint8, device=self.device)
         with torch.cuda.device(self.device):
@@ -152,11 +178,18 @@ class PackedWeight:
         word, format bit folded into bit 7 of the scale byte; no format array), with its table."""
         return self._repack("kernel").with_decode_table()
 
+    def to_stream_layout(self) -> "PackedWeight":
+        """Copy in the stream layout (one contiguous 1152-byte chunk per 16 rows x 128 K elements:
+        what the decode kernels stream with one bulk copy per step), with its decode table."""
+        return self._repack("stream").with_decode_table()
+
     def to_canonical(self) -> "PackedWeight":
         return self._repack("canonical")
 
     def row_shard(self, start: int, stop: int) -> "PackedWeight":
         """Rows [start, stop) -- a column-parallel (split N) shard; shares the tensor scale."""
+        if self.layout == "stream":
+            return self.to_canonical().row_shard(start, stop)._repack("stream")
         fmt = None if self.fmt is None else self.fmt[start:stop].contiguous()
         return PackedWeight(self.codes[start:stop].contiguous(), self.scales[start:stop].contiguous(), fmt,
                             self.global_scale, stop - start, self.k, self.rotation, self.layout, self.lut)
@@ -165,6 +198,8 @@ class PackedWeight:
         """Columns [start, stop) along K (multiples of 128) -- a row-parallel (split K) shard."""
         if start % 128 or (stop % 128 and stop != self.k):
             raise ValueError("K shards must start and end on multiples of 128")
+        if self.layout == "stream":
+            return self.to_canonical().k_shard(start, stop)._repack("stream")
         pstop = padded_k(stop)
         fmt = None if self.fmt is None else self.fmt[:, start // 128: pstop // 128].contiguous()
         return PackedWeight(self.codes[:, start // 2: pstop // 2].contiguous(),

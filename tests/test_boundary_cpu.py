@@ -22,7 +22,7 @@ def test_library_exports_every_declared_symbol():
     handle = nat.lib()
     for name in declared:
         assert getattr(handle, name) is not None
-    assert handle.mixfp4_abi_version() == 2
+    assert handle.mixfp4_abi_version() == 3
     assert handle.mixfp4_padded_k(70) == 128 and handle.mixfp4_padded_k(4096) == 4096
 
 
@@ -56,12 +56,14 @@ def test_c_abi_argument_validation_needs_no_gpu():
     seg = (nat.GemvSegment * 1)()
     seg[0].codes = seg[0].scales = seg[0].global_scale = seg[0].y = 16
     seg[0].ldy, seg[0].n = 8, 8
-    assert h.mixfp4_gemv_grouped(one, 1, 64, 64, seg, 0, nat.F32, 0, None) == -2     # count out of range
-    assert h.mixfp4_gemv_grouped(one, 17, 64, 64, seg, 1, nat.F32, 0, None) == -2    # more than 16 rows of x
-    assert h.mixfp4_gemv_grouped(one, 1, 64, 64, None, 1, nat.F32, 0, None) == -1
-    assert h.mixfp4_gemv_grouped(one, 1, 64, 64, seg, 1, nat.F16, 0, None) == -4
+    assert h.mixfp4_gemv_grouped(one, 1, 64, 64, seg, 0, 1, nat.F32, 0, None) == -2     # count out of range
+    assert h.mixfp4_gemv_grouped(one, 17, 64, 64, seg, 1, 1, nat.F32, 0, None) == -2    # more than 16 rows of x
+    assert h.mixfp4_gemv_grouped(one, 1, 64, 64, None, 1, 1, nat.F32, 0, None) == -1
+    assert h.mixfp4_gemv_grouped(one, 1, 64, 64, seg, 1, 0, nat.F32, 0, None) == -5     # grouped launches: kernel or stream layout
+    assert h.mixfp4_gemv_grouped(one, 17, 64, 64, seg, 1, 2, nat.F32, 0, None) == -2
+    assert h.mixfp4_gemv_grouped(one, 1, 64, 64, seg, 1, 1, nat.F16, 0, None) == -4
     seg[0].ldy = 4
-    assert h.mixfp4_gemv_grouped(one, 1, 64, 64, seg, 1, nat.F32, 0, None) == -2     # ldy < n
+    assert h.mixfp4_gemv_grouped(one, 1, 64, 64, seg, 1, 1, nat.F32, 0, None) == -2     # ldy < n
     assert h.mixfp4_select_regions(one, one, 8, 256, 8, 4, None, None) == -1
     assert h.mixfp4_select_regions(one, one, 8, 256, 8, 3, one, None) == -5      # region width must be 2 or 4 blocks
     assert h.mixfp4_select_regions(one, one, 8, 64, 8, 4, one, None) == -5       # one region along K, several rows
@@ -80,6 +82,37 @@ def test_c_abi_argument_validation_needs_no_gpu():
     assert h.mixfp4_gemm_a4(*bad) == -1
     assert h.mixfp4_gemm_workspace_bytes(64, 64, 64) >= 64 * 64 * 2 + 4
     assert h.mixfp4_repack(one, one, None, 4, 64, 1, one, one, None, None) == -1
+    # stream layout: sizes, argument checks, the x-fits predicate (host arithmetic only)
+    assert h.mixfp4_stream_bytes(33, 70) == 3 * 1 * 1152 and h.mixfp4_stream_bytes(4096, 4096) == 256 * 32 * 1152
+    assert h.mixfp4_stream_bytes(0, 64) == 0
+    assert h.mixfp4_repack_stream(one, one, None, 4, 64, one, None) == -1
+    assert h.mixfp4_repack_stream(one, one, one, 4, 0, one, None) == -2
+    assert h.mixfp4_repack_from_stream(one, 4, 64, one, one, None, None) == -1
+    assert h.mixfp4_gemv(one, 1, 64, one, None, None, one, 8, 64, 2, None, None, nat.F32, 8, 0, None) == -1   # stream: scales and fmt may be NULL, y not
+    assert h.mixfp4_gemv(one, 1, 64, one, None, None, one, 8, 64, 1, None, one, nat.F32, 8, 0, None) == -1   # kernel layout needs scales
+    assert h.mixfp4_gemv_x_fits(1, 4096, 3) == 1 and h.mixfp4_gemv_x_fits(8, 14336, 1) == 0
+    assert h.mixfp4_gemv_x_fits(17, 64, 1) == 0 and h.mixfp4_gemv_x_fits(1, 64, 4) == 0
+    assert h.mixfp4_set_wait_limit_ns(0) == -2 and h.mixfp4_set_wait_limit_ns(2_000_000_000) == 0
+    assert h.mixfp4_comm_buffer_bytes(2, 100) == 2 * 2 * 100 * 8 and h.mixfp4_comm_buffer_bytes(9, 100) == 0
+    assert h.mixfp4_comm_open_local(None, None) == -1
+    # the GEMM entry points check every argument before they enqueue anything
+    st = [one, 64, 64, one, one, one, one, 64, 64, 0, None, one, nat.F32, 64, None, None]
+    bad = list(st); bad[9] = 7
+    assert h.mixfp4_gemm_h128_static(*bad) == -5                                                # unknown layout
+    bad = list(st); bad[12] = nat.F16
+    assert h.mixfp4_gemm_h128_static(*bad) == -4                                                # f32 or bf16 out
+    bad = list(st); bad[3] = ctypes.c_void_p(24)
+    assert h.mixfp4_gemm_h128_static(*bad) == -3                                                # codes 16-byte aligned
+    bad = list(st); bad[5] = None
+    assert h.mixfp4_gemm_h128_static(*bad) == -1                                                # canonical needs fmt
+    bad = list(st); bad[1] = 1 << 40
+    assert h.mixfp4_gemm_h128_static(*bad) == -2                                                # m beyond 2^31
+    bad = list(st); bad[1] = 1 << 20; bad[7] = 16; bad[13] = 16
+    assert h.mixfp4_gemm_h128_static(*bad) == -10                                               # beyond the built-in array
+    bad = list(a4); bad[12] = 3
+    assert h.mixfp4_gemm_a4(*bad) == -5                                                         # activation mode 0..2
+    bad = list(a4); bad[14] = nat.F16
+    assert h.mixfp4_gemm_a4(*bad) == -4
     assert h.mixfp4_decode_table(None, one, None) == -1
     assert h.mixfp4_status_string(-3).decode().startswith("pointer or stride")
 
