@@ -145,6 +145,12 @@ MIXFP4_API int mixfp4_select_regions(const float* e2_err, const float* e0_err, i
  * it leaves the number of disagreements (expected 0) in *mismatches (device memory). */
 MIXFP4_API int mixfp4_selftest_division(unsigned long long* mismatches, void* stream);
 
+/* Element-wise rounding to a codebook: y[i] = sign(x[i]) * nearest level of |x[i]| with the
+ * reference's tie rules (project_quant/codebook.py:12-25 quantize_e2m1: round half up on the
+ * private mantissa, saturate at 6; :41-43 quantize_e0m3: round half even, saturate at 7).
+ * x, y: device f32 [n]; e0m3: 0 = E2M1, 1 = E0M3. */
+MIXFP4_API int mixfp4_round_codebook(const float* x, float* y, int64_t n, int e0m3, void* stream);
+
 /* Packed -> dense weight in out_dtype (the tensor the reference stores back into
  * nn.Linear.weight, project_quant/modeling.py:629). */
 MIXFP4_API int mixfp4_dequant(const uint8_t* codes, const uint8_t* scales, const uint8_t* fmt,

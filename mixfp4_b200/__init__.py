@@ -6,14 +6,15 @@ All compute runs in hand-written CUDA kernels reached through the C ABI declared
 include/mixfp4_b200.h; importing the package does not need a GPU, calling it does.
 """
 
-from .quant import (E0M3_LEVELS, E2M1_LEVELS, SCALE_GROUP_SIZE, GranularityResult, PackedWeight, dequantize,
-                    fake_quantize_activations, packed_nbytes, quant_mixfp4_granularity, quantize_packed, tensor_amax)
+from .quant import (E0M3_LEVELS, E2M1_LEVELS, SCALE_GROUP_SIZE, CandidateBlocks, GranularityResult, PackedWeight,
+                    build_candidates, dequantize, fake_quantize_activations, quantize_e0m3, quantize_e2m1, packed_nbytes, quant_mixfp4_granularity, quantize_packed, tensor_amax)
 from .rotation import TRANSFORM_BANK, TransformSpec, apply_transform, get_transform
 from .linear import MixFP4Linear, decode_status, gemm_status, mixfp4_linear, mixfp4_linear_grouped
 from .convert import load_packed, named_linears, quantize_model_weights, save_packed
 
 __all__ = [
-    "E0M3_LEVELS", "E2M1_LEVELS", "SCALE_GROUP_SIZE", "GranularityResult", "PackedWeight", "dequantize",
+    "E0M3_LEVELS", "E2M1_LEVELS", "SCALE_GROUP_SIZE", "CandidateBlocks", "GranularityResult", "build_candidates",
+    "quantize_e0m3", "quantize_e2m1", "PackedWeight", "dequantize",
     "fake_quantize_activations", "packed_nbytes", "quant_mixfp4_granularity", "quantize_packed", "tensor_amax", "TRANSFORM_BANK",
     "TransformSpec", "apply_transform", "get_transform", "MixFP4Linear", "decode_status", "gemm_status", "mixfp4_linear", "mixfp4_linear_grouped",
     "load_packed", "named_linears", "quantize_model_weights", "save_packed",

@@ -49,7 +49,15 @@ struct GemvStreamArgs {
     AllReduceArgs ar;                      // used by the all-reduce instantiation only
     int* status;                           // device word: nonzero after an expired wait
     uint64_t wait_ns;                      // limit of every wait on a chunk
+#ifdef MIXFP4_TRACE
+    unsigned long long* trace;             // [launch % 64][CTA][8] globaltimer stamps
+#endif
 };
+#ifdef MIXFP4_TRACE
+#define MIXFP4_STAMP(i) do { if (a.trace && lane == 0 && (warp == 0 || warp == kWarps - 1)) a.trace[(size_t)blockIdx.x * 8 + (i) + (warp ? 4 : 0)] = gemv_timer_ns(); } while (0)
+#else
+#define MIXFP4_STAMP(i) do { } while (0)
+#endif
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -115,10 +123,13 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
     float* pieces = reinterpret_cast<float*>(smem + (x_base - sbase) + x_bytes);   // [warp][head, tail][16 rows][m]
 
     // this CTA's row tiles and this warp's run of their chunks
-    const int t0 = (int)((int64_t)a.ntiles * blockIdx.x / gridDim.x);
-    const int t1 = (int)((int64_t)a.ntiles * (blockIdx.x + 1) / gridDim.x);
-    const int nchunks = (t1 - t0) * S;
-    auto run_start = [&](int w) { return (int)((int64_t)nchunks * w / kWarps); };
+    // (the CTAs with the lowest indices take the odd tiles: under programmatic dependent launch they
+    // are the first to get an SM, so the extra work goes where the head start is)
+    const int per_cta = a.ntiles / (int)gridDim.x, extra = a.ntiles % (int)gridDim.x;
+    const int t0 = (int)blockIdx.x * per_cta + min((int)blockIdx.x, extra);
+    const int t1 = t0 + per_cta + ((int)blockIdx.x < extra ? 1 : 0);
+    const int nchunks = (t1 - t0) * S;                      // at most 2^31 / kWarps: the host checks
+    auto run_start = [&](int w) { return (int)((uint32_t)nchunks * (uint32_t)w / (uint32_t)kWarps); };
     const int wa = run_start(warp), wb = run_start(warp + 1), cnt = wb - wa;
 
     auto seg_first = [&](int s) { return s == 0 ? 0 : s == 1 ? a.seg[0].tile_end : a.seg[1].tile_end; };
@@ -154,18 +165,21 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
         }
     };
 
-    // Prologue.  Weights first: they never depend on the previous kernel in the stream.
+    // Prologue.  The next kernel in the stream may be scheduled as soon as every CTA has passed this
+    // point (it still waits for this grid's completion before it touches x).  Weights first: they
+    // never depend on the previous kernel.  Only the first chunk goes out here: a bulk copy can
+    // stall its issuer while the copy engine's queue is full, and nothing below should wait for that;
+    // the main loop fills the ring.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    MIXFP4_STAMP(0);
     if (lane == 0) {
 #pragma unroll
         for (int d = 0; d < kDepth; ++d) mbar_init(bars + d * 8, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the copy engine sees initialised barriers
     }
     __syncwarp();
     Cursor p = make_cursor(wa);
-#pragma unroll
-    for (int d = 0; d < kDepth; ++d)
-        if (d < cnt) { issue(p, d); advance(p); }
+    if (cnt > 0) { issue(p, 0); advance(p); }
 
     // Table entries go through registers: loaded here, stored after the x copies have been issued,
     // so the two latencies overlap.  (entry, copy) pairs: a warp writes 512 contiguous bytes.
@@ -182,10 +196,14 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
             tv[s][it] = lut ? __ldg(lut + e) : make_lut_entry(e & 127, e >> 7, gs);
         }
     }
-    // x may be the previous kernel's output: wait for it (no-op without the launch attribute), and
-    // let the next kernel in the stream start its own weight prefetch.
+    // The rest of the ring.  These issues can stall while the copy engine's queue is full, which is
+    // harmless here: under programmatic dependent launch this CTA waits for the previous kernel next.
+#pragma unroll
+    for (int d = 1; d < kDepth; ++d)
+        if (d < cnt) { issue(p, d); advance(p); }
+    // x may be the previous kernel's output: wait for it (no-op without the launch attribute).
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    MIXFP4_STAMP(1);
     uint32_t seq = 0;       // sequence number of this launch (advanced by the previous launch's last CTA)
     if constexpr (kAR) seq = *reinterpret_cast<volatile uint32_t*>(a.ar.words);
     {   // the whole x (m rows, zero-filled to kpad) once per CTA
@@ -217,6 +235,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
     }
     cp_async_wait<0>();
     __syncthreads();
+    MIXFP4_STAMP(2);
 
     // Outputs.  kAR: every value goes as a packet into every rank's buffer (this rank's included)
     // and is added up at the end; else it is stored.
@@ -324,7 +343,9 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
             if (++slot == kDepth) { slot = 0; phase ^= 1u; }
         }
     }
+    if (warp != 0) MIXFP4_STAMP(3);
     __syncthreads();
+    if (warp == 0) MIXFP4_STAMP(3);
 
     // Row tiles cut by run boundaries: the warp whose run holds the end of such a tile adds the
     // partial sums of the runs before it (ascending K) and its own head piece.
@@ -337,18 +358,15 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
             const int tile = t0 + tl;
             const int cs = (tile >= a.seg[0].tile_end) + (tile >= a.seg[1].tile_end);
             const uint32_t row0 = (uint32_t)(tile - seg_first(cs)) * kRowsPerCta;
+            // the first run holds the tile as its tail piece unless it starts exactly at the tile; every
+            // run after it lies inside the tile (its head piece); empty runs (fewer chunks than warps)
+            // start where the next one starts, have written nothing and are skipped
+            const float* first_piece = pieces + (size_t)((wf * 2 + (run_start(wf) < lo ? 1 : 0)) * kRowsPerCta) * m;
             for (int v = lane; v < kRowsPerCta * m; v += 32) {
                 const int r = v % kRowsPerCta, b = v / kRowsPerCta;
-                float sum = 0.0f;
-                bool first = true;
-                for (int w2 = wf; w2 <= warp; ++w2) {
-                    const int s2 = run_start(w2);
-                    if (s2 == run_start(w2 + 1)) continue;   // empty run
-                    const int which = s2 / S == tl ? 0 : 1;  // the tile is that run's head or its tail
-                    const float val = pieces[(size_t)((w2 * 2 + which) * kRowsPerCta + r) * m + b];
-                    sum = first ? val : sum + val;
-                    first = false;
-                }
+                float sum = first_piece[r * m + b];
+                for (int w2 = wf + 1; w2 <= warp; ++w2)
+                    if (run_start(w2) != run_start(w2 + 1)) sum += pieces[(size_t)(w2 * 2 * kRowsPerCta + r) * m + b];
                 emit(cs, row0 + r, b, sum);
             }
         }
@@ -427,6 +445,11 @@ int device_info(DeviceInfo* out) {
     *out = info[dev];
     return MIXFP4_OK;
 }
+
+#ifdef MIXFP4_TRACE
+static __device__ unsigned long long g_trace[64 * 160 * 8];
+std::atomic<unsigned> g_trace_launch{0};
+#endif
 
 constexpr size_t kSmemLimit = 227 * 1024;
 
@@ -507,6 +530,13 @@ int gemv_stream(const void* x, int64_t m, int64_t ldx, int64_t k, const mixfp4_g
     DeviceInfo info;
     if (const int rc = device_info(&info)) return rc;
     g.status = info.status;
+#ifdef MIXFP4_TRACE
+    {
+        void* tp = nullptr;
+        MIXFP4_CUDA_CHECK(cudaGetSymbolAddress(&tp, g_trace));
+        g.trace = static_cast<unsigned long long*>(tp) + (size_t)(g_trace_launch.fetch_add(1) % 64) * 160 * 8;
+    }
+#endif
     if (comm) {
         const int rc = comm_view(comm, &g.ar.rank, &g.ar.world, &g.ar.slot_packets, &g.ar.recv, g.ar.peer, &g.ar.words);
         if (rc != MIXFP4_OK) return rc;
@@ -557,3 +587,13 @@ extern "C" int mixfp4_check_status(const int* dev_status, int* value, void* stre
     if (value) *value = v;
     return v == 0 ? MIXFP4_OK : MIXFP4_E_DEVICE_WAIT;
 }
+
+#ifdef MIXFP4_TRACE
+// Profiling build only: copies the time stamps of the last 64 launches to the host and restarts the count.
+extern "C" __attribute__((visibility("default"))) int mixfp4_trace_read(unsigned long long* host_out) {
+    MIXFP4_CUDA_CHECK(cudaDeviceSynchronize());
+    MIXFP4_CUDA_CHECK(cudaMemcpyFromSymbol(host_out, g_trace, sizeof(unsigned long long) * 64 * 160 * 8));
+    g_trace_launch.store(0);
+    return MIXFP4_OK;
+}
+#endif

@@ -227,6 +227,18 @@ __device__ __forceinline__ void candidate(const float (&ax)[kGroup], const float
     }
 }
 
+// Element-wise codebook rounding (project_quant/codebook.py:12-25 quantize_e2m1, :41-43 quantize_e0m3):
+// y = sign(x) * level(|x|), with the reference's signed zero (a negative x that rounds to zero gives -0,
+// x = +-0 gives +0 because sign(0) = 0).
+__global__ void __launch_bounds__(kThreads) round_codebook_kernel(const float* __restrict__ x, float* __restrict__ y,
+                                                                  int64_t n, bool e0) {
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += (int64_t)gridDim.x * kThreads) {
+        const float v = x[i], mag = fabsf(v);
+        const float q = e0 ? e0m3_round(mag) : e2m1_round(mag);
+        y[i] = v < 0.0f ? -q : (v > 0.0f ? q : __fmul_rn(v != v ? v : 0.0f, q));
+    }
+}
+
 // Exhaustive check of div_rcp against IEEE division: all 2^23 significands of the dividend
 // for each of the 8 significands a divisor can have (E4M3 scales; 6 = 1.5 * 4, 7 = 1.75 * 4).
 __global__ void selftest_division_kernel(unsigned long long* mismatches) {
@@ -729,6 +741,16 @@ extern "C" int mixfp4_dequant(const uint8_t* codes, const uint8_t* scales, const
 #undef MIXFP4_LAUNCH_DEQUANT
 #undef MIXFP4_LAUNCH_DEQUANT_L
     return check_launch("dequant_kernel");
+}
+
+extern "C" int mixfp4_round_codebook(const float* x, float* y, int64_t n, int e0m3, void* stream) {
+    if (!x || !y) return MIXFP4_E_NULL;
+    if (n <= 0) return MIXFP4_E_SHAPE;
+    if (e0m3 != 0 && e0m3 != 1) return MIXFP4_E_MODE;
+    const int64_t ctas = (n + kThreads - 1) / kThreads;
+    round_codebook_kernel<<<(unsigned)(ctas < 4096 ? ctas : 4096), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        x, y, n, e0m3 != 0);
+    return check_launch("round_codebook_kernel");
 }
 
 extern "C" int64_t mixfp4_stream_bytes(int64_t rows, int64_t k) {

@@ -331,6 +331,114 @@ def quantize_packed(x: torch.Tensor, *, mode: str = "oracle16", amax: torch.Tens
     return PackedWeight(codes, scales, fmt, gs, rows, k, rotation), dq, stats
 
 
+def _codebook(x: torch.Tensor, e0m3: bool) -> torch.Tensor:
+    if not torch.is_floating_point(x):
+        raise TypeError("x must be floating point")
+    host_input = not x.is_cuda
+    xf = x.detach().to(torch.float32)
+    xf = (xf.cuda() if host_input else xf).contiguous()
+    out = torch.empty_like(xf)
+    if xf.numel():
+        with torch.cuda.device(xf.device):
+            st = nat.lib().mixfp4_round_codebook(xf.data_ptr(), out.data_ptr(), xf.numel(), int(e0m3),
+                                                 nat.stream_ptr(xf.device))
+        nat.check("mixfp4_round_codebook", st)
+    out = out.to(x.dtype)
+    return out.to(x.device) if host_input else out
+
+
+@torch.no_grad()
+def quantize_e2m1(x: torch.Tensor) -> torch.Tensor:
+    """E2M1 round-to-nearest of every element, ties away from zero on the private mantissa, saturated
+    to +-6 (project_quant/codebook.py:12-25); computed by the CUDA kernel the quantizer shares its
+    rounding with."""
+    return _codebook(x, False)
+
+
+@torch.no_grad()
+def quantize_e0m3(x: torch.Tensor) -> torch.Tensor:
+    """Project E0M3: sign-magnitude integers 0, +-1 ... +-7, round half even
+    (project_quant/codebook.py:41-43)."""
+    return _codebook(x, True)
+
+
+@dataclass
+class CandidateBlocks:
+    """Both independently scaled K16 candidates of a tensor; fields as
+    project_quant/candidates.py:22-43 (codes are level values in float32, -0.0 where a negative
+    element rounds to zero; everything [rows, groups(, 16)] float32 unless noted)."""
+
+    original_shape: tuple[int, ...]
+    source_dtype: torch.dtype
+    operand_role: str
+    rows: int
+    k: int
+    groups: int
+    padded_k: int
+    tail_padding: int
+    grouped_original: torch.Tensor
+    e2_dequant: torch.Tensor
+    e0_dequant: torch.Tensor
+    e2_codes: torch.Tensor
+    e0_codes: torch.Tensor
+    e2_scales: torch.Tensor
+    e0_scales: torch.Tensor
+    e2_errors: torch.Tensor
+    e0_errors: torch.Tensor
+    e2_scale_expansion_ids: torch.Tensor    # uint8, all zero under the standard scale rule
+    e0_scale_expansion_ids: torch.Tensor
+    global_scale: torch.Tensor              # 0-dim float32
+    scale_rule: str
+
+
+def _level_values(codes: torch.Tensor, groups: int, levels: tuple[float, ...]) -> torch.Tensor:
+    """Packed nibbles [rows, kpad/2] -> signed level values float32 [rows, groups, 16]."""
+    rows = codes.shape[0]
+    nib = torch.stack((codes & 15, codes >> 4), dim=-1).reshape(rows, -1)[:, : groups * 16].long()
+    mag = torch.tensor(levels, dtype=torch.float32, device=codes.device)[nib & 7]
+    return torch.where((nib & 8) != 0, -mag, mag).reshape(rows, groups, 16)
+
+
+@torch.no_grad()
+def build_candidates(x: torch.Tensor, *, scale_group_size: int = SCALE_GROUP_SIZE, operand_role: str = "weight_b",
+                     scale_rule: str = "standard") -> CandidateBlocks:
+    """The reference's ``build_candidates`` (project_quant/candidates.py:62-106): the tensor up-cast
+    to float32, right-zero-padded to whole K16 blocks, and for each block the E2M1 and the E0M3
+    candidate with its own E4M3 scale -- level values, dequantized values, scales and squared errors.
+    Two launches of the CUDA quantizer (one per forced format) on the float32 tensor produce every
+    field; the nibble codes are expanded to level values on the device.  A host tensor is copied to
+    the current CUDA device and the fields are copied back."""
+    validate_layout(x, scale_group_size=scale_group_size, operand_role=operand_role)
+    if scale_rule == "four_over_six":
+        raise NotImplementedError("scale_rule='four_over_six' needs the FourOverSix upstream for its E2M1 branch")
+    if scale_rule != "standard":
+        raise ValueError(f"unknown scale_rule={scale_rule!r}")
+    original_shape = tuple(x.shape)
+    k = x.shape[-1]
+    rows = x.numel() // k
+    host_input = not x.is_cuda
+    source = x.detach().reshape(rows, k).to(torch.float32)
+    source = source.cuda() if host_input else source
+    tail = (-k) % scale_group_size
+    padded = torch.nn.functional.pad(source, (0, tail)) if tail else source.contiguous()
+    groups = padded.shape[1] // scale_group_size
+    amax = tensor_amax(padded)
+    e2p, e2d, stats = quantize_packed(padded, mode="all_e2m1", amax=amax, want_dequant=True, want_stats=True)
+    e0p, e0d, _ = quantize_packed(padded, mode="all_e0m3", amax=amax, want_dequant=True)
+    zeros = torch.zeros((rows, groups), dtype=torch.uint8, device=padded.device)
+    mv = (lambda t: t.to(x.device)) if host_input else (lambda t: t)
+    return CandidateBlocks(
+        original_shape=original_shape, source_dtype=x.dtype, operand_role=operand_role, rows=rows, k=k, groups=groups,
+        padded_k=padded.shape[1], tail_padding=tail,
+        grouped_original=mv(padded.reshape(rows, groups, scale_group_size)),
+        e2_dequant=mv(e2d.reshape(rows, groups, scale_group_size)), e0_dequant=mv(e0d.reshape(rows, groups, scale_group_size)),
+        e2_codes=mv(_level_values(e2p.codes, groups, E2M1_LEVELS)), e0_codes=mv(_level_values(e0p.codes, groups, E0M3_LEVELS)),
+        e2_scales=mv(stats["e2_scales"]), e0_scales=mv(stats["e0_scales"]),
+        e2_errors=mv(stats["e2_errors"]), e0_errors=mv(stats["e0_errors"]),
+        e2_scale_expansion_ids=mv(zeros), e0_scale_expansion_ids=mv(zeros.clone()),
+        global_scale=mv(e2p.global_scale.reshape(())), scale_rule=scale_rule)
+
+
 HIGH_PRECISION_MODES = ("high_precision", "fp16", "bf16")
 
 

@@ -343,6 +343,19 @@ int mixfp4_oracle_linear(const float* x, const float* w, int64_t m, int64_t n, i
     return 0;
 }
 
+/* codebook.py:12-25 quantize_e2m1 / :41-43 quantize_e0m3 element by element: sign(x) * level(|x|),
+ * where sign(+-0) = 0 makes the result +0 and a negative x that rounds to zero gives -0. */
+int mixfp4_oracle_round_codebook(const float* x, float* y, int64_t n, int e0m3) {
+    if (!x || !y || n < 0) return -1;
+    for (int64_t i = 0; i < n; ++i) {
+        const float v = x[i], mag = fabsf(v);
+        const float q = e0m3 ? (float)e0m3_index(mag) : kE2M1Levels[e2m1_index(mag)];
+        const float sign = v > 0.0f ? 1.0f : (v < 0.0f ? -1.0f : 0.0f);
+        y[i] = sign * q;
+    }
+    return 0;
+}
+
 int mixfp4_oracle_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -10,6 +10,8 @@ CPU path on small seeded tensors and writes
     tests/golden/quant_cases.npz      inputs + per-block results of the quantizer
     tests/golden/rotation_cases.npz   inputs + outputs of the block-Hadamard bank
     tests/golden/digests.json         SHA-256 of the packed bytes for full-size tensors
+    tests/golden/candidate_cases.npz  build_candidates fields (both candidates' dequantized values)
+                                      and the two codebook quantizers on a dense probe
 
 The reference has no packed form, so its per-block results (level values, E4M3
 scale values, format ids) are packed here by a small host adapter into the layout
@@ -222,14 +224,47 @@ def digest_cases(pq) -> dict:
     return out
 
 
+CANDIDATE_CASES = ("t_17x79_s3", "t_19x131_s10", "t_11x64_s17_bf16", "t_2x17x70_s14_act", "zeros_9x70_bf16",
+                   "student_t_48x384_fp16", "wide_range_24x256_f32", "neg_zero_4x32_f32")
+
+
+def candidate_case_list(pq) -> dict:
+    """Fields of the reference's build_candidates that quant_cases.npz does not hold (the float32
+    dequantized values of both candidates), and quantize_e2m1 / quantize_e0m3 on the dense probe of
+    the reference's own level test (tests/test_quant_core.py:34-41) plus tie and edge values."""
+    out = {}
+    wanted = {name: (x, role) for name, x, _, role in quant_case_list() if name in CANDIDATE_CASES}
+    for name in CANDIDATE_CASES:
+        x, role = wanted[name]
+        cand = pq.build_candidates(x, operand_role=role)
+        out[f"{name}__e2_dequant"] = cand.e2_dequant.numpy().copy()
+        out[f"{name}__e0_dequant"] = cand.e0_dequant.numpy().copy()
+        out[f"{name}__grouped_original"] = cand.grouped_original.numpy().copy()
+        out[f"{name}__meta"] = np.array([cand.rows, cand.k, cand.groups, cand.padded_k, cand.tail_padding], np.int64)
+    probe = torch.linspace(-10, 10, 80001, dtype=torch.float32)
+    ties = torch.tensor([0.0, -0.0, 0.25, 0.24999998509883881, 0.2500000298023224, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 0.5,
+                         1.5, 2.4999998, 6.0, 6.5, 7.5, 8.0, 1e-30, 3e38, 4.5, 5.5, -0.1, -0.3, -2.5, -3.5, -6.5, -7.5],
+                        dtype=torch.float32)
+    x = torch.cat([probe, ties, -ties, torch.randn(4096, generator=torch.Generator().manual_seed(5)) * 3])
+    out["probe__x"] = x.numpy().copy()
+    out["probe__e2m1"] = pq.quantize_e2m1(x).numpy().copy()
+    out["probe__e0m3"] = pq.quantize_e0m3(x).numpy().copy()
+    return out
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of a checkout of the reference project")
     ap.add_argument("--skip-digests", action="store_true")
+    ap.add_argument("--only-candidates", action="store_true", help="write candidate_cases.npz only")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     import project_quant as pq
     from project_quant import rotation as rot
+
+    np.savez_compressed(os.path.join(HERE, "candidate_cases.npz"), **candidate_case_list(pq))
+    if args.only_candidates:
+        return
 
     quant = {}
     names = []

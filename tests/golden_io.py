@@ -42,6 +42,16 @@ def quant_cases() -> list[QuantCase]:
     return out
 
 
+def candidate_cases() -> dict:
+    """name -> {e2_dequant, e0_dequant, grouped_original, meta} plus 'probe' -> {x, e2m1, e0m3}."""
+    z = np.load(os.path.join(GOLDEN, "candidate_cases.npz"))
+    out: dict = {}
+    for key in z.files:
+        name, field = key.split("__", 1)
+        out.setdefault(name, {})[field] = z[key]
+    return out
+
+
 def rotation_cases() -> dict:
     z = np.load(os.path.join(GOLDEN, "rotation_cases.npz"))
     return {k: z[k] for k in z.files}

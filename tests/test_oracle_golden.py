@@ -126,3 +126,32 @@ def test_torch_port_matches_c_oracle():
         ref = oracle.dequant(p, "bf16" if w.dtype == torch.bfloat16 else "f32")
         got = out.view(torch.int16).numpy().view(np.uint16) if w.dtype == torch.bfloat16 else out.numpy()
         assert np.array_equal(got.reshape(-1), ref.reshape(-1))
+
+
+def test_codebook_rounding_matches_reference_probe():
+    # quantize_e2m1 / quantize_e0m3 of the reference on its own dense level probe plus tie values
+    # (tests/golden/make_golden.py: candidate_case_list); signed zeros compared as bit patterns
+    from tests.golden_io import candidate_cases
+    probe = candidate_cases()["probe"]
+    for key, e0 in (("e2m1", False), ("e0m3", True)):
+        got = oracle.round_codebook(probe["x"], e0)
+        assert np.array_equal(got.view(np.uint32), probe[key].view(np.uint32)), key
+    levels = sorted(set(np.abs(oracle.round_codebook(np.linspace(-10, 10, 80001, dtype=np.float32), False)).tolist()))
+    assert levels == list(oracle.E2M1_LEVELS)
+
+
+def test_both_candidates_dequantized_values_match_reference():
+    # build_candidates' float32 e2_dequant / e0_dequant: the oracle with the format forced
+    from tests.golden_io import candidate_cases
+    cases = {c.name: c for c in quant_cases()}
+    for name, d in candidate_cases().items():
+        if name == "probe":
+            continue
+        x = cases[name].x_f32()
+        rows, k, groups, kp, tail = (int(v) for v in d["meta"])
+        assert (rows, k) == x.shape and kp == groups * 16 and tail == (-k) % 16
+        xp = np.pad(x, ((0, 0), (0, tail)))
+        assert np.array_equal(xp.reshape(rows, groups, 16).view(np.uint32), d["grouped_original"].view(np.uint32))
+        for mode, key in (("all_e2m1", "e2_dequant"), ("all_e0m3", "e0_dequant")):
+            got = oracle.dequant(oracle.quantize(xp, mode), "f32")
+            assert np.array_equal(got.reshape(rows, groups, 16).view(np.uint32), d[key].view(np.uint32)), (name, key)
