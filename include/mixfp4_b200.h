@@ -78,7 +78,11 @@ enum {
      * stream is still draining.  It prefetches the packed weight early and reads x only
      * after the previous kernel has completed.  Set it only if the previous kernel in the
      * stream does not write this call's packed weight, decode table or global scale. */
-    MIXFP4_FLAG_OVERLAP_PREVIOUS = 1
+    MIXFP4_FLAG_OVERLAP_PREVIOUS = 1,
+    /* Every `lut` of the call points to a table from mixfp4_decode_table_wide (36864 bytes: the
+     * 4 KB table followed by its eightfold, bank-interleaved copy).  The stream-layout decode
+     * kernel then takes the tables with one bulk copy instead of replicating them in every CTA. */
+    MIXFP4_FLAG_WIDE_TABLE = 2
 };
 
 /* format selection (project_quant/region.py:22-39 mode names) */
@@ -178,6 +182,11 @@ MIXFP4_API int mixfp4_repack_from_stream(const uint8_t* chunks, int64_t rows, in
  * byte) holding the block's eight bf16 magnitudes bf16((level * scale) * global).  Optional
  * input of the linear kernels (they build it per launch when given NULL). */
 MIXFP4_API int mixfp4_decode_table(const float* global_scale, void* lut, void* stream);
+/* The same table (first 4096 bytes, usable wherever a `lut` is taken) followed by 32768 bytes that
+ * hold every entry eight times (entry e, copy j at 4096 + (8 e + j) * 16): the image the
+ * stream-layout decode kernel keeps in shared memory, where a quarter-warp's eight look-ups then
+ * never share a bank.  lut: 36864 bytes, 16-byte aligned.  See MIXFP4_FLAG_WIDE_TABLE. */
+MIXFP4_API int mixfp4_decode_table_wide(const float* global_scale, void* lut, void* stream);
 
 /* Normalised block Hadamard along the last axis (project_quant/rotation.py:47-75
  * fwht / apply_transform).  size in {16,32,64,128}; only whole blocks are transformed,

@@ -21,6 +21,14 @@ BF16, F16, F32 = 0, 1, 2
 MODE_ORACLE16, MODE_ALL_E2M1, MODE_ALL_E0M3, MODE_GIVEN = 0, 1, 2, 3
 LAYOUT_CANONICAL, LAYOUT_KERNEL, LAYOUT_STREAM = 0, 1, 2
 FLAG_OVERLAP_PREVIOUS = 1
+FLAG_WIDE_TABLE = 2
+WIDE_TABLE_BYTES = 4096 + 32768
+
+
+def gemv_flags(overlap_previous: bool, *luts) -> int:
+    """Flags of a decode call: programmatic dependent launch, and whether every table is a wide one."""
+    wide = bool(luts) and all(t is not None and t.numel() >= WIDE_TABLE_BYTES for t in luts)
+    return (FLAG_OVERLAP_PREVIOUS if overlap_previous else 0) | (FLAG_WIDE_TABLE if wide else 0)
 
 DTYPE_CODE = {torch.bfloat16: BF16, torch.float16: F16, torch.float32: F32}
 
@@ -71,6 +79,8 @@ def _declare(h: ctypes.CDLL) -> None:
     h.mixfp4_dequant.argtypes = [p, p, p, p, i64, i64, i32, p, i32, i64, p]
     h.mixfp4_repack.restype = i32
     h.mixfp4_repack.argtypes = [p, p, p, i64, i64, i32, p, p, p, p]
+    h.mixfp4_decode_table_wide.restype = i32
+    h.mixfp4_decode_table_wide.argtypes = [p, p, p]
     h.mixfp4_decode_table.restype = i32
     h.mixfp4_decode_table.argtypes = [p, p, p]
     h.mixfp4_fwht.restype = i32
@@ -124,7 +134,7 @@ def _declare(h: ctypes.CDLL) -> None:
 # every symbol include/mixfp4_b200.h declares
 EXPORTED = (
     "mixfp4_abi_version", "mixfp4_status_string", "mixfp4_last_cuda_error", "mixfp4_padded_k",
-    "mixfp4_amax", "mixfp4_quantize", "mixfp4_fake_quantize", "mixfp4_select_regions", "mixfp4_selftest_division", "mixfp4_round_codebook", "mixfp4_dequant", "mixfp4_repack", "mixfp4_decode_table", "mixfp4_fwht",
+    "mixfp4_amax", "mixfp4_quantize", "mixfp4_fake_quantize", "mixfp4_select_regions", "mixfp4_selftest_division", "mixfp4_round_codebook", "mixfp4_dequant", "mixfp4_repack", "mixfp4_decode_table", "mixfp4_decode_table_wide", "mixfp4_fwht",
     "mixfp4_stream_bytes", "mixfp4_repack_stream", "mixfp4_repack_from_stream",
     "mixfp4_gemv", "mixfp4_gemv_x_fits", "mixfp4_gemv_grouped",
     "mixfp4_comm_create", "mixfp4_comm_handle_bytes", "mixfp4_comm_handle", "mixfp4_comm_open",

@@ -29,6 +29,10 @@
 namespace mixfp4 {
 namespace {
 
+#ifdef MIXFP4_DECODE_FMA_SHIFTS
+#define decode8_kl decode8_kl_v
+#endif
+
 constexpr int kMaxSeg = 3;
 
 struct StreamSeg {
@@ -45,16 +49,17 @@ struct GemvStreamArgs {
     int64_t ldx, k, kpad;
     int m, nseg, ntiles, out_dtype;
     bool x_vec;
+    bool wide_lut;                         // every segment's table is followed by its eightfold copy (mixfp4_decode_table_wide)
     StreamSeg seg[kMaxSeg];
     AllReduceArgs ar;                      // used by the all-reduce instantiation only
     int* status;                           // device word: nonzero after an expired wait
     uint64_t wait_ns;                      // limit of every wait on a chunk
 #ifdef MIXFP4_TRACE
-    unsigned long long* trace;             // [launch % 64][CTA][8] globaltimer stamps
+    unsigned long long* trace;             // [launch % 64][CTA][16] globaltimer stamps
 #endif
 };
 #ifdef MIXFP4_TRACE
-#define MIXFP4_STAMP(i) do { if (a.trace && lane == 0 && (warp == 0 || warp == kWarps - 1)) a.trace[(size_t)blockIdx.x * 8 + (i) + (warp ? 4 : 0)] = gemv_timer_ns(); } while (0)
+#define MIXFP4_STAMP(i) do { if (a.trace && lane == 0 && (warp == 0 || warp == kWarps - 1)) a.trace[(size_t)blockIdx.x * 16 + (i) + (warp ? 8 : 0)] = gemv_timer_ns(); } while (0)
 #else
 #define MIXFP4_STAMP(i) do { } while (0)
 #endif
@@ -103,9 +108,12 @@ __device__ __forceinline__ bool wait_chunk(uint32_t bar, uint32_t parity, uint64
 template <int kWarps, int kDepth, bool kAR, int kNT, int kLutRep>
 __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvStreamArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
+#ifdef MIXFP4_TRACE
+    const unsigned long long t_top = gemv_timer_ns();
+#endif
     constexpr int kThreadsS = kWarps * 32;
     constexpr uint32_t kLutBytesS = 256u * 16u * kLutRep;
-    constexpr uint32_t kBarBytes = (kWarps * kDepth * 8 + 127) & ~127;
+    constexpr uint32_t kBarBytes = (kWarps * kDepth * 8 + 8 + 127) & ~127;      // the rings' barriers and the tables' one
     // the warp index through a shuffle: provably warp-uniform, so everything derived from it stays
     // on the uniform datapath
     const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
@@ -172,35 +180,55 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
     // the main loop fills the ring.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     MIXFP4_STAMP(0);
+#ifdef MIXFP4_TRACE
+    if (a.trace && lane == 0 && (warp == 0 || warp == kWarps - 1)) a.trace[(size_t)blockIdx.x * 16 + 10 + (warp ? 1 : 0)] = t_top;
+#endif
+    // Tables: with the eightfold table in global memory (mixfp4_decode_table_wide) one thread hands each
+    // segment's 32 KB to the copy engine before anything else; otherwise every thread loads a few
+    // entries and stores their copies.  x goes through cp.async by all threads either way: a bulk copy
+    // of x would queue behind the weight chunks already handed to the copy engine.
+    const bool bulk = kLutRep == 8 && a.wide_lut;
+    const uint32_t bar_lut = sbase + kWarps * kDepth * 8;
     if (lane == 0) {
 #pragma unroll
         for (int d = 0; d < kDepth; ++d) mbar_init(bars + d * 8, 1);
+        if (warp == 0) mbar_init(bar_lut, 1);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the copy engine sees initialised barriers
     }
     __syncwarp();
-    Cursor p = make_cursor(wa);
-    if (cnt > 0) { issue(p, 0); advance(p); }
-
-    // Table entries go through registers: loaded here, stored after the x copies have been issued,
-    // so the two latencies overlap.  (entry, copy) pairs: a warp writes 512 contiguous bytes.
-    constexpr int kLutIters = (256 * kLutRep + kThreadsS - 1) / kThreadsS;
-    uint4 tv[kMaxSeg][kLutIters];
-#pragma unroll
-    for (int s = 0; s < kMaxSeg; ++s) {
-        if (s >= a.nseg) break;
-        const uint4* lut = a.seg[s].lut;
-        const float gs = lut ? 0.0f : *a.seg[s].global_scale;
-#pragma unroll
-        for (int it = 0; it < kLutIters; ++it) {
-            const int e = min((int)threadIdx.x + it * kThreadsS, 256 * kLutRep - 1) / kLutRep;
-            tv[s][it] = lut ? __ldg(lut + e) : make_lut_entry(e & 127, e >> 7, gs);
+    MIXFP4_STAMP(5);
+    if (bulk && threadIdx.x == 0) {
+        mbar_expect_tx(bar_lut, (uint32_t)a.nseg * kLutBytesS);
+        for (int sgm = 0; sgm < a.nseg; ++sgm) {
+            const uint4* lut = sgm == 0 ? a.seg[0].lut : sgm == 1 ? a.seg[1].lut : a.seg[2].lut;
+            bulk_load(lut_base + sgm * kLutBytesS, reinterpret_cast<const uint8_t*>(lut) + 4096, kLutBytesS, bar_lut);
         }
     }
-    // The rest of the ring.  These issues can stall while the copy engine's queue is full, which is
-    // harmless here: under programmatic dependent launch this CTA waits for the previous kernel next.
+    if (cnt == 0)                        // a warp without chunks adds zeros where the tile sums are collected
+        for (int v = lane; v < kRowsPerCta * m; v += 32) pieces[(size_t)(warp * 2 * kRowsPerCta) * m + v] = 0.0f;
+    MIXFP4_STAMP(6);
+    Cursor p = make_cursor(wa);
+    MIXFP4_STAMP(7);
+    if (cnt > 0) { issue(p, 0); advance(p); }
+    MIXFP4_STAMP(4);
+
+    // Without the wide table: entries go through registers, loaded here and stored after the x copies
+    // have been issued, so the two latencies overlap.  (entry, copy) pairs: a warp writes 512 contiguous bytes.
+    constexpr int kLutIters = (256 * kLutRep + kThreadsS - 1) / kThreadsS;
+    uint4 tv[kMaxSeg][kLutIters];
+    if (!bulk) {
 #pragma unroll
-    for (int d = 1; d < kDepth; ++d)
-        if (d < cnt) { issue(p, d); advance(p); }
+        for (int sgm = 0; sgm < kMaxSeg; ++sgm) {
+            if (sgm >= a.nseg) break;
+            const uint4* lut = a.seg[sgm].lut;
+            const float gs = lut ? 0.0f : *a.seg[sgm].global_scale;
+#pragma unroll
+            for (int it = 0; it < kLutIters; ++it) {
+                const int e = min((int)threadIdx.x + it * kThreadsS, 256 * kLutRep - 1) / kLutRep;
+                tv[sgm][it] = lut ? __ldg(lut + e) : make_lut_entry(e & 127, e >> 7, gs);
+            }
+        }
+    }
     // x may be the previous kernel's output: wait for it (no-op without the launch attribute).
     asm volatile("griddepcontrol.wait;" ::: "memory");
     MIXFP4_STAMP(1);
@@ -224,17 +252,26 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
         }
     }
     cp_async_commit();
+    // The rest of the ring, after x has been asked for: a bulk copy stalls its issuer while the copy
+    // engine's queue is full (a few microseconds when every warp fills its ring at once), and the
+    // first multiply needs only the tables, x and the first chunk.
 #pragma unroll
-    for (int s = 0; s < kMaxSeg; ++s) {
-        if (s >= a.nseg) break;
+    for (int d = 1; d < kDepth; ++d)
+        if (d < cnt) { issue(p, d); advance(p); }
+    if (!bulk) {
 #pragma unroll
-        for (int it = 0; it < kLutIters; ++it) {
-            const int i = threadIdx.x + it * kThreadsS;
-            if (i < 256 * kLutRep) sts128(lut_base + s * kLutBytesS + i * 16, tv[s][it]);
+        for (int sgm = 0; sgm < kMaxSeg; ++sgm) {
+            if (sgm >= a.nseg) break;
+#pragma unroll
+            for (int it = 0; it < kLutIters; ++it) {
+                const int i2 = threadIdx.x + it * kThreadsS;
+                if (i2 < 256 * kLutRep) sts128(lut_base + sgm * kLutBytesS + i2 * 16, tv[sgm][it]);
+            }
         }
     }
     cp_async_wait<0>();
-    __syncthreads();
+    __syncthreads();                     // x and the stored tables; also: warp 0 has initialised the table barrier
+    if (bulk && !wait_chunk(bar_lut, 0, a.wait_ns) && a.status) atomicCAS(a.status, 0, 299);
     MIXFP4_STAMP(2);
 
     // Outputs.  kAR: every value goes as a packet into every rank's buffer (this rank's included)
@@ -272,76 +309,89 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
         for (int i = 0; i < 4; ++i) acc[nt][0][i] = acc[nt][1][i] = 0.0f;
     }
 
+    // Main loop: one row tile (or the part of it inside this run) at a time, its chunks in a counted
+    // inner loop.  `issued` chunks have been handed to the copy engine; the cursor p stands at the next.
     Cursor c = make_cursor(wa);
-    int piece_sub0 = c.sub;              // first chunk (along K) of the sums now in the accumulators
-    bool head = true;                    // they include this run's first chunk
-    uint32_t slot = 0, phase = 0;
-    int i = 0;
-    for (; i < cnt; ++i) {
-        if (!__all_sync(0xffffffffu, wait_chunk(bars + slot * 8, phase, a.wait_ns))) break;
-        const uint32_t base = ring + slot * kChunkBytes;
+    int issued = cnt < kDepth ? cnt : kDepth, done = 0;
+    bool head = true;                    // the sums in the accumulators include this run's first chunk
+    bool ok = true;                      // false after a chunk did not arrive within the wait limit
+    uint32_t use = ring, use_bar = bars, phase = 0;          // ring slot of the chunk consumed next
+    while (done < cnt) {
+        const int sub0 = c.sub;
+        const int piece = min(S - sub0, cnt - done);         // chunks of this tile inside the run
         const uint32_t lut_seg = lut_lane + c.seg * kLutBytesS;
-        const uint32_t xsub = (uint32_t)c.sub * 256u;
-        const uint4 cl = lds128(base + lane * 16);
-        const uint4 ch = lds128(base + 512 + lane * 16);
-        const uint32_t sa = base + kChunkCodeBytes + g * 8 + t * 2;
-        const uint32_t sl0 = lds_u8(sa), sl1 = lds_u8(sa + 1), sh0 = lds_u8(sa + 64), sh1 = lds_u8(sa + 65);
+        uint32_t xsub = (uint32_t)sub0 * 256u;
+        for (int j = 0; j < piece; ++j) {
+            if (ok) ok = wait_chunk(use_bar, phase, a.wait_ns);
+            const uint4 cl = lds128(use + lane * 16);
+            const uint4 ch = lds128(use + 512 + lane * 16);
+            const uint32_t sa = use + kChunkCodeBytes + g * 8 + t * 2;
+            const uint32_t sl0 = lds_u8(sa), sl1 = lds_u8(sa + 1), sh0 = lds_u8(sa + 64), sh1 = lds_u8(sa + 65);
 #pragma unroll
-        for (int b = 0; b < 2; ++b) {                        // the 2 blocks of this lane's piece
-            const uint4 tl = lds128(lut_seg + (b == 0 ? sl0 : sl1) * (16u * kLutRep));
-            const uint4 th = lds128(lut_seg + (b == 0 ? sh0 : sh1) * (16u * kLutRep));
+            for (int b = 0; b < 2; ++b) {                    // the 2 blocks of this lane's piece
+                const uint4 tl = lds128(lut_seg + (b == 0 ? sl0 : sl1) * (16u * kLutRep));
+                const uint4 th = lds128(lut_seg + (b == 0 ? sh0 : sh1) * (16u * kLutRep));
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {           // 8 elements = 2 MMAs
-                const int w = 2 * b + half;                  // word index inside the piece
-                uint32_t pl[4], ph[4];
-                decode8_kl(w == 0 ? cl.x : w == 1 ? cl.y : w == 2 ? cl.z : cl.w, tl, pl);
-                decode8_kl(w == 0 ? ch.x : w == 1 ? ch.y : w == 2 ? ch.z : ch.w, th, ph);
+                for (int half = 0; half < 2; ++half) {       // 8 elements = 2 MMAs
+                    const int w = 2 * b + half;              // word index inside the piece
+                    uint32_t pl[4], ph[4];
+                    decode8_kl(w == 0 ? cl.x : w == 1 ? cl.y : w == 2 ? cl.z : cl.w, tl, pl);
+                    decode8_kl(w == 0 ? ch.x : w == 1 ? ch.y : w == 2 ? ch.z : ch.w, th, ph);
 #pragma unroll
-                for (int nt = 0; nt < kNT; ++nt) {
-                    lds128_if(xv[nt], xrow_off[nt] + xsub + w * 16, x_ok[nt]);
-                    mma_bf16(acc[nt][0], pl[0], ph[0], pl[1], ph[1], xv[nt].x, xv[nt].y);
-                    mma_bf16(acc[nt][1], pl[2], ph[2], pl[3], ph[3], xv[nt].z, xv[nt].w);
+                    for (int nt = 0; nt < kNT; ++nt) {
+                        if (x_ok[nt]) xv[nt] = lds128(xrow_off[nt] + xsub + w * 16);   // other lanes keep zeros
+                        mma_bf16(acc[nt][0], pl[0], ph[0], pl[1], ph[1], xv[nt].x, xv[nt].y);
+                        mma_bf16(acc[nt][1], pl[2], ph[2], pl[3], ph[3], xv[nt].z, xv[nt].w);
+                    }
                 }
             }
-        }
-        __syncwarp();                    // every lane has read the slot: refill it
-        if (i + kDepth < cnt) { issue(p, slot); advance(p); }
-
-        if (c.sub == S - 1 || i == cnt - 1) {
-            // End of a row tile or of the run.  accumulator fragment: c0,c1 = (row g, batch 2t, 2t+1);
-            // c2,c3 = (row g+8, same batches)
-            const bool whole = piece_sub0 == 0 && c.sub == S - 1;
-            const uint32_t row0 = (uint32_t)(c.tile - seg_first(c.seg)) * kRowsPerCta;
-            float* rw = pieces + (size_t)((warp * 2 + (head ? 0 : 1)) * kRowsPerCta) * m;
-#pragma unroll
-            for (int nt = 0; nt < kNT; ++nt) {
-                const int b0 = 8 * nt + 2 * t;
-                const float v0 = acc[nt][0][0] + acc[nt][1][0], v1 = acc[nt][0][1] + acc[nt][1][1];
-                const float v2 = acc[nt][0][2] + acc[nt][1][2], v3 = acc[nt][0][3] + acc[nt][1][3];
-                if (whole) {
-                    if (b0 < m) { emit(c.seg, row0 + g, b0, v0); emit(c.seg, row0 + g + 8, b0, v2); }
-                    if (b0 + 1 < m) { emit(c.seg, row0 + g, b0 + 1, v1); emit(c.seg, row0 + g + 8, b0 + 1, v3); }
-                } else {
-                    if (b0 < m) { rw[g * m + b0] = v0; rw[(g + 8) * m + b0] = v2; }
-                    if (b0 + 1 < m) { rw[g * m + b0 + 1] = v1; rw[(g + 8) * m + b0 + 1] = v3; }
+            __syncwarp();                // every lane has read the slot: refill it
+            if (issued < cnt) {
+                if (lane == 0) {
+                    mbar_expect_tx(use_bar, kChunkBytes);
+                    bulk_load(use, p.ptr, kChunkBytes, use_bar);
                 }
-#pragma unroll
-                for (int q = 0; q < 4; ++q) acc[nt][0][q] = acc[nt][1][q] = 0.0f;
+                advance(p);
+                ++issued;
             }
-            head = false;
-            piece_sub0 = 0;
+            xsub += 256u;
+            use += kChunkBytes;
+            use_bar += 8;
+            if (use_bar == bars + kDepth * 8) { use = ring; use_bar = bars; phase ^= 1u; }
         }
-        advance(c);
-        if (++slot == kDepth) { slot = 0; phase ^= 1u; }
+        // End of a row tile or of the run.  accumulator fragment: c0,c1 = (row g, batch 2t, 2t+1);
+        // c2,c3 = (row g+8, same batches)
+        const bool whole = sub0 == 0 && piece == S;
+        const uint32_t row0 = (uint32_t)(c.tile - seg_first(c.seg)) * kRowsPerCta;
+        float* rw = pieces + (size_t)((warp * 2 + (head ? 0 : 1)) * kRowsPerCta) * m;
+#pragma unroll
+        for (int nt = 0; nt < kNT; ++nt) {
+            const int b0 = 8 * nt + 2 * t;
+            const float v0 = acc[nt][0][0] + acc[nt][1][0], v1 = acc[nt][0][1] + acc[nt][1][1];
+            const float v2 = acc[nt][0][2] + acc[nt][1][2], v3 = acc[nt][0][3] + acc[nt][1][3];
+            if (whole) {
+                if (b0 < m) { emit(c.seg, row0 + g, b0, v0); emit(c.seg, row0 + g + 8, b0, v2); }
+                if (b0 + 1 < m) { emit(c.seg, row0 + g, b0 + 1, v1); emit(c.seg, row0 + g + 8, b0 + 1, v3); }
+            } else {
+                if (b0 < m) { rw[g * m + b0] = v0; rw[(g + 8) * m + b0] = v2; }
+                if (b0 + 1 < m) { rw[g * m + b0 + 1] = v1; rw[(g + 8) * m + b0 + 1] = v3; }
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) acc[nt][0][q] = acc[nt][1][q] = 0.0f;
+        }
+        head = false;
+        done += piece;
+        // the next tile of the run (its first chunk is the tile's first)
+        c.sub = 0;
+        ++c.tile;
+        if (c.tile == seg_end(c.seg) && c.seg + 1 < a.nseg) ++c.seg;
     }
-    if (i < cnt) {
-        // A chunk did not arrive within the limit: report it, then give the copies still in flight
-        // one more (bounded) chance to land before this CTA's shared memory is released.
+    if (!__all_sync(0xffffffffu, ok)) {
+        // A chunk did not arrive within the limit (the sums are then wrong; later chunks were not
+        // waited for): report it.
         if (lane == 0 && a.status) atomicCAS(a.status, 0, 300 + (int)(blockIdx.x & 0xff));
-        for (int j = i; j < cnt && j < i + kDepth; ++j) {
-            wait_chunk(bars + slot * 8, phase, a.wait_ns >> 2);
-            if (++slot == kDepth) { slot = 0; phase ^= 1u; }
-        }
+        const uint64_t t0 = gemv_timer_ns(), grace = a.wait_ns < 1000000ull ? a.wait_ns : 1000000ull;
+        while (gemv_timer_ns() - t0 < grace) {}      // a last (bounded) chance for copies in flight to land
     }
     if (warp != 0) MIXFP4_STAMP(3);
     __syncthreads();
@@ -353,25 +403,28 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
         const int tl = wa / S, a_sub = wa - tl * S;
         if (a_sub != 0 && (tl + 1) * S <= wb) {
             const int lo = tl * S;
-            int wf = warp;
-            while (wf > 0 && run_start(wf) > lo) --wf;       // the run that holds the tile's first chunk
+            // the run that holds the tile's first chunk: the largest w with floor(nchunks * w / kWarps) <= lo
+            const int wf = (int)(((uint32_t)kWarps * (uint32_t)(lo + 1) - 1u) / (uint32_t)nchunks);
             const int tile = t0 + tl;
             const int cs = (tile >= a.seg[0].tile_end) + (tile >= a.seg[1].tile_end);
             const uint32_t row0 = (uint32_t)(tile - seg_first(cs)) * kRowsPerCta;
             // the first run holds the tile as its tail piece unless it starts exactly at the tile; every
-            // run after it lies inside the tile (its head piece); empty runs (fewer chunks than warps)
-            // start where the next one starts, have written nothing and are skipped
+            // run after it lies inside the tile (its head piece; zeros for a run without chunks)
             const float* first_piece = pieces + (size_t)((wf * 2 + (run_start(wf) < lo ? 1 : 0)) * kRowsPerCta) * m;
+            const int stride = 2 * kRowsPerCta * m;
+            MIXFP4_STAMP(2);
             for (int v = lane; v < kRowsPerCta * m; v += 32) {
                 const int r = v % kRowsPerCta, b = v / kRowsPerCta;
                 float sum = first_piece[r * m + b];
-                for (int w2 = wf + 1; w2 <= warp; ++w2)
-                    if (run_start(w2) != run_start(w2 + 1)) sum += pieces[(size_t)(w2 * 2 * kRowsPerCta + r) * m + b];
+                const float* q = pieces + (size_t)(wf + 1) * stride + r * m + b;
+                for (int w2 = wf + 1; w2 <= warp; ++w2, q += stride) sum += *q;
+                MIXFP4_STAMP(0);
                 emit(cs, row0 + r, b, sum);
             }
         }
     }
 
+    if (warp != 0) MIXFP4_STAMP(1);      // (profiling builds: end of the last warp)
     if constexpr (kAR) {
         // Every output of this CTA's tiles: wait (bounded) for the packet of each rank and add them
         // in rank order, so that every rank ends with the same bits.
@@ -447,7 +500,7 @@ int device_info(DeviceInfo* out) {
 }
 
 #ifdef MIXFP4_TRACE
-static __device__ unsigned long long g_trace[64 * 160 * 8];
+static __device__ unsigned long long g_trace[64 * 160 * 16];
 std::atomic<unsigned> g_trace_launch{0};
 #endif
 
@@ -455,7 +508,7 @@ constexpr size_t kSmemLimit = 227 * 1024;
 
 template <int kWarps, int kDepth, bool kAR, int kNT, int kLutRep>
 int launch_stream(const GemvStreamArgs& a, int sms, int flags, cudaStream_t st) {
-    const size_t smem = ((size_t)(kWarps * kDepth * 8 + 127) & ~(size_t)127) + (size_t)kWarps * kDepth * kChunkBytes +
+    const size_t smem = ((size_t)(kWarps * kDepth * 8 + 8 + 127) & ~(size_t)127) + (size_t)kWarps * kDepth * kChunkBytes +
                         (size_t)a.nseg * 256 * 16 * kLutRep + (((size_t)a.m * xres_row_bytes(a.kpad) + 15) & ~(size_t)15) +
                         (size_t)kWarps * 2 * kRowsPerCta * a.m * 4;
     if (smem > kSmemLimit) return MIXFP4_E_SHAPE;
@@ -511,6 +564,7 @@ int gemv_stream(const void* x, int64_t m, int64_t ldx, int64_t k, const mixfp4_g
     g.ldx = ldx; g.k = k; g.kpad = padded_k(k);
     g.m = (int)m; g.nseg = count; g.out_dtype = out_dtype;
     g.x_vec = aligned(x, 16) && (ldx % 8 == 0) && (k % 8 == 0);
+    g.wide_lut = (flags & MIXFP4_FLAG_WIDE_TABLE) != 0;
     g.wait_ns = wait_limit_ns();
     const int64_t subs = g.kpad / kChunkK;
     int64_t tiles = 0;
@@ -520,6 +574,7 @@ int gemv_stream(const void* x, int64_t m, int64_t ldx, int64_t k, const mixfp4_g
             if (!in.codes || !in.global_scale || !in.y) return MIXFP4_E_NULL;
             if (in.n <= 0 || in.ldy < in.n) return MIXFP4_E_SHAPE;
             if (!aligned(in.codes, 16) || (in.lut && !aligned(in.lut, 16))) return MIXFP4_E_ALIGN;
+            if (!in.lut) g.wide_lut = false;
             tiles += stream_tiles(in.n);
             if (tiles * subs > 0x7ffffff0LL) return MIXFP4_E_SHAPE;
         }
@@ -534,7 +589,7 @@ int gemv_stream(const void* x, int64_t m, int64_t ldx, int64_t k, const mixfp4_g
     {
         void* tp = nullptr;
         MIXFP4_CUDA_CHECK(cudaGetSymbolAddress(&tp, g_trace));
-        g.trace = static_cast<unsigned long long*>(tp) + (size_t)(g_trace_launch.fetch_add(1) % 64) * 160 * 8;
+        g.trace = static_cast<unsigned long long*>(tp) + (size_t)(g_trace_launch.fetch_add(1) % 64) * 160 * 16;
     }
 #endif
     if (comm) {
@@ -562,7 +617,7 @@ using namespace mixfp4;
 extern "C" int mixfp4_gemv_x_fits(int64_t m, int64_t k, int count) {
     if (m < 1 || m > 16 || k <= 0 || count < 1 || count > kMaxSeg) return 0;
     // the smallest configuration: 16 warps, rings of 3 chunks, one table copy per weight
-    const size_t smem = 128 + (size_t)16 * 3 * kChunkBytes + (size_t)count * 4096 +
+    const size_t smem = 512 + (size_t)16 * 3 * kChunkBytes + (size_t)count * 4096 +
                         (((size_t)m * xres_row_bytes(padded_k(k)) + 15) & ~(size_t)15) + (size_t)16 * 2 * kRowsPerCta * m * 4;
     return smem <= kSmemLimit ? 1 : 0;
 }
@@ -592,7 +647,7 @@ extern "C" int mixfp4_check_status(const int* dev_status, int* value, void* stre
 // Profiling build only: copies the time stamps of the last 64 launches to the host and restarts the count.
 extern "C" __attribute__((visibility("default"))) int mixfp4_trace_read(unsigned long long* host_out) {
     MIXFP4_CUDA_CHECK(cudaDeviceSynchronize());
-    MIXFP4_CUDA_CHECK(cudaMemcpyFromSymbol(host_out, g_trace, sizeof(unsigned long long) * 64 * 160 * 8));
+    MIXFP4_CUDA_CHECK(cudaMemcpyFromSymbol(host_out, g_trace, sizeof(unsigned long long) * 64 * 160 * 16));
     g_trace_launch.store(0);
     return MIXFP4_OK;
 }

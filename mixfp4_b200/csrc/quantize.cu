@@ -570,6 +570,14 @@ __global__ void decode_table_kernel(const float* __restrict__ global_scale, uint
     lut[e] = make_lut_entry(e & 127, e >> 7, *global_scale);
 }
 
+__global__ void decode_table_wide_kernel(const float* __restrict__ global_scale, uint4* __restrict__ lut) {
+    const int e = threadIdx.x;
+    const uint4 v = make_lut_entry(e & 127, e >> 7, *global_scale);
+    lut[e] = v;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) lut[256 + e * 8 + j] = v;
+}
+
 size_t elem_size(int dtype) { return dtype == MIXFP4_F32 ? 4 : 2; }
 
 bool rows_vectorizable(const void* p, int64_t ld, int dtype) {
@@ -810,6 +818,13 @@ extern "C" int mixfp4_decode_table(const float* global_scale, void* lut, void* s
     if (!aligned(lut, 16)) return MIXFP4_E_ALIGN;
     decode_table_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(global_scale, static_cast<uint4*>(lut));
     return check_launch("decode_table_kernel");
+}
+
+extern "C" int mixfp4_decode_table_wide(const float* global_scale, void* lut, void* stream) {
+    if (!global_scale || !lut) return MIXFP4_E_NULL;
+    if (!aligned(lut, 16)) return MIXFP4_E_ALIGN;
+    decode_table_wide_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(global_scale, static_cast<uint4*>(lut));
+    return check_launch("decode_table_wide_kernel");
 }
 
 extern "C" int mixfp4_selftest_division(unsigned long long* mismatches, void* stream) {

@@ -140,7 +140,7 @@ def mixfp4_linear(x: torch.Tensor, packed: PackedWeight, *, bias: torch.Tensor |
             st = lib.mixfp4_gemv(x2.data_ptr(), m, x2.stride(0), packed.codes.data_ptr(), packed.scales.data_ptr(),
                                  nat.ptr(packed.fmt), packed.global_scale.data_ptr(), packed.n, packed.k,
                                  packed.layout_code, nat.ptr(packed.lut), y.data_ptr(), nat.DTYPE_CODE[out_dtype],
-                                 y.stride(0), nat.FLAG_OVERLAP_PREVIOUS if overlap_previous else 0, stream)
+                                 y.stride(0), nat.gemv_flags(overlap_previous, packed.lut), stream)
             nat.check("mixfp4_gemv", st)
         else:
             fused = 0
@@ -193,7 +193,7 @@ def mixfp4_linear_grouped(x: torch.Tensor, packs: list[PackedWeight], *, out_dty
         with torch.cuda.device(x.device):
             st = nat.lib().mixfp4_gemv_grouped(x2.data_ptr(), m, x2.stride(0), k, segs, len(packs),
                                                packs[0].layout_code, nat.DTYPE_CODE[out_dtype],
-                                               nat.FLAG_OVERLAP_PREVIOUS if overlap_previous else 0,
+                                               nat.gemv_flags(overlap_previous, *[p.lut for p in packs]),
                                                nat.stream_ptr(x.device))
         if st != nat.E_SHAPE:
             nat.check("mixfp4_gemv_grouped", st)

@@ -149,7 +149,7 @@ class PeerCommunicator:
                 self.handle, x2.data_ptr(), m, x2.stride(0), packed_shard.codes.data_ptr(), nat.ptr(packed_shard.scales),
                 packed_shard.global_scale.data_ptr(), nat.ptr(packed_shard.lut), packed_shard.n, k,
                 packed_shard.layout_code, y.data_ptr(), nat.DTYPE_CODE[out_dtype], y.stride(0), self.status.data_ptr(),
-                nat.FLAG_OVERLAP_PREVIOUS if overlap_previous else 0, nat.stream_ptr(x_shard.device))
+                nat.gemv_flags(overlap_previous, packed_shard.lut), nat.stream_ptr(x_shard.device))
         if st == nat.E_SHAPE:
             return None
         nat.check("mixfp4_gemv_allreduce", st)

@@ -131,12 +131,15 @@ class PackedWeight:
                             int(state["n"]), int(state["k"]), state.get("rotation"), state.get("layout", "canonical"))
 
     def with_decode_table(self) -> "PackedWeight":
-        """Attach the 4 KB (format, scale) -> bf16 magnitudes table so that the linear kernels
-        copy it instead of rebuilding it in every launch."""
-        if self.lut is None:
-            lut = torch.empty(4096, dtype=torch.uint8, device=self.device)
+        """Attach the (format, scale) -> bf16 magnitudes table so that the linear kernels copy it
+        instead of rebuilding it in every launch: 4 KB, followed for the stream layout by the eightfold
+        copy the decode kernel keeps in shared memory (36 KB in all, taken with one bulk copy)."""
+        wide = self.layout == "stream"
+        if self.lut is None or (wide and self.lut.numel() < nat.WIDE_TABLE_BYTES):
+            lut = torch.empty(nat.WIDE_TABLE_BYTES if wide else 4096, dtype=torch.uint8, device=self.device)
+            fn = nat.lib().mixfp4_decode_table_wide if wide else nat.lib().mixfp4_decode_table
             with torch.cuda.device(self.device):
-                st = nat.lib().mixfp4_decode_table(self.global_scale.data_ptr(), lut.data_ptr(), nat.stream_ptr(self.device))
+                st = fn(self.global_scale.data_ptr(), lut.data_ptr(), nat.stream_ptr(self.device))
             nat.check("mixfp4_decode_table", st)
             self.lut = lut
         return self

@@ -61,7 +61,8 @@ class LocalComm:
         st = self.lib.mixfp4_gemv_allreduce(
             self.handle, x.data_ptr(), m, x.stride(0), packed.codes.data_ptr(), nat.ptr(packed.scales),
             packed.global_scale.data_ptr(), nat.ptr(packed.lut), packed.n, packed.k, packed.layout_code, y.data_ptr(),
-            nat.DTYPE_CODE[out_dtype], y.stride(0), self.status.data_ptr(), 0, nat.stream_ptr(x.device))
+            nat.DTYPE_CODE[out_dtype], y.stride(0), self.status.data_ptr(), nat.gemv_flags(False, packed.lut),
+            nat.stream_ptr(x.device))
         nat.check("mixfp4_gemv_allreduce", st)
         torch.cuda.synchronize()
         return y
