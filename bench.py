@@ -147,6 +147,7 @@ def build_model(device, rank: int, world: int, m: int, layout: str = "stream"):
             del z, chi
             row_parallel = name in ("o", "down")
             amax = mx.tensor_amax(w)
+            full = w
             if world > 1:
                 if row_parallel:       # split K
                     step = k // world
@@ -154,8 +155,14 @@ def build_model(device, rank: int, world: int, m: int, layout: str = "stream"):
                 else:                  # split N
                     step = n // world
                     w = w[rank * step:(rank + 1) * step].contiguous()
+            if li == 0 and name in ("o", "down"):
+                # the unsharded weight of layer 0, dequantized by the (bit-exact) dequant kernel: the
+                # reference of the correctness check printed with the result
+                entry["full_" + name] = mx.dequantize(mx.quantize_packed(full, amax=amax)[0]) if world > 1 else None
             packed, _, _ = mx.quantize_packed(w, amax=amax)
             entry[name] = to_layout(packed, layout)
+            if li == 0 and name in ("o", "down") and world == 1:
+                entry["full_" + name] = mx.dequantize(packed)
             del w
         model.append(entry)
     torch.cuda.synchronize(device)
@@ -192,6 +199,51 @@ def decode_pass(model, h, world: int, out_dtype=torch.bfloat16, comm=None):
     return out
 
 
+def rel_err(y: torch.Tensor, ref: torch.Tensor) -> float:
+    y, ref = y.double(), ref.double()
+    return float((y - ref).norm() / ref.norm().clamp_min(1e-300))
+
+
+def correctness_check(model, world: int, rank: int, m: int, comm, dev) -> dict:
+    """Layer 0's o and down projections, outside the timed region, against a float64 matmul on the
+    dequantized UNSHARDED weight (mixfp4_dequant: bit-equal to the reference's dequantized weight).
+    One GPU: the decode kernel alone.  Several GPUs: the fused GEMV + all-reduce and the GEMV followed
+    by an NCCL all-reduce of fp32 partial sums; also whether all ranks hold the same bits."""
+    import torch.distributed as dist
+    import mixfp4_b200 as mx
+    out = {"tolerance": 1e-3}
+    worst, same_bits, fused_vs_nccl = 0.0, True, 0.0
+    for name in ("o", "down"):
+        shard = model[0][name]
+        wfull = model[0]["full_" + name]
+        kfull = wfull.shape[1]
+        x = torch.randn((m, kfull), generator=torch.Generator().manual_seed(11)).to(torch.bfloat16).to(dev)
+        ref = x.double() @ wfull.double().T
+        step = kfull // world
+        xs = x[:, rank * step:(rank + 1) * step].contiguous() if world > 1 else x
+        y_plain = mx.mixfp4_linear(xs, shard, out_dtype=torch.float32)
+        if world > 1:
+            dist.all_reduce(y_plain)
+            if comm is not None:
+                y_fused = comm.linear(xs, shard, out_dtype=torch.float32)
+                worst = max(worst, rel_err(y_fused, ref))
+                fused_vs_nccl = max(fused_vs_nccl, rel_err(y_fused, y_plain))
+                gathered = [torch.empty_like(y_fused) for _ in range(world)]
+                dist.all_gather(gathered, y_fused)
+                same_bits = same_bits and all(torch.equal(g, gathered[0]) for g in gathered)
+        worst = max(worst, rel_err(y_plain, ref))
+        out[name + "_rel"] = round(rel_err(y_plain, ref), 9)
+    flag = torch.tensor([worst, fused_vs_nccl, 0.0 if same_bits else 1.0], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+    worst, fused_vs_nccl, differ = flag.tolist()
+    out.update({"vs_dequantized_fp64_rel": round(worst, 9), "ok": bool(worst <= 1e-3 and differ == 0.0)})
+    if world > 1:
+        out.update({"fused_vs_nccl_rel": round(fused_vs_nccl, 9), "all_ranks_same_bits": differ == 0.0,
+                    "fused_path": comm is not None})
+    return out
+
+
 def run_ours(args):
     import torch.distributed as dist
     import mixfp4_b200 as mx
@@ -220,6 +272,12 @@ def run_ours(args):
     if world > 1 and not args.nccl_allreduce and m <= 8:
         from mixfp4_b200.parallel import PeerCommunicator
         comm = PeerCommunicator(slot_floats=m * 4096, device=dev)
+
+    check = correctness_check(model, world, rank, m, comm, dev)
+    if not check["ok"]:
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "error": "correctness check failed", "check": check}), flush=True)
+        os._exit(3)
 
     side = torch.cuda.Stream(dev)
     side.wait_stream(torch.cuda.current_stream(dev))
@@ -272,19 +330,34 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dev_ms, e2e_ms = t.tolist()
 
+    finite = bool(torch.isfinite(static_out.float()).all().item())
+    fused = comm is not None
+    peer_status = int(comm.status.item()) if comm is not None else None
+    decode_status = mx.decode_status(dev)
     extra = {}
-    if rank == 0 and world == 1 and not args.no_extra:
-        extra = secondary_numbers(dev)
-        extra["decode_tokens_per_s_linears_only"] = round(1e3 / dev_ms * m, 1)
-        # whole decoder (norms, RoPE, attention over a 2048-token bf16 KV cache, bf16 head as stock
-        # PyTorch operators around the packed linears): tokens/s and the linears' share of a step
-        del model, graph
+    if not args.no_extra:
+        del model, graph, static_out
+        if comm is not None:
+            comm.close()
+            comm = None
         torch.cuda.empty_cache()
         from mixfp4_b200 import llama_decode
-        for batch in (1, 8):
-            r = llama_decode.run(layers=nlayers, batch=batch, prompt=2048, tokens=16, device=dev)
+        if world == 1:
+            # short kernels first: the sections after them keep the GPU under its power cap for seconds
+            extra.update(secondary_numbers(dev))
+            extra["decode_tokens_per_s_linears_only"] = round(1e3 / dev_ms * m, 1)
+            extra["prefill_h128"] = prefill_sweep(dev)
+            torch.cuda.empty_cache()
+        extra["tp70b"] = tp70b(dev, rank, world, args.layout)
+        torch.cuda.empty_cache()
+        # whole decoder (norms, RoPE, attention over a bf16 KV cache, bf16 head as stock PyTorch operators
+        # around the packed linears): tokens/s and the linears' share of a step; head-parallel over the ranks
+        keep = {}
+        for batch, prompt in ((1, 2048), (8, 2048), (16, 2048), (32, 2048)) if world == 1 else ((1, 2048), (8, 2048)):
+            r = llama_decode.run(layers=nlayers, batch=batch, prompt=prompt, tokens=8, device=dev, tp=world,
+                                 weights=keep.get("weights"), keep=keep)
             extra["decode_full_model_b%d" % batch] = {k: r[k] for k in (
-                "decode_tokens_per_s", "decode_ms_per_step", "mixfp4_linear_time_fraction", "prefill_tokens_per_s")}
+                "decode_tokens_per_s", "decode_ms_per_step", "mixfp4_linear_time_fraction", "prefill_tokens_per_s", "tp")}
 
     if rank == 0:
         peak, peak_kind = measured_peak()
@@ -296,7 +369,7 @@ def run_ours(args):
             "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic", "impl": "ours",
             "config": {"workload": "llama3-8b decode linears, M=%d, 32 layers x 7 linears in 4 launches (q/k/v and gate/up grouped), mixed E2M1/E0M3 K16 blocks" % m,
-                       "parallelism": ("tp%d, all-reduce %s" % (world, "fused into the row-parallel GEMV" if comm else "NCCL")) if world > 1 else "single",
+                       "parallelism": ("tp%d, all-reduce %s" % (world, "fused into the row-parallel GEMV" if fused else "NCCL")) if world > 1 else "single",
                        "l2": "working set 3.98 GB of distinct weights >> 126 MB L2 (no flush needed)",
                        "timing": "cuda events around graph replays, max over ranks"},
             "clocks": clocks,
@@ -308,7 +381,8 @@ def run_ours(args):
                          "frac": round(per_gpu / peak, 4), "peak_kind": peak_kind, "kernel": "gemv_stream_kernel" if args.layout == "stream" else "gemv_sm_kernel",
                          "traffic": TRAFFIC_BYTES_PER_LAUNCH,
                          "note": "achieved = algorithmic bytes of the %d GEMV launches of a step / CUDA-event time" % launches_per_step},
-            "peer_wait_status": int(comm.status.item()) if comm is not None else None,
+            "check": check, "tp_check": check if world > 1 else None, "output_finite": finite, "decode_status": decode_status,
+            "peer_wait_status": peer_status,
             "cpu_baseline": cpu_baseline(m, budget_s=12.0) if world == 1 and not args.no_cpu else None,
             "extra": extra,
         }
@@ -321,6 +395,217 @@ def run_ours(args):
         dist.barrier()
         sys.stdout.flush()
         os._exit(0)
+
+
+def graph_time(fn, dev, iters: int, world: int = 1) -> float:
+    """Seconds per call of fn, captured once as a CUDA graph and replayed (max over ranks)."""
+    import torch.distributed as dist
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        fn()
+        torch.cuda.synchronize(dev)
+        with torch.cuda.graph(g, stream=side):
+            fn()
+    for _ in range(3):
+        g.replay()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(dev)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        g.replay()
+    b.record()
+    torch.cuda.synchronize(dev)
+    t = torch.tensor([a.elapsed_time(b) / iters * 1e-3], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    del g
+    return float(t.item())
+
+
+def tp70b(dev, rank: int, world: int, layout: str) -> dict:
+    """BASELINE config 4: Llama-3-70B-shaped linears (hidden 8192, kv 1024, FFN 28672) tensor-parallel
+    over the ranks -- q/k/v/gate/up split along N, o/down along K.  Four distinct layers are cycled
+    (a layer is 488 MB packed, so four exceed the L2 many times over).
+      decode  M = 1: the seven linears of each layer in four launches, the row-parallel ones with the
+              all-reduce fused into the GEMV (NCCL-free) when there is more than one rank;
+      prefill M = 4096: gate, up (column-parallel) and down (row-parallel) through the tcgen05 GEMM,
+              the [4096, 8192] bf16 partial sums of down all-reduced by NCCL, once in stream order and
+              once on a side stream under the next layer's GEMMs;
+      quantize: the 80-layer weight quantization sharded by layer (layer l on rank l mod N), timed on
+              one layer's set of unsharded weights per owned layer.
+    Values are whole-job figures (all ranks), times the maximum over ranks."""
+    import torch.distributed as dist
+    import mixfp4_b200 as mx
+    from mixfp4_b200 import synth
+    from mixfp4_b200.parallel import PeerCommunicator
+    hidden, kvd, ffn, cycled = 8192, 1024, 28672, 4
+    shapes = {"q": (hidden, hidden), "k": (kvd, hidden), "v": (kvd, hidden), "o": (hidden, hidden),
+              "gate": (ffn, hidden), "up": (ffn, hidden), "down": (hidden, ffn)}
+    gen = torch.Generator(device=dev)
+
+    def weight(n, k, seed):
+        gen.manual_seed(seed)
+        return (torch.randn((n, k), generator=gen, device=dev) * 0.02).to(torch.bfloat16)
+
+    # ---- layer-sharded quantization of 80 layers (unsharded shapes), before anything else holds memory
+    full = {name: weight(n, k, 7000 + i) for i, (name, (n, k)) in enumerate(shapes.items()) if name not in ("v", "up")}
+    full["v"], full["up"] = full["k"], full["gate"]
+    owned = len(range(rank, synth.LLAMA3_70B_NUM_LAYERS, world))
+    for w in full.values():
+        mx.quantize_packed(w)
+    torch.cuda.synchronize(dev)
+    t0 = time.perf_counter()
+    for _ in range(owned):
+        for name in shapes:
+            mx.quantize_packed(full[name])
+    torch.cuda.synchronize(dev)
+    tq = torch.tensor([time.perf_counter() - t0], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(tq, op=dist.ReduceOp.MAX)
+    elems_layer = sum(n * k for n, k in shapes.values())
+    out = {"quantize_80_layers_s": round(float(tq.item()), 4),
+           "quantize_gelem_per_s": round(80 * elems_layer / float(tq.item()) / 1e9, 1),
+           "layers_per_rank": owned}
+
+    # ---- sharded packed layers
+    layers = []
+    for li in range(cycled):
+        entry = {}
+        for i, (name, (n, k)) in enumerate(shapes.items()):
+            w = weight(n, k, 100 * li + i)
+            amax = mx.tensor_amax(w)
+            if world > 1:
+                if name in ("o", "down"):
+                    step = k // world
+                    w = w[:, rank * step:(rank + 1) * step].contiguous()
+                else:
+                    step = n // world
+                    w = w[rank * step:(rank + 1) * step].contiguous()
+            entry[name] = to_layout(mx.quantize_packed(w, amax=amax)[0], layout)
+            del w
+        layers.append(entry)
+    del full
+    torch.cuda.empty_cache()
+    layer_bytes = sum(algorithmic_bytes(n, k, 1) for n, k in shapes.values())
+    comm = PeerCommunicator(slot_floats=hidden, device=dev) if world > 1 else None
+    x1 = torch.randn((1, hidden), device=dev).to(torch.bfloat16)
+
+    def decode():
+        for layer in layers:
+            q, _, _ = mx.mixfp4_linear_grouped(x1, [layer["q"], layer["k"], layer["v"]], overlap_previous=True)
+            if comm is not None:
+                o = comm.linear(q, layer["o"], overlap_previous=True)
+            else:
+                o = mx.mixfp4_linear(q, layer["o"], overlap_previous=True)
+            g, _ = mx.mixfp4_linear_grouped(o, [layer["gate"], layer["up"]], overlap_previous=True)
+            if comm is not None:
+                comm.linear(g, layer["down"], overlap_previous=True)
+            else:
+                mx.mixfp4_linear(g, layer["down"], overlap_previous=True)
+
+    t = graph_time(decode, dev, 10, world) / cycled
+    peak, _ = measured_peak()
+    out["decode_m1"] = {"ms_per_layer": round(t * 1e3, 4), "gbs": round(layer_bytes / t / 1e9, 1),
+                        "per_gpu_frac_of_hbm": round(layer_bytes / t / 1e9 / world / peak, 4),
+                        "tokens_per_s_80_layers_linears_only": round(1.0 / (80 * t), 1),
+                        "all_reduce": "fused into the GEMV" if comm is not None else "none (one GPU)"}
+    if comm is not None:
+        out["decode_m1"]["peer_wait_status"] = int(comm.status.item())
+
+    # ---- prefill MLP at M = 4096
+    mtok = 4096
+    xp = torch.randn((mtok, hidden), device=dev).to(torch.bfloat16)
+    side = torch.cuda.Stream(dev)
+    flops_layer = 2.0 * mtok * 3 * ffn * hidden
+
+    def prefill(overlap: bool):
+        pending = None
+        for layer in layers:
+            g = mx.mixfp4_linear(xp, layer["gate"])
+            mx.mixfp4_linear(xp, layer["up"])
+            d = mx.mixfp4_linear(g, layer["down"])               # [4096, 8192] bf16 partial sums of this rank's K shard
+            if world > 1:
+                if overlap:
+                    ev = torch.cuda.Event()
+                    ev.record()
+                    with torch.cuda.stream(side):
+                        side.wait_event(ev)
+                        dist.all_reduce(d)
+                        pending = torch.cuda.Event()
+                        pending.record()
+                else:
+                    dist.all_reduce(d)
+        if pending is not None:
+            torch.cuda.current_stream(dev).wait_event(pending)
+
+    def timed_prefill(overlap):
+        for _ in range(2):
+            prefill(overlap)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(3):
+            prefill(overlap)
+        b.record()
+        torch.cuda.synchronize(dev)
+        tt = torch.tensor([a.elapsed_time(b) / 3 / cycled * 1e-3], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return float(tt.item())
+
+    tp = timed_prefill(False)
+    out["prefill_m4096_mlp"] = {"ms_per_layer": round(tp * 1e3, 3), "tflops": round(flops_layer / tp / 1e12, 1),
+                                "all_reduce": "NCCL, bf16 [4096, 8192], in stream order" if world > 1 else "none (one GPU)",
+                                "gemm_status": mx.gemm_status(dev)}
+    if world > 1:
+        to = timed_prefill(True)
+        out["prefill_m4096_mlp"]["tflops_all_reduce_on_side_stream"] = round(flops_layer / to / 1e12, 1)
+    if comm is not None:
+        comm.close()
+    return out
+
+
+def prefill_sweep(dev) -> dict:
+    """BASELINE config 3: the Llama-3-8B layer shapes at M = 512, 2048 and 8192 through the tcgen05
+    GEMM with the H128 rotation of x applied inside the call (weights rotated before quantization),
+    activations N(0,1) with 1 % of the channels scaled by 30, bf16 out.  TFLOP/s and the fraction of
+    the measured dense bf16 peak."""
+    import mixfp4_b200 as mx
+    from mixfp4_b200 import synth
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peak_tf = float(json.load(f)["bf16_tflops"])
+    except Exception:
+        peak_tf = 1590.0
+    out = {}
+    shapes = {"q": (4096, 4096), "kv": (1024, 4096), "o": (4096, 4096), "gate_up": (14336, 4096), "down": (4096, 14336)}
+    for name, (n, k) in shapes.items():
+        w = (torch.randn((n, k), device=dev) * 0.02).to(torch.bfloat16)
+        packed = mx.quantize_packed(mx.apply_transform(w, "H128"), rotation="H128")[0].to_stream_layout()
+        for m in (512, 2048, 8192):
+            x = synth.activations(m, k, seed=m, outlier_fraction=0.01).to(dev)
+            fn = lambda: mx.mixfp4_linear(x, packed)
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize(dev)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(6):
+                fn()
+            b.record()
+            torch.cuda.synchronize(dev)
+            t = a.elapsed_time(b) / 6 * 1e-3
+            tf = 2.0 * m * n * k / t / 1e12
+            out["%s_%dx%d_m%d" % (name, n, k, m)] = {"tflops": round(tf, 1), "frac_bf16_peak": round(tf / peak_tf, 3)}
+        del w, packed
+    out["gemm_status"] = mx.gemm_status(dev)
+    return out
 
 
 def secondary_numbers(dev) -> dict:
@@ -360,8 +645,9 @@ def secondary_numbers(dev) -> dict:
         x = torch.randn((m, k), device=dev).to(torch.bfloat16)
 
         def gemv_pass():
-            for p in packs:
-                mx.mixfp4_linear(x, p, overlap_previous=True)
+            for _ in range(4):           # 16 launches per replay: the replay's own launch cost stays small
+                for p in packs:
+                    mx.mixfp4_linear(x, p, overlap_previous=True)
 
         # as a CUDA graph of dependent launches, like the headline (a Python call per launch costs
         # more than the kernel)
@@ -374,7 +660,7 @@ def secondary_numbers(dev) -> dict:
             with torch.cuda.graph(g, stream=side):
                 gemv_pass()
         torch.cuda.synchronize(dev)
-        t = timeit(g.replay, 10) / len(packs)
+        t = timeit(g.replay, 10) / (4 * len(packs))
         out["gemv_gbs_m%d_14336x4096" % m] = round(algorithmic_bytes(n, k, m) / t / 1e9, 1)
 
     peak_tf = None

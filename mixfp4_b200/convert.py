@@ -83,13 +83,13 @@ def quantize_model_weights(model: nn.Module, weight_mode: str = "oracle16", *, r
                                          activation_mode=activation_mode)
         layer.weight_mode = weight_mode
         _set_submodule(model, name, layer)
-        scales = layer.scales[:, : (layer.in_features + 15) // 16]
+        packed = layer.packed
         rows.append({
             "module_name": name, "module_type": module_type(name), "layer_idx": layer_index(name),
             "out_features": layer.out_features, "in_features": layer.in_features, "transform": chosen or "identity",
             "format_granularity": weight_mode,
-            "e0_ratio": float((scales >= 128).float().mean().item()),     # kernel layout: bit 7 of the scale byte
-            "packed_bytes": layer.codes.numel() + layer.scales.numel() + layer.codes.shape[0] * (layer.codes.shape[1] // 64),
+            "e0_ratio": float(packed.format_ids().float().mean().item()),
+            "packed_bytes": packed.nbytes(),
         })
     return rows
 

@@ -67,6 +67,17 @@ def quantize_shard(w_shard: torch.Tensor, group=None, **kwargs):
     return quantize_packed(x2, amax=amax, **kwargs)[0]
 
 
+def row_parallel_fused_ok(m: int, k_total: int, n: int, world: int, slot_floats: int,
+                          multiple: int = K_SHARD_MULTIPLE) -> bool:
+    """Whether a row-parallel layer [n, k_total] split over `world` ranks runs the fused GEMV +
+    all-reduce for m rows of x.  Decided from global quantities only -- the LARGEST K shard any
+    rank holds under shard_bounds -- so every rank takes the same branch even when the shards are
+    unequal.  Host arithmetic (no GPU needed)."""
+    from . import _native as nat
+    largest = max(b - a for a, b in (shard_bounds(k_total, world, r, multiple) for r in range(world)))
+    return 1 <= m <= 8 and m * n <= slot_floats and bool(nat.lib().mixfp4_gemv_x_fits(m, largest, 1))
+
+
 class ColumnParallelMixFP4Linear(torch.nn.Module):
     """y_shard = x @ W[n0:n1]^T; the output stays sharded along N."""
 
@@ -120,13 +131,9 @@ class PeerCommunicator:
             self._nat.lib().mixfp4_comm_destroy(self.handle)
             self.handle = None
 
-    def fused_ok(self, m: int, k_total: int, n: int, multiple: int = 128) -> bool:
-        """Whether a row-parallel layer of this shape runs the fused kernel.  Decided from global
-        quantities only (the largest K shard any rank holds), so every rank takes the same branch."""
-        blocks = -(-k_total // multiple)
-        largest = -(-blocks // self.world) * multiple
-        return (1 <= m <= 8 and m * n <= self.slot_floats
-                and bool(self._nat.lib().mixfp4_gemv_x_fits(m, min(largest, k_total), 1)))
+    def fused_ok(self, m: int, k_total: int, n: int, multiple: int = K_SHARD_MULTIPLE) -> bool:
+        """row_parallel_fused_ok for this communicator's world size and buffer."""
+        return row_parallel_fused_ok(m, k_total, n, self.world, self.slot_floats, multiple)
 
     def linear(self, x_shard: torch.Tensor, packed_shard, *, out_dtype: torch.dtype | None = None,
                overlap_previous: bool = False) -> torch.Tensor | None:

@@ -26,6 +26,29 @@ def test_shard_bounds_cover_and_align():
         parallel.shard_bounds(10, 2, 2)
 
 
+def test_row_parallel_branch_is_decided_from_global_quantities():
+    # the fused GEMV + all-reduce keeps x in shared memory; whether it fits is asked for the largest K
+    # shard, so ranks with unequal shards agree (m = 8, K = 20 blocks of 128 over 3 ranks: shards of
+    # 896, 896 and 768 columns)
+    k = 20 * 128
+    shards = [b - a for a, b in (parallel.shard_bounds(k, 3, r, 128) for r in range(3))]
+    assert shards == [896, 896, 768]
+    for m in (1, 8):
+        assert parallel.row_parallel_fused_ok(m, k, 4096, 3, 8 * 4096)
+    assert not parallel.row_parallel_fused_ok(9, k, 4096, 3, 16 * 4096)          # more than 8 rows
+    assert not parallel.row_parallel_fused_ok(8, k, 4096, 3, 4096)               # receive buffer too small
+    # near the shared-memory limit the answer follows the largest shard, never this rank's own
+    big = 8 * 14336
+    fits_whole = parallel.row_parallel_fused_ok(8, big, 4096, 8, 8 * 4096)       # shards of 14336: too large
+    assert not fits_whole
+    assert parallel.row_parallel_fused_ok(8, 8 * 4096, 4096, 8, 8 * 4096)        # shards of 4096 fit
+    # 113 blocks over 2 ranks: 57 and 56 blocks -- both ranks answer for 57
+    from mixfp4_b200 import _native as nat
+    k2 = 113 * 128
+    want = bool(nat.lib().mixfp4_gemv_x_fits(8, 57 * 128, 1))
+    assert parallel.row_parallel_fused_ok(8, k2, 1024, 2, 8 * 1024) == want
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
