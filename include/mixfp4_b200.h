@@ -155,6 +155,19 @@ MIXFP4_API int mixfp4_selftest_division(unsigned long long* mismatches, void* st
  * x, y: device f32 [n]; e0m3: 0 = E2M1, 1 = E0M3. */
 MIXFP4_API int mixfp4_round_codebook(const float* x, float* y, int64_t n, int e0m3, void* stream);
 
+/* The E0M3 candidate of every K16 block under the reference's scale_rule "four_over_six"
+ * (project_quant/scale.py:64-103 _four_over_six_scale_candidate with qmax 7 and :207-225: the base
+ * and the 1.5x expanded E4M3 scale, the expanded one kept where its squared error is strictly
+ * smaller).  Bit-exact with the reference's CPU arithmetic.  The E2M1 side of that rule lives in an
+ * upstream package the reference does not vendor and is not provided.
+ *   grouped        device f32 [nblocks, 16]: the tensor up-cast, zero-padded and grouped
+ *   amax           device float: max |x| of the whole tensor (mixfp4_amax)
+ *   codes, dequant f32 [nblocks, 16]: level values with sign, dequantized values
+ *   scales, errors f32 [nblocks];  expansion_ids u8 [nblocks] (1 = the expanded scale was kept) */
+MIXFP4_API int mixfp4_e0_four_over_six(const float* grouped, int64_t nblocks, const float* amax,
+                            float* codes, float* dequant, float* scales, float* errors,
+                            uint8_t* expansion_ids, void* stream);
+
 /* Packed -> dense weight in out_dtype (the tensor the reference stores back into
  * nn.Linear.weight, project_quant/modeling.py:629). */
 MIXFP4_API int mixfp4_dequant(const uint8_t* codes, const uint8_t* scales, const uint8_t* fmt,

@@ -7,13 +7,13 @@ include/mixfp4_b200.h; importing the package does not need a GPU, calling it doe
 """
 
 from .quant import (E0M3_LEVELS, E2M1_LEVELS, SCALE_GROUP_SIZE, CandidateBlocks, GranularityResult, PackedWeight,
-                    build_candidates, dequantize, fake_quantize_activations, quantize_e0m3, quantize_e2m1, packed_nbytes, quant_mixfp4_granularity, quantize_packed, tensor_amax)
+                    ScaledCandidate, build_candidates, build_scaled_candidate, dequantize, fake_quantize_activations, quantize_e0m3, quantize_e2m1, packed_nbytes, quant_mixfp4_granularity, quantize_packed, tensor_amax)
 from .rotation import TRANSFORM_BANK, TransformSpec, apply_transform, get_transform
 from .linear import MixFP4Linear, decode_status, gemm_status, mixfp4_linear, mixfp4_linear_grouped
 from .convert import load_packed, named_linears, quantize_model_weights, save_packed
 
 __all__ = [
-    "E0M3_LEVELS", "E2M1_LEVELS", "SCALE_GROUP_SIZE", "CandidateBlocks", "GranularityResult", "build_candidates",
+    "E0M3_LEVELS", "E2M1_LEVELS", "SCALE_GROUP_SIZE", "CandidateBlocks", "GranularityResult", "ScaledCandidate", "build_candidates", "build_scaled_candidate",
     "quantize_e0m3", "quantize_e2m1", "PackedWeight", "dequantize",
     "fake_quantize_activations", "packed_nbytes", "quant_mixfp4_granularity", "quantize_packed", "tensor_amax", "TRANSFORM_BANK",
     "TransformSpec", "apply_transform", "get_transform", "MixFP4Linear", "decode_status", "gemm_status", "mixfp4_linear", "mixfp4_linear_grouped",

@@ -239,6 +239,64 @@ __global__ void __launch_bounds__(kThreads) round_codebook_kernel(const float* _
     }
 }
 
+// The E0M3 candidate under the reference's scale_rule "four_over_six" (project_quant/scale.py:64-103
+// _four_over_six_scale_candidate with qmax 7, :207-225 the choice between the x1.0 and the x1.5
+// scale).  One thread per block; every fp32 operation in the reference's order, IEEE, no contraction.
+__device__ __forceinline__ float e0_four_over_six_block(const float (&x)[kGroup], float amax, float expansion,
+                                                        float (&codes)[kGroup], float (&deq)[kGroup], float& scale_out) {
+    const float denominator = 1536.0f;
+    float bmax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kGroup; ++i) bmax = fmaxf(bmax, fabsf(x[i]));
+    float ideal = 0.0f;
+    if (amax != 0.0f) ideal = __fmul_rn(__fdiv_rn(bmax, 7.0f), __fdiv_rn(denominator, amax));
+    ideal = __fmul_rn(ideal, expansion);
+    const float scale = e4m3_to_float(__nv_cvt_float_to_fp8(ideal, __NV_SATFINITE, __NV_E4M3));   // no clamp: may be 0
+    const float decode_scale = amax > 0.0f ? __fdiv_rn(1.0f, __fdiv_rn(denominator, amax)) : 0.0f;
+    const float recip = scale != 0.0f ? __fdiv_rn(1.0f, __fmul_rn(decode_scale, scale)) : 0.0f;
+    float sq[kGroup];
+#pragma unroll
+    for (int i = 0; i < kGroup; ++i) {
+        const float n = scale != 0.0f ? __fmul_rn(x[i], recip) : 0.0f;
+        const float level = e0m3_round(fabsf(n));
+        const float code = n < 0.0f ? -level : (n > 0.0f ? level : 0.0f);
+        codes[i] = code;
+        const float d = __fdiv_rn(__fmul_rn(__fmul_rn(code, scale), amax), denominator);
+        deq[i] = d;
+        const float e = __fsub_rn(d, x[i]);
+        sq[i] = __fmul_rn(e, e);
+    }
+    float acc = __fadd_rn(sq[0], sq[8]);
+#pragma unroll
+    for (int j = 1; j < 8; ++j) acc = __fadd_rn(acc, __fadd_rn(sq[j], sq[j + 8]));
+    scale_out = scale;
+    return acc;
+}
+
+__global__ void __launch_bounds__(128) e0_four_over_six_kernel(const float* __restrict__ x, int64_t nblocks,
+                                                               const float* __restrict__ amax_ptr,
+                                                               float* __restrict__ codes, float* __restrict__ dequant,
+                                                               float* __restrict__ scales, float* __restrict__ errors,
+                                                               uint8_t* __restrict__ expanded) {
+    const int64_t b = (int64_t)blockIdx.x * 128 + threadIdx.x;
+    if (b >= nblocks) return;
+    const float amax = *amax_ptr;
+    float v[kGroup], c0[kGroup], d0[kGroup], c1[kGroup], d1[kGroup], s0, s1;
+#pragma unroll
+    for (int i = 0; i < kGroup; ++i) v[i] = x[b * kGroup + i];
+    const float e0 = e0_four_over_six_block(v, amax, 1.0f, c0, d0, s0);
+    const float e1 = e0_four_over_six_block(v, amax, 1.5f, c1, d1, s1);
+    const bool pick = e1 < e0;
+#pragma unroll
+    for (int i = 0; i < kGroup; ++i) {
+        codes[b * kGroup + i] = pick ? c1[i] : c0[i];
+        dequant[b * kGroup + i] = pick ? d1[i] : d0[i];
+    }
+    scales[b] = pick ? s1 : s0;
+    errors[b] = pick ? e1 : e0;
+    expanded[b] = pick ? 1 : 0;
+}
+
 // Exhaustive check of div_rcp against IEEE division: all 2^23 significands of the dividend
 // for each of the 8 significands a divisor can have (E4M3 scales; 6 = 1.5 * 4, 7 = 1.75 * 4).
 __global__ void selftest_division_kernel(unsigned long long* mismatches) {
@@ -749,6 +807,16 @@ extern "C" int mixfp4_dequant(const uint8_t* codes, const uint8_t* scales, const
 #undef MIXFP4_LAUNCH_DEQUANT
 #undef MIXFP4_LAUNCH_DEQUANT_L
     return check_launch("dequant_kernel");
+}
+
+extern "C" int mixfp4_e0_four_over_six(const float* grouped, int64_t nblocks, const float* amax, float* codes,
+                                       float* dequant, float* scales, float* errors, uint8_t* expansion_ids,
+                                       void* stream) {
+    if (!grouped || !amax || !codes || !dequant || !scales || !errors || !expansion_ids) return MIXFP4_E_NULL;
+    if (nblocks <= 0 || nblocks > (0x7fffffffLL - 1) * 128) return MIXFP4_E_SHAPE;
+    e0_four_over_six_kernel<<<(unsigned)((nblocks + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        grouped, nblocks, amax, codes, dequant, scales, errors, expansion_ids);
+    return check_launch("e0_four_over_six_kernel");
 }
 
 extern "C" int mixfp4_round_codebook(const float* x, float* y, int64_t n, int e0m3, void* stream) {

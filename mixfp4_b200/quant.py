@@ -442,6 +442,67 @@ def build_candidates(x: torch.Tensor, *, scale_group_size: int = SCALE_GROUP_SIZ
         global_scale=mv(e2p.global_scale.reshape(())), scale_rule=scale_rule)
 
 
+@dataclass
+class ScaledCandidate:
+    """One independently scaled datatype candidate per K16 block (project_quant/scale.py:19-25)."""
+
+    codes: torch.Tensor          # float32 [..., 16] level values with sign
+    dequant: torch.Tensor        # float32 [..., 16]
+    scales: torch.Tensor         # float32 [...]
+    errors: torch.Tensor         # float32 [...]
+    expansion_ids: torch.Tensor  # uint8 [...]: 1 where the expanded (x1.5) scale was kept
+
+
+@torch.no_grad()
+def build_scaled_candidate(grouped: torch.Tensor, *, format_name: str, global_scale: torch.Tensor | None = None,
+                           scale_rule: str = "standard") -> ScaledCandidate:
+    """The reference's ``build_scaled_candidate`` (project_quant/scale.py:165-225) for a grouped float32
+    tensor [..., 16]: one candidate (``format_name`` "e2m1" or "e0m3") per block.
+
+    scale_rule "standard": the candidate the quantizer builds (scale.py:43-61); ``global_scale`` is
+    recomputed from the tensor as the reference's callers do.  scale_rule "four_over_six": the E0M3
+    candidate with the base or the 1.5x expanded scale, whichever has the smaller error
+    (scale.py:64-103, 207-225).  Its E2M1 counterpart is delegated by the reference to the FourOverSix
+    package, which its tree does not contain: NotImplementedError."""
+    if format_name not in ("e2m1", "e0m3"):
+        raise ValueError(f"unknown format {format_name!r}")
+    if scale_rule not in ("standard", "four_over_six"):
+        raise ValueError(f"unknown scale_rule={scale_rule!r}")
+    if grouped.shape[-1] != SCALE_GROUP_SIZE:
+        raise ValueError("grouped must have 16 elements along its last axis")
+    host_input = not grouped.is_cuda
+    g = grouped.detach().to(torch.float32)
+    g = (g.cuda() if host_input else g).contiguous()
+    lead = g.shape[:-1]
+    mv = (lambda t: t.to(grouped.device)) if host_input else (lambda t: t)
+    if scale_rule == "standard":
+        flat = g.reshape(-1, SCALE_GROUP_SIZE) if g.ndim < 3 else g.reshape(-1, g.shape[-2] * SCALE_GROUP_SIZE)
+        mode = "all_e2m1" if format_name == "e2m1" else "all_e0m3"
+        packed, dq, stats = quantize_packed(flat, mode=mode, want_dequant=True, want_stats=True)
+        groups = flat.shape[1] // SCALE_GROUP_SIZE
+        levels = E2M1_LEVELS if format_name == "e2m1" else E0M3_LEVELS
+        key = "e2" if format_name == "e2m1" else "e0"
+        return ScaledCandidate(mv(_level_values(packed.codes, groups, levels).reshape(g.shape)), mv(dq.reshape(g.shape)),
+                               mv(stats[key + "_scales"].reshape(lead)), mv(stats[key + "_errors"].reshape(lead)),
+                               mv(torch.zeros(lead, dtype=torch.uint8, device=g.device)))
+    if format_name == "e2m1":
+        raise NotImplementedError("scale_rule='four_over_six' delegates its E2M1 candidate to the FourOverSix package, "
+                                  "which the reference tree does not contain")
+    nblocks = g.numel() // SCALE_GROUP_SIZE
+    codes, deq = torch.empty_like(g), torch.empty_like(g)
+    scales = torch.empty(lead, dtype=torch.float32, device=g.device)
+    errors = torch.empty(lead, dtype=torch.float32, device=g.device)
+    exp = torch.empty(lead, dtype=torch.uint8, device=g.device)
+    if nblocks:
+        amax = tensor_amax(g.reshape(-1, SCALE_GROUP_SIZE))
+        with torch.cuda.device(g.device):
+            st = nat.lib().mixfp4_e0_four_over_six(g.data_ptr(), nblocks, amax.data_ptr(), codes.data_ptr(), deq.data_ptr(),
+                                                   scales.data_ptr(), errors.data_ptr(), exp.data_ptr(),
+                                                   nat.stream_ptr(g.device))
+        nat.check("mixfp4_e0_four_over_six", st)
+    return ScaledCandidate(mv(codes), mv(deq), mv(scales), mv(errors), mv(exp))
+
+
 HIGH_PRECISION_MODES = ("high_precision", "fp16", "bf16")
 
 

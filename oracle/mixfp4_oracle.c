@@ -21,6 +21,7 @@
  *   project_quant/core.py:115-143        oracle16 choice (e0 < e2, ties keep E2M1), select, un-pad, cast
  *   project_quant/rotation.py:47-75      fwht / apply_transform
  *   project_quant/region.py:42-86, selector.py:28-33   coarse format regions (mse selector)
+ *   project_quant/scale.py:64-103, 207-225   the E0M3 candidate under scale_rule "four_over_six"
  *
  * All arithmetic is IEEE binary32, round-to-nearest-even, with NO fused
  * multiply-add (compile with -ffp-contract=off, no -ffast-math).
@@ -352,6 +353,67 @@ int mixfp4_oracle_round_codebook(const float* x, float* y, int64_t n, int e0m3) 
         const float q = e0m3 ? (float)e0m3_index(mag) : kE2M1Levels[e2m1_index(mag)];
         const float sign = v > 0.0f ? 1.0f : (v < 0.0f ? -1.0f : 0.0f);
         y[i] = sign * q;
+    }
+    return 0;
+}
+
+/* scale.py:64-103 _four_over_six_scale_candidate for the E0M3 codebook (qmax 7), one expansion
+ * factor: every operation in the reference's order (the encode scale 1536 / amax, the reciprocal
+ * of decode_scale * scale, the left-to-right dequantization).  No clamp before the E4M3 cast:
+ * tiny ideals round to a zero scale, which zeroes the block. */
+static float e0_four_over_six_block(const float* x, float amax, float expansion, float* codes, float* dequant,
+                                    float* scale_out) {
+    const float denominator = 1536.0f;
+    float bmax = 0.0f;
+    for (int i = 0; i < MIXFP4_GROUP; ++i) { float a = fabsf(x[i]); if (a > bmax) bmax = a; }
+    float ideal = 0.0f;
+    if (amax != 0.0f) {
+        const float encode_scale = denominator / amax;
+        ideal = bmax / 7.0f * encode_scale;
+    }
+    ideal = ideal * expansion;
+    float scale = 0.0f;
+    if (ideal > 0.0f) (void)e4m3_round(ideal, &scale);
+    const float decode_scale = amax > 0.0f ? 1.0f / (denominator / amax) : 0.0f;
+    float sq[MIXFP4_GROUP];
+    for (int i = 0; i < MIXFP4_GROUP; ++i) {
+        float n = 0.0f;
+        if (scale != 0.0f) n = x[i] * (1.0f / (decode_scale * scale));
+        const float level = (float)e0m3_index(fabsf(n));
+        const float sign = n > 0.0f ? 1.0f : (n < 0.0f ? -1.0f : 0.0f);
+        const float code = sign * level;
+        codes[i] = code;
+        float d = code * scale;
+        d = d * amax;
+        d = d / denominator;
+        dequant[i] = d;
+        const float e = d - x[i];
+        sq[i] = e * e;
+    }
+    float acc = sq[0] + sq[8];
+    for (int j = 1; j < 8; ++j) acc = acc + (sq[j] + sq[j + 8]);
+    *scale_out = scale;
+    return acc;
+}
+
+/* scale.py:207-225: the base (x1.0) and the expanded (x1.5) E0M3 candidate of every block, the
+ * expanded one kept where its error is strictly smaller.  x: nblocks * 16 floats (the padded,
+ * grouped tensor); amax is taken over all of it. */
+int mixfp4_oracle_e0_four_over_six(const float* x, int64_t nblocks, float* codes, float* dequant, float* scales,
+                                   float* errors, uint8_t* expanded) {
+    if (!x || !codes || !dequant || !scales || !errors || !expanded || nblocks < 0) return -1;
+    float amax = 0.0f;
+    for (int64_t i = 0; i < nblocks * MIXFP4_GROUP; ++i) { float a = fabsf(x[i]); if (a > amax) amax = a; }
+    for (int64_t b = 0; b < nblocks; ++b) {
+        float c0[MIXFP4_GROUP], d0[MIXFP4_GROUP], c1[MIXFP4_GROUP], d1[MIXFP4_GROUP], s0, s1;
+        const float e0 = e0_four_over_six_block(x + b * MIXFP4_GROUP, amax, 1.0f, c0, d0, &s0);
+        const float e1 = e0_four_over_six_block(x + b * MIXFP4_GROUP, amax, 1.5f, c1, d1, &s1);
+        const int pick = e1 < e0;
+        memcpy(codes + b * MIXFP4_GROUP, pick ? c1 : c0, sizeof(c0));
+        memcpy(dequant + b * MIXFP4_GROUP, pick ? d1 : d0, sizeof(d0));
+        scales[b] = pick ? s1 : s0;
+        errors[b] = pick ? e1 : e0;
+        expanded[b] = (uint8_t)pick;
     }
     return 0;
 }

@@ -10,6 +10,7 @@ CPU path on small seeded tensors and writes
     tests/golden/quant_cases.npz      inputs + per-block results of the quantizer
     tests/golden/rotation_cases.npz   inputs + outputs of the block-Hadamard bank
     tests/golden/digests.json         SHA-256 of the packed bytes for full-size tensors
+    tests/golden/four_over_six_e0_cases.npz  the E0M3 candidate under scale_rule "four_over_six"
     tests/golden/candidate_cases.npz  build_candidates fields (both candidates' dequantized values)
                                       and the two codebook quantizers on a dense probe
 
@@ -252,6 +253,37 @@ def candidate_case_list(pq) -> dict:
     return out
 
 
+def four_over_six_case_list(pq) -> dict:
+    """The E0M3 candidate under scale_rule "four_over_six" (project_quant/scale.py:64-103, 207-225; the
+    E2M1 side needs an upstream that is absent).  Inputs: seeded tensors of the reference's tests, a
+    wide dynamic range, an all-zero tensor, and the crafted boundary tensor of
+    tests/test_quant_core.py:216-226."""
+    from project_quant.scale import build_scaled_candidate, compute_global_scale
+    s = synth.seeded
+    g = torch.Generator().manual_seed(78)
+    wide = torch.randn((24, 256), generator=g) * torch.exp2(torch.randint(-30, 4, (24, 256), generator=g).float())
+    boundary = torch.zeros((128, 64), dtype=torch.bfloat16)
+    boundary[0, 0] = 5.625
+    boundary[1, :16] = torch.tensor([1.2891, -0.9062, 0.4258, -0.3438, 1.3984, -1.8125, 2.7500, 1.7969,
+                                     -0.7227, -2.0625, -0.3262, -2.3438, -0.4883, -0.6875, 0.2168, -1.0547],
+                                    dtype=torch.bfloat16)
+    cases = {"s18_16x128_bf16": s((16, 128), 18, torch.bfloat16), "s3_17x80": s((17, 80), 3), "wide_24x256": wide,
+             "zeros_4x32": torch.zeros((4, 32)), "boundary_128x64_bf16": boundary,
+             "student_t_48x384_bf16": synth.student_t_weight(48, 384, 1)}
+    out = {}
+    for name, x in cases.items():
+        grouped = x.float().reshape(x.shape[0], -1, 16)
+        cand = build_scaled_candidate(grouped, format_name="e0m3", global_scale=compute_global_scale(grouped, "four_over_six"),
+                                      scale_rule="four_over_six")
+        out[f"{name}__grouped"] = grouped.numpy().copy()
+        out[f"{name}__codes"] = cand.codes.numpy().copy()
+        out[f"{name}__dequant"] = cand.dequant.numpy().copy()
+        out[f"{name}__scales"] = cand.scales.numpy().copy()
+        out[f"{name}__errors"] = cand.errors.numpy().copy()
+        out[f"{name}__expansion_ids"] = cand.expansion_ids.numpy().copy()
+    return out
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of a checkout of the reference project")
@@ -263,6 +295,7 @@ def main() -> None:
     from project_quant import rotation as rot
 
     np.savez_compressed(os.path.join(HERE, "candidate_cases.npz"), **candidate_case_list(pq))
+    np.savez_compressed(os.path.join(HERE, "four_over_six_e0_cases.npz"), **four_over_six_case_list(pq))
     if args.only_candidates:
         return
 

@@ -52,6 +52,17 @@ def candidate_cases() -> dict:
     return out
 
 
+def four_over_six_e0_cases() -> dict:
+    """name -> {grouped, codes, dequant, scales, errors, expansion_ids} of the E0M3 candidate under the
+    reference's scale_rule "four_over_six"."""
+    z = np.load(os.path.join(GOLDEN, "four_over_six_e0_cases.npz"))
+    out: dict = {}
+    for key in z.files:
+        name, field = key.split("__", 1)
+        out.setdefault(name, {})[field] = z[key]
+    return out
+
+
 def rotation_cases() -> dict:
     z = np.load(os.path.join(GOLDEN, "rotation_cases.npz"))
     return {k: z[k] for k in z.files}

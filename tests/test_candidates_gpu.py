@@ -99,3 +99,37 @@ def test_codebook_quantizers_match_reference_probe():
     assert mx.quantize_e0m3(h).shape == h.shape and mx.quantize_e0m3(h).dtype == torch.bfloat16
     want = oracle.round_codebook(h.float().cpu().numpy(), False)
     assert np.array_equal(f32_bits(mx.quantize_e2m1(h).float()), want.view(np.uint32))
+
+
+def test_e0_four_over_six_candidate_matches_reference_and_oracle():
+    from tests.golden_io import four_over_six_e0_cases
+    for name, d in four_over_six_e0_cases().items():
+        g = torch.from_numpy(d["grouped"].copy())
+        for tensor in (g.cuda(), g):
+            c = mx.build_scaled_candidate(tensor, format_name="e0m3", scale_rule="four_over_six")
+            assert c.codes.device == tensor.device and c.codes.shape == g.shape and c.scales.shape == g.shape[:-1]
+            for key in ("codes", "dequant", "scales", "errors"):
+                assert np.array_equal(f32_bits(getattr(c, key)), d[key].view(np.uint32)), (name, key)
+            assert np.array_equal(c.expansion_ids.cpu().numpy(), d["expansion_ids"]), name
+    # a larger tensor against the oracle
+    w = synth.student_t_weight(512, 2048, 9).float().reshape(512, -1, 16)
+    c = mx.build_scaled_candidate(w.cuda(), format_name="e0m3", scale_rule="four_over_six")
+    want = oracle.e0_four_over_six(w.numpy())
+    for key in ("codes", "dequant", "scales", "errors"):
+        assert np.array_equal(f32_bits(getattr(c, key)), want[key].view(np.uint32)), key
+    assert np.array_equal(c.expansion_ids.cpu().numpy(), want["expansion_ids"]) and int(want["expansion_ids"].sum()) > 0
+    with pytest.raises(NotImplementedError):
+        mx.build_scaled_candidate(w.cuda(), format_name="e2m1", scale_rule="four_over_six")
+    with pytest.raises(ValueError, match="unknown scale_rule"):
+        mx.build_scaled_candidate(w.cuda(), format_name="e0m3", scale_rule="other")
+
+
+def test_standard_scaled_candidate_matches_build_candidates():
+    case = CASES["t_19x131_s10"]
+    x = case_tensor(case).cuda()
+    cand = mx.build_candidates(x)
+    for fmt, key in (("e2m1", "e2"), ("e0m3", "e0")):
+        c = mx.build_scaled_candidate(cand.grouped_original, format_name=fmt, scale_rule="standard")
+        assert torch.equal(c.codes, getattr(cand, key + "_codes")) and torch.equal(c.dequant, getattr(cand, key + "_dequant"))
+        assert torch.equal(c.scales, getattr(cand, key + "_scales")) and torch.equal(c.errors, getattr(cand, key + "_errors"))
+        assert not bool(c.expansion_ids.any())

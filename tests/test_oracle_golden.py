@@ -155,3 +155,17 @@ def test_both_candidates_dequantized_values_match_reference():
         for mode, key in (("all_e2m1", "e2_dequant"), ("all_e0m3", "e0_dequant")):
             got = oracle.dequant(oracle.quantize(xp, mode), "f32")
             assert np.array_equal(got.reshape(rows, groups, 16).view(np.uint32), d[key].view(np.uint32)), (name, key)
+
+
+def test_e0_four_over_six_candidate_matches_reference():
+    # scale_rule "four_over_six", E0M3 side (project_quant/scale.py:64-103, 207-225), incl. the crafted
+    # boundary tensor of the reference's tests and blocks whose unclamped scale rounds to zero
+    from tests.golden_io import four_over_six_e0_cases
+    picked = 0
+    for name, d in four_over_six_e0_cases().items():
+        got = oracle.e0_four_over_six(d["grouped"])
+        for key in ("codes", "dequant", "scales", "errors"):
+            assert np.array_equal(got[key].view(np.uint32), d[key].view(np.uint32)), (name, key)
+        assert np.array_equal(got["expansion_ids"], d["expansion_ids"]), name
+        picked += int(d["expansion_ids"].sum())
+    assert picked > 0            # the expanded scale wins somewhere in the fixtures
