@@ -192,12 +192,14 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
     if (lane == 0) {
 #pragma unroll
         for (int d = 0; d < kDepth; ++d) mbar_init(bars + d * 8, 1);
-        if (warp == 0) mbar_init(bar_lut, 1);
+        if (warp == kWarps - 1) mbar_init(bar_lut, 1);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the copy engine sees initialised barriers
     }
     __syncwarp();
-    MIXFP4_STAMP(5);
-    if (bulk && threadIdx.x == 0) {
+    Cursor p = make_cursor(wa);
+    if (cnt > 0) { issue(p, 0); advance(p); }
+    MIXFP4_STAMP(4);
+    if (bulk && warp == kWarps - 1 && lane == 0) {
         mbar_expect_tx(bar_lut, (uint32_t)a.nseg * kLutBytesS);
         for (int sgm = 0; sgm < a.nseg; ++sgm) {
             const uint4* lut = sgm == 0 ? a.seg[0].lut : sgm == 1 ? a.seg[1].lut : a.seg[2].lut;
@@ -206,11 +208,6 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
     }
     if (cnt == 0)                        // a warp without chunks adds zeros where the tile sums are collected
         for (int v = lane; v < kRowsPerCta * m; v += 32) pieces[(size_t)(warp * 2 * kRowsPerCta) * m + v] = 0.0f;
-    MIXFP4_STAMP(6);
-    Cursor p = make_cursor(wa);
-    MIXFP4_STAMP(7);
-    if (cnt > 0) { issue(p, 0); advance(p); }
-    MIXFP4_STAMP(4);
 
     // Without the wide table: entries go through registers, loaded here and stored after the x copies
     // have been issued, so the two latencies overlap.  (entry, copy) pairs: a warp writes 512 contiguous bytes.
@@ -236,18 +233,19 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
     if constexpr (kAR) seq = *reinterpret_cast<volatile uint32_t*>(a.ar.words);
     {   // the whole x (m rows, zero-filled to kpad) once per CTA
         const uint32_t chunks_per_row = (uint32_t)(a.kpad >> 3), k_lim = (uint32_t)a.k;
-        for (uint32_t i = threadIdx.x; i < (uint32_t)m * chunks_per_row; i += kThreadsS) {
-            const uint32_t r = i / chunks_per_row, c = i - r * chunks_per_row;
-            const uint32_t dst = x_base + r * xres_rs + c * 16;
-            const __nv_bfloat16* src = a.x + (size_t)r * a.ldx + c * 8;
-            if (a.x_vec) {
-                const bool in = c * 8 < k_lim;
-                cp_async16(dst, in ? static_cast<const void*>(src) : static_cast<const void*>(a.x), in ? 16u : 0u);
-            } else {
-                uint32_t e[8];
+        for (int r = 0; r < m; ++r) {
+            for (uint32_t c = threadIdx.x; c < chunks_per_row; c += kThreadsS) {
+                const uint32_t dst = x_base + (uint32_t)r * xres_rs + c * 16;
+                const __nv_bfloat16* src = a.x + (size_t)r * a.ldx + c * 8;
+                if (a.x_vec) {
+                    const bool in = c * 8 < k_lim;
+                    cp_async16(dst, in ? static_cast<const void*>(src) : static_cast<const void*>(a.x), in ? 16u : 0u);
+                } else {
+                    uint32_t e[8];
 #pragma unroll
-                for (int q = 0; q < 8; ++q) e[q] = c * 8 + q < k_lim ? __bfloat16_as_ushort(src[q]) : 0u;
-                sts128(dst, make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16)));
+                    for (int q = 0; q < 8; ++q) e[q] = c * 8 + q < k_lim ? __bfloat16_as_ushort(src[q]) : 0u;
+                    sts128(dst, make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16)));
+                }
             }
         }
     }
@@ -270,7 +268,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
         }
     }
     cp_async_wait<0>();
-    __syncthreads();                     // x and the stored tables; also: warp 0 has initialised the table barrier
+    __syncthreads();                     // x and the stored tables; also: the table barrier is initialised
     if (bulk && !wait_chunk(bar_lut, 0, a.wait_ns) && a.status) atomicCAS(a.status, 0, 299);
     MIXFP4_STAMP(2);
 
@@ -314,6 +312,10 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
     Cursor c = make_cursor(wa);
     int issued = cnt < kDepth ? cnt : kDepth, done = 0;
     bool head = true;                    // the sums in the accumulators include this run's first chunk
+    int comb_n = 0, comb_seg = 0;        // after the barrier: pieces to add to the first (0: nothing to add up)
+    uint32_t comb_row0 = 0;
+    const float* comb_first = pieces;
+    const float* comb_next = pieces;
     bool ok = true;                      // false after a chunk did not arrive within the wait limit
     uint32_t use = ring, use_bar = bars, phase = 0;          // ring slot of the chunk consumed next
     while (done < cnt) {
@@ -379,6 +381,24 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
 #pragma unroll
             for (int q = 0; q < 4; ++q) acc[nt][0][q] = acc[nt][1][q] = 0.0f;
         }
+        if (head) {
+            // Once, after this run's first piece and off the kernel's last steps: does this warp add up a
+            // row tile after the barrier (its run holds the end of a tile that started in an earlier
+            // run), and from where.
+            const int tl = wa / S, a_sub = wa - tl * S;
+            if (a_sub != 0 && (tl + 1) * S <= wb) {
+                const int lo = tl * S;
+                // the run that holds the tile's first chunk: the largest w with floor(nchunks * w / kWarps) <= lo
+                const int wf = (int)(((uint32_t)kWarps * (uint32_t)(lo + 1) - 1u) / (uint32_t)nchunks);
+                comb_n = warp - wf;
+                comb_seg = c.seg;
+                comb_row0 = row0;
+                // that run holds the tile as its tail piece unless it starts exactly at the tile; every run
+                // after it lies inside the tile (its head piece; zeros for a run without chunks)
+                comb_first = pieces + (size_t)((wf * 2 + (run_start(wf) < lo ? 1 : 0)) * kRowsPerCta) * m;
+                comb_next = pieces + (size_t)((wf + 1) * 2 * kRowsPerCta) * m;
+            }
+        }
         head = false;
         done += piece;
         // the next tile of the run (its first chunk is the tile's first)
@@ -399,28 +419,14 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
 
     // Row tiles cut by run boundaries: the warp whose run holds the end of such a tile adds the
     // partial sums of the runs before it (ascending K) and its own head piece.
-    if (cnt > 0) {
-        const int tl = wa / S, a_sub = wa - tl * S;
-        if (a_sub != 0 && (tl + 1) * S <= wb) {
-            const int lo = tl * S;
-            // the run that holds the tile's first chunk: the largest w with floor(nchunks * w / kWarps) <= lo
-            const int wf = (int)(((uint32_t)kWarps * (uint32_t)(lo + 1) - 1u) / (uint32_t)nchunks);
-            const int tile = t0 + tl;
-            const int cs = (tile >= a.seg[0].tile_end) + (tile >= a.seg[1].tile_end);
-            const uint32_t row0 = (uint32_t)(tile - seg_first(cs)) * kRowsPerCta;
-            // the first run holds the tile as its tail piece unless it starts exactly at the tile; every
-            // run after it lies inside the tile (its head piece; zeros for a run without chunks)
-            const float* first_piece = pieces + (size_t)((wf * 2 + (run_start(wf) < lo ? 1 : 0)) * kRowsPerCta) * m;
-            const int stride = 2 * kRowsPerCta * m;
-            MIXFP4_STAMP(2);
-            for (int v = lane; v < kRowsPerCta * m; v += 32) {
-                const int r = v % kRowsPerCta, b = v / kRowsPerCta;
-                float sum = first_piece[r * m + b];
-                const float* q = pieces + (size_t)(wf + 1) * stride + r * m + b;
-                for (int w2 = wf + 1; w2 <= warp; ++w2, q += stride) sum += *q;
-                MIXFP4_STAMP(0);
-                emit(cs, row0 + r, b, sum);
-            }
+    if (comb_n > 0) {
+        const int stride = 2 * kRowsPerCta * m;
+        for (int v = lane; v < kRowsPerCta * m; v += 32) {
+            const int r = v % kRowsPerCta, b = v / kRowsPerCta;
+            float sum = comb_first[r * m + b];
+            const float* q = comb_next + r * m + b;
+            for (int w2 = 0; w2 < comb_n; ++w2, q += stride) sum += *q;
+            emit(comb_seg, comb_row0 + r, b, sum);
         }
     }
 
