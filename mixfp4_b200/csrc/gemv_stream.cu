@@ -549,6 +549,10 @@ int dispatch_stream(const GemvStreamArgs& a, int sms, int flags, cudaStream_t st
             return rc;
         }
     }
+#ifdef MIXFP4_CFG_WARPS
+    rc = launch_stream<MIXFP4_CFG_WARPS, MIXFP4_CFG_DEPTH, kAR, 1, 8>(a, sms, flags, st);
+    if (rc != MIXFP4_E_SHAPE) return rc;
+#endif
     rc = launch_stream<24, 4, kAR, 1, 8>(a, sms, flags, st);
     if (rc == MIXFP4_E_SHAPE) rc = launch_stream<24, 3, kAR, 1, 8>(a, sms, flags, st);
     if (rc == MIXFP4_E_SHAPE) rc = launch_stream<24, 3, kAR, 1, 4>(a, sms, flags, st);
