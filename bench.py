@@ -45,10 +45,10 @@ METRIC = "mixed-FP4 linear: GEMV HBM GB/s @M=1 (Llama-3-8B decode linears)"
 UNIT = "GB/s"
 FALLBACK_HBM_GBS = 6650.0
 # DRAM traffic of one launch of the dominant kernel from an ncu capture of the gate/up layer
-# (14336 x 4096, M = 1): dram__bytes_read.sum + dram__bytes_write.sum = 33.06 MB against 33.52 MB
-# algorithmic (the kernel layout does not read the separate format array), i.e. 0.986 x the
+# (14336 x 4096, M = 1): dram__bytes_read.sum + dram__bytes_write.sum = 33.11 MB against 33.52 MB
+# algorithmic (the stream layout has no separate format array), i.e. 0.988 x the
 # algorithmic bytes; scaled here to the average launch of the step (traffic grows with N*K).
-TRAFFIC_OVER_ALGORITHMIC = 0.986
+TRAFFIC_OVER_ALGORITHMIC = 0.988
 TRAFFIC_BYTES_PER_LAUNCH = None   # set in run_ours once the step's bytes are known
 LAUNCHES_PER_LAYER = 4            # q/k/v grouped, o, gate/up grouped, down
 
