@@ -106,21 +106,6 @@ __host__ __device__ inline int64_t stream_bytes(int64_t rows, int64_t k) {
     return stream_tiles(rows) * (padded_k(k) / kChunkK) * kChunkBytes;
 }
 
-#ifdef MIXFP4_DECODE_FMA_SHIFTS
-// Variant: both shifts as integer multiplies (FMA pipe) instead of ALU-pipe shifts.
-__device__ __forceinline__ void decode8_kl_v(uint32_t w, const uint4& t, uint32_t (&p)[4]) {
-    const uint32_t mag = w & 0x77777777u;
-    const uint32_t mag_hi = __umulhi(mag, 0x10000u), w4 = w * 16u;
-    uint32_t lo_a = prmt(t.x, t.y, mag), hi_a = prmt(t.z, t.w, mag);
-    uint32_t lo_b = prmt(t.x, t.y, mag_hi), hi_b = prmt(t.z, t.w, mag_hi);
-    hi_a |= w & 0x80808080u;
-    hi_b |= w4 & 0x80808080u;
-    p[0] = prmt(lo_a, hi_a, 0x5140u);
-    p[1] = prmt(lo_a, hi_a, 0x7362u);
-    p[2] = prmt(lo_b, hi_b, 0x5140u);
-    p[3] = prmt(lo_b, hi_b, 0x7362u);
-}
-#endif
 
 template <bool kKernelLayout>
 __device__ __forceinline__ void decode_word(uint32_t w, const uint4& t, uint32_t (&p)[4]) {

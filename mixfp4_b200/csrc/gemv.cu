@@ -341,7 +341,6 @@ int launch(const GemvArgs& a, int flags, cudaStream_t st) {
 // group's warps as above and synchronise with a named barrier per group.
 // Up to kMaxSegments weights that share x (q/k/v, gate/up) run as one launch: their row tiles
 // are numbered through, every segment has its own table in shared memory.
-constexpr uint32_t kLut8Bytes = 256u * 16u * 8u;     // 32 KB
 constexpr int kMaxSegments = 3;
 
 struct GemvSegment {

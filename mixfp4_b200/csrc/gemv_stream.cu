@@ -29,10 +29,6 @@
 namespace mixfp4 {
 namespace {
 
-#ifdef MIXFP4_DECODE_FMA_SHIFTS
-#define decode8_kl decode8_kl_v
-#endif
-
 constexpr int kMaxSeg = 3;
 
 struct StreamSeg {
@@ -54,15 +50,7 @@ struct GemvStreamArgs {
     AllReduceArgs ar;                      // used by the all-reduce instantiation only
     int* status;                           // device word: nonzero after an expired wait
     uint64_t wait_ns;                      // limit of every wait on a chunk
-#ifdef MIXFP4_TRACE
-    unsigned long long* trace;             // [launch % 64][CTA][16] globaltimer stamps
-#endif
 };
-#ifdef MIXFP4_TRACE
-#define MIXFP4_STAMP(i) do { if (a.trace && lane == 0 && (warp == 0 || warp == kWarps - 1)) a.trace[(size_t)blockIdx.x * 16 + (i) + (warp ? 8 : 0)] = gemv_timer_ns(); } while (0)
-#else
-#define MIXFP4_STAMP(i) do { } while (0)
-#endif
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -108,9 +96,6 @@ __device__ __forceinline__ bool wait_chunk(uint32_t bar, uint32_t parity, uint64
 template <int kWarps, int kDepth, bool kAR, int kNT, int kLutRep>
 __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvStreamArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
-#ifdef MIXFP4_TRACE
-    const unsigned long long t_top = gemv_timer_ns();
-#endif
     constexpr int kThreadsS = kWarps * 32;
     constexpr uint32_t kLutBytesS = 256u * 16u * kLutRep;
     constexpr uint32_t kBarBytes = (kWarps * kDepth * 8 + 8 + 127) & ~127;      // the rings' barriers and the tables' one
@@ -179,10 +164,6 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
     // stall its issuer while the copy engine's queue is full, and nothing below should wait for that;
     // the main loop fills the ring.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    MIXFP4_STAMP(0);
-#ifdef MIXFP4_TRACE
-    if (a.trace && lane == 0 && (warp == 0 || warp == kWarps - 1)) a.trace[(size_t)blockIdx.x * 16 + 10 + (warp ? 1 : 0)] = t_top;
-#endif
     // Tables: with the eightfold table in global memory (mixfp4_decode_table_wide) one thread hands each
     // segment's 32 KB to the copy engine before anything else; otherwise every thread loads a few
     // entries and stores their copies.  x goes through cp.async by all threads either way: a bulk copy
@@ -198,7 +179,6 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
     __syncwarp();
     Cursor p = make_cursor(wa);
     if (cnt > 0) { issue(p, 0); advance(p); }
-    MIXFP4_STAMP(4);
     if (bulk && warp == kWarps - 1 && lane == 0) {
         mbar_expect_tx(bar_lut, (uint32_t)a.nseg * kLutBytesS);
         for (int sgm = 0; sgm < a.nseg; ++sgm) {
@@ -228,7 +208,6 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
     }
     // x may be the previous kernel's output: wait for it (no-op without the launch attribute).
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    MIXFP4_STAMP(1);
     uint32_t seq = 0;       // sequence number of this launch (advanced by the previous launch's last CTA)
     if constexpr (kAR) seq = *reinterpret_cast<volatile uint32_t*>(a.ar.words);
     {   // the whole x (m rows, zero-filled to kpad) once per CTA
@@ -270,7 +249,6 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
     cp_async_wait<0>();
     __syncthreads();                     // x and the stored tables; also: the table barrier is initialised
     if (bulk && !wait_chunk(bar_lut, 0, a.wait_ns) && a.status) atomicCAS(a.status, 0, 299);
-    MIXFP4_STAMP(2);
 
     // Outputs.  kAR: every value goes as a packet into every rank's buffer (this rank's included)
     // and is added up at the end; else it is stored.
@@ -413,9 +391,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
         const uint64_t t0 = gemv_timer_ns(), grace = a.wait_ns < 1000000ull ? a.wait_ns : 1000000ull;
         while (gemv_timer_ns() - t0 < grace) {}      // a last (bounded) chance for copies in flight to land
     }
-    if (warp != 0) MIXFP4_STAMP(3);
     __syncthreads();
-    if (warp == 0) MIXFP4_STAMP(3);
 
     // Row tiles cut by run boundaries: the warp whose run holds the end of such a tile adds the
     // partial sums of the runs before it (ascending K) and its own head piece.
@@ -430,7 +406,6 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
         }
     }
 
-    if (warp != 0) MIXFP4_STAMP(1);      // (profiling builds: end of the last warp)
     if constexpr (kAR) {
         // Every output of this CTA's tiles: wait (bounded) for the packet of each rank and add them
         // in rank order, so that every rank ends with the same bits.
@@ -505,11 +480,6 @@ int device_info(DeviceInfo* out) {
     return MIXFP4_OK;
 }
 
-#ifdef MIXFP4_TRACE
-static __device__ unsigned long long g_trace[64 * 160 * 16];
-std::atomic<unsigned> g_trace_launch{0};
-#endif
-
 constexpr size_t kSmemLimit = 227 * 1024;
 
 template <int kWarps, int kDepth, bool kAR, int kNT, int kLutRep>
@@ -549,10 +519,6 @@ int dispatch_stream(const GemvStreamArgs& a, int sms, int flags, cudaStream_t st
             return rc;
         }
     }
-#ifdef MIXFP4_CFG_WARPS
-    rc = launch_stream<MIXFP4_CFG_WARPS, MIXFP4_CFG_DEPTH, kAR, 1, 8>(a, sms, flags, st);
-    if (rc != MIXFP4_E_SHAPE) return rc;
-#endif
     rc = launch_stream<24, 4, kAR, 1, 8>(a, sms, flags, st);
     if (rc == MIXFP4_E_SHAPE) rc = launch_stream<24, 3, kAR, 1, 8>(a, sms, flags, st);
     if (rc == MIXFP4_E_SHAPE) rc = launch_stream<24, 3, kAR, 1, 4>(a, sms, flags, st);
@@ -595,13 +561,6 @@ int gemv_stream(const void* x, int64_t m, int64_t ldx, int64_t k, const mixfp4_g
     DeviceInfo info;
     if (const int rc = device_info(&info)) return rc;
     g.status = info.status;
-#ifdef MIXFP4_TRACE
-    {
-        void* tp = nullptr;
-        MIXFP4_CUDA_CHECK(cudaGetSymbolAddress(&tp, g_trace));
-        g.trace = static_cast<unsigned long long*>(tp) + (size_t)(g_trace_launch.fetch_add(1) % 64) * 160 * 16;
-    }
-#endif
     if (comm) {
         const int rc = comm_view(comm, &g.ar.rank, &g.ar.world, &g.ar.slot_packets, &g.ar.recv, g.ar.peer, &g.ar.words);
         if (rc != MIXFP4_OK) return rc;
@@ -652,13 +611,3 @@ extern "C" int mixfp4_check_status(const int* dev_status, int* value, void* stre
     if (value) *value = v;
     return v == 0 ? MIXFP4_OK : MIXFP4_E_DEVICE_WAIT;
 }
-
-#ifdef MIXFP4_TRACE
-// Profiling build only: copies the time stamps of the last 64 launches to the host and restarts the count.
-extern "C" __attribute__((visibility("default"))) int mixfp4_trace_read(unsigned long long* host_out) {
-    MIXFP4_CUDA_CHECK(cudaDeviceSynchronize());
-    MIXFP4_CUDA_CHECK(cudaMemcpyFromSymbol(host_out, g_trace, sizeof(unsigned long long) * 64 * 160 * 16));
-    g_trace_launch.store(0);
-    return MIXFP4_OK;
-}
-#endif
