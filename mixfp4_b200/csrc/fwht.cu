@@ -130,6 +130,123 @@ __global__ void __launch_bounds__(kThreads) fwht_kernel(const T* __restrict__ x,
     }
 }
 
+// Block size 128 on 16-bit inputs, one rounding at the end, no sign vector: what the prefill GEMM
+// runs in front of itself.  Same stages, same order and the same single-add outputs as fwht_kernel
+// (so the same bits), arranged for fewer instructions: a pair of lanes owns one 128-element block;
+// a lane keeps the four 16-element groups h, h+2, h+4, h+6 (h = lane parity), so strides 1..8 and
+// 32, 64 stay in its registers and only stride 16 crosses to the neighbouring lane (one shuffle
+// per element instead of three).  Strides above 1 and the division run as packed two-element
+// fp32 operations (add/fma .f32x2: each half is the IEEE operation).  The division by sqrt(128)
+// takes the reciprocal form for the whole lane when every value lies inside the range for which
+// that form was swept; a lane holding a zero, a tiny or an infinite value redoes its 64 divisions one by
+// one with div_root (a NaN passes through either form as a NaN).
+__device__ __forceinline__ void butterfly2(float2& a, float2& b) {      // (a, b) <- (a + b, a - b), both halves
+    const float2 sum = __fadd2_rn(a, b);
+    b = __ffma2_rn(b, make_float2(-1.0f, -1.0f), a);
+    a = sum;
+}
+
+constexpr int kFastThreads = 128;
+constexpr int kFastBlocksPerWarp = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(kFastThreads) fwht128_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows,
+                                                               int64_t ldx, int64_t ldy, int64_t blocks_per_row,
+                                                               int64_t total_blocks, float root) {
+    // a kernel launched behind this one with programmatic dependent launch (the prefill GEMM) may set itself
+    // up once every CTA of this grid is under way; it still waits for this grid's end before it reads y
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int lane = threadIdx.x & 31, h = lane & 1;
+    const int64_t warp = (int64_t)blockIdx.x * (kFastThreads / 32) + (threadIdx.x >> 5);
+    const int64_t blk = warp * kFastBlocksPerWarp + (lane >> 1);
+    const bool live = blk < total_blocks;        // dead lanes still take part in the shuffles
+    const int64_t row = live ? blk / blocks_per_row : 0;
+    const int64_t col = live ? (blk - row * blocks_per_row) * 128 : 0;
+    const T* src = x + row * ldx + col;
+    T* dst = y + row * ldy + col;
+
+    float2 v[4][8];                              // [group][pair]: elements 16 * (h + 2 i) + 2 j, + 1
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint4 w[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+        if (live) {
+            w[0] = __ldg(reinterpret_cast<const uint4*>(src + 16 * (h + 2 * i)));
+            w[1] = __ldg(reinterpret_cast<const uint4*>(src + 16 * (h + 2 * i)) + 1);
+        }
+        const T* e = reinterpret_cast<const T*>(w);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float l = Elem<T>::load(e + 2 * j), r = Elem<T>::load(e + 2 * j + 1);
+            v[i][j] = make_float2(__fadd_rn(l, r), __fsub_rn(l, r));       // stride 1
+        }
+#pragma unroll
+        for (int s = 1; s < 8; s <<= 1)          // strides 2, 4, 8: pair j with pair j + s
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (!(j & s)) butterfly2(v[i][j], v[i][j | s]);
+    }
+    // stride 16: the neighbouring lane holds the partner group; the even lane keeps l + r, the odd one l - r
+    const float2 sgn = h ? make_float2(-1.0f, -1.0f) : make_float2(1.0f, 1.0f);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            float2 o;
+            o.x = __shfl_xor_sync(0xffffffffu, v[i][j].x, 1);
+            o.y = __shfl_xor_sync(0xffffffffu, v[i][j].y, 1);
+            v[i][j] = __ffma2_rn(v[i][j], sgn, o);       // v + o, or o - v: one rounding either way
+        }
+    // strides 32 and 64: groups i, i + 1 and i, i + 2
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        butterfly2(v[0][j], v[1][j]);
+        butterfly2(v[2][j], v[3][j]);
+        butterfly2(v[0][j], v[2][j]);
+        butterfly2(v[1][j], v[3][j]);
+    }
+    // division by sqrt(128)
+    const float inv = __frcp_rn(root);
+    const float2 inv2 = make_float2(inv, inv), nroot2 = make_float2(-root, -root);
+    float hi = 0.0f, lo = 3.0e38f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float ax = fabsf(v[i][j].x), ay = fabsf(v[i][j].y);      // |.| folds into the comparisons
+            hi = fmaxf(hi, fmaxf(ax, ay));
+            lo = fminf(lo, fminf(ax, ay));
+        }
+    if (lo >= 7.888609e-31f && hi <= 1.2676506e30f) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float2 t = __fmul2_rn(v[i][j], inv2);
+                const float2 rem = __ffma2_rn(t, nroot2, v[i][j]);
+                v[i][j] = __ffma2_rn(rem, inv2, t);
+            }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                v[i][j] = make_float2(div_root(v[i][j].x, root, inv, false), div_root(v[i][j].y, root, inv, false));
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            T o[16];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                o[2 * j] = Elem<T>::round(v[i][j].x);
+                o[2 * j + 1] = Elem<T>::round(v[i][j].y);
+            }
+            reinterpret_cast<uint4*>(dst + 16 * (h + 2 * i))[0] = reinterpret_cast<const uint4*>(o)[0];
+            reinterpret_cast<uint4*>(dst + 16 * (h + 2 * i))[1] = reinterpret_cast<const uint4*>(o)[1];
+        }
+    }
+}
+
 // Sweep of div_root's reciprocal form against IEEE division: all 2^23 significands of the
 // dividend for both irrational roots.
 __global__ void fwht_selftest_kernel(unsigned long long* mismatches) {
@@ -155,6 +272,17 @@ int launch(const void* x, void* y, int64_t rows, int64_t k, int64_t ldx, int64_t
     if (ctas > 0x7fffffffLL) return MIXFP4_E_SHAPE;
     const bool vec = aligned(x, 16) && aligned(y, 16) && (ldx * sizeof(T)) % 16 == 0 && (ldy * sizeof(T)) % 16 == 0;
     const float root = static_cast<float>(sqrt(static_cast<double>(size)));
+    if constexpr (sizeof(T) == 2) {
+        if (size == 128 && !stagewise && !signs && vec && k % 128 == 0) {
+            const int64_t blocks_per_row = k / 128, total = rows * blocks_per_row;
+            const int64_t per_cta = (kFastThreads / 32) * kFastBlocksPerWarp;
+            const int64_t fast_ctas = (total + per_cta - 1) / per_cta;
+            if (fast_ctas > 0x7fffffffLL) return MIXFP4_E_SHAPE;
+            fwht128_kernel<T><<<(unsigned)fast_ctas, kFastThreads, 0, st>>>(static_cast<const T*>(x), static_cast<T*>(y), rows,
+                                                                           ldx, ldy, blocks_per_row, total, root);
+            return check_launch("fwht128_kernel");
+        }
+    }
     if (stagewise && sizeof(T) == 2)
         fwht_kernel<T, true><<<(unsigned)ctas, kThreads, 0, st>>>(static_cast<const T*>(x), static_cast<T*>(y), rows, k,
                                                                   ldx, ldy, size, root, signs, vec, chunks);

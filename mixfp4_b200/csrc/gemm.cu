@@ -356,6 +356,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0) {
+            // x may come from the kernel launched just before (see launch_gemm's after_producer)
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            asm volatile("fence.proxy.async.global;" ::: "memory");
             int issued = 0;
             for (int kt = 0; kt < num_kt; ++kt) {
                 const int s = kt % kStages;
@@ -756,6 +759,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_pair_kernel(const __grid_con
     if (warp == 0) {
         // ------------------------------------------------- TMA producer of this CTA's x tile
         if (lane == 0) {
+            // x may be written by the kernel launched just before (the rotation pass): with programmatic
+            // dependent launch everything above and the weight side below run under that kernel's tail,
+            // and only the x loads wait for it (a no-op without the launch attribute)
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            asm volatile("fence.proxy.async.global;" ::: "memory");      // ordinary stores of that kernel, read by TMA
             int issued = 0;
             for (int kt = 0; kt < num_kt; ++kt) {
                 const int s = kt % kStages;
@@ -949,8 +957,10 @@ bool encode_code_map(EncodeTiledFn encode, CUtensorMap* map, const GemmArgs& a, 
 int64_t x_staging_bytes(int64_t m, int64_t k) { return m * ((k + 7) / 8 * 8) * 2; }
 constexpr int64_t kAmaxSlotBytes = 256;
 
+// after_producer: the kernel launched just before on this stream wrote xa (and nothing else this kernel
+// reads) and signals its dependents early; this launch may then start under its tail.
 template <int kMT, int kBN, bool kKL>
-int launch_gemm(const void* xa, int64_t lda, const GemmArgs& a, cudaStream_t st) {
+int launch_gemm(const void* xa, int64_t lda, const GemmArgs& a, cudaStream_t st, bool after_producer = false) {
     using C = Cfg<kMT, kBN>;
     EncodeTiledFn encode = encode_tiled_fn();
     if (!encode) return record_error_text("cuTensorMapEncodeTiled is not available from the driver");
@@ -972,7 +982,17 @@ int launch_gemm(const void* xa, int64_t lda, const GemmArgs& a, cudaStream_t st)
     const int splits = (total_kt + a.kt_per_split - 1) / a.kt_per_split;
     const dim3 grid((unsigned)((a.n + C::BN - 1) / C::BN), (unsigned)((a.m + C::BM - 1) / C::BM), (unsigned)splits);
     if (grid.y > 65535) return MIXFP4_E_SHAPE;
-    gemm_kernel<kMT, kBN, kKL><<<grid, kThreads, C::kSmemBytes, st>>>(tmap, tmap_w, a);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = C::kSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = after_producer ? 1 : 0;
+    MIXFP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_kernel<kMT, kBN, kKL>, tmap, tmap_w, a));
     int rc = check_launch("gemm_kernel");
     if (rc == MIXFP4_OK && splits > 1) {
         const int64_t total = a.m * a.n;
@@ -1016,8 +1036,10 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k) {
 }
 int64_t partial_ld(int64_t n) { return (n + 3) / 4 * 4; }
 
+// after_producer: the kernel launched just before on this stream wrote xa (and nothing else this kernel
+// reads) and signals its dependents early; this launch may then start under its tail.
 template <int kMT, bool kKL>
-int launch_gemm_pair(const void* xa, int64_t lda, const GemmArgs& args, cudaStream_t st) {
+int launch_gemm_pair(const void* xa, int64_t lda, const GemmArgs& args, cudaStream_t st, bool after_producer = false) {
     using C = PairCfg<kMT>;
     GemmArgs a = args;
     EncodeTiledFn encode = encode_tiled_fn();
@@ -1053,13 +1075,15 @@ int launch_gemm_pair(const void* xa, int64_t lda, const GemmArgs& args, cudaStre
     cfg.dynamicSmemBytes = C::kSmemBytes;
     cfg.stream = st;
     if (cfg.gridDim.y > 65535) return MIXFP4_E_SHAPE;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = after_producer ? 2 : 1;
     MIXFP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_pair_kernel<kMT, kKL>, tmap, tmap_w, tmap_y, a));
     return check_launch("gemm_pair_kernel");
 }
@@ -1149,18 +1173,19 @@ extern "C" int mixfp4_gemm(const void* x, int64_t m, int64_t ldx, const uint8_t*
     // Pairs of 256-row CTAs unless pairs of 128-row CTAs pad the token rows noticeably less.  With at
     // most 256 tokens a pair's second CTA would hold no rows and still decode: measured 88 us against 51
     // for the single-CTA kernel at M = 17 .. 128 on a 28672 x 4096 weight.
+    const bool dep = rotation_block == 128;              // the rotation pass above is this launch's only producer
     if (m > 256) {
         const int64_t tiles_n = (n + 255) / 256;
         const int64_t rows2 = (m + 511) / 512 * 512, rows1 = (m + 255) / 256 * 256;
         if (rows2 * 100 <= rows1 * 108 && 2 * (rows2 / 512) * tiles_n >= 112)
-            return kl ? launch_gemm_pair<2, true>(xa, lda, a, st) : launch_gemm_pair<2, false>(xa, lda, a, st);
+            return kl ? launch_gemm_pair<2, true>(xa, lda, a, st, dep) : launch_gemm_pair<2, false>(xa, lda, a, st, dep);
         if (2 * (rows1 / 256) * tiles_n >= 112)
-            return kl ? launch_gemm_pair<1, true>(xa, lda, a, st) : launch_gemm_pair<1, false>(xa, lda, a, st);
+            return kl ? launch_gemm_pair<1, true>(xa, lda, a, st, dep) : launch_gemm_pair<1, false>(xa, lda, a, st, dep);
     }
-    if (mt == 1 && bn == 128) return kl ? launch_gemm<1, 128, true>(xa, lda, a, st) : launch_gemm<1, 128, false>(xa, lda, a, st);
-    if (mt == 1 && bn == 256) return kl ? launch_gemm<1, 256, true>(xa, lda, a, st) : launch_gemm<1, 256, false>(xa, lda, a, st);
-    if (mt == 2 && bn == 128) return kl ? launch_gemm<2, 128, true>(xa, lda, a, st) : launch_gemm<2, 128, false>(xa, lda, a, st);
-    return kl ? launch_gemm<2, 256, true>(xa, lda, a, st) : launch_gemm<2, 256, false>(xa, lda, a, st);
+    if (mt == 1 && bn == 128) return kl ? launch_gemm<1, 128, true>(xa, lda, a, st, dep) : launch_gemm<1, 128, false>(xa, lda, a, st, dep);
+    if (mt == 1 && bn == 256) return kl ? launch_gemm<1, 256, true>(xa, lda, a, st, dep) : launch_gemm<1, 256, false>(xa, lda, a, st, dep);
+    if (mt == 2 && bn == 128) return kl ? launch_gemm<2, 128, true>(xa, lda, a, st, dep) : launch_gemm<2, 128, false>(xa, lda, a, st, dep);
+    return kl ? launch_gemm<2, 256, true>(xa, lda, a, st, dep) : launch_gemm<2, 256, false>(xa, lda, a, st, dep);
 }
 
 extern "C" int mixfp4_gemm_a4(const void* x, int64_t m, int64_t ldx, const uint8_t* codes, const uint8_t* scales,

@@ -13,10 +13,10 @@
 // into an FMA, and the 16 squared errors are added in the order the reference's CPU
 // reduction uses (lane j + lane j+8 first, then the eight sums left to right).
 //
-// Work split: one thread owns one 16-element block (two candidates, ~50
-// instructions per element -- the kernel is bound by instruction issue, not by HBM); a warp
-// owns 32 consecutive blocks of one row, so its loads cover 1 KB of contiguous bf16 and
-// its stores 256 B of codes, 32 B of scales and one 32-bit word of format bits.
+// Work split: one thread owns one 16-element block at a time (two candidates, ~35 instructions per
+// element -- the kernel is bound by instruction issue, not by HBM); a warp item is 64 consecutive
+// blocks of one row (a lane takes blocks lane and lane + 32), so a warp's loads cover 2 x 1 KB of
+// contiguous bf16 and its stores 2 x (256 B of codes, 32 B of scales, one word of format bits).
 
 #include <cuda_fp4.h>
 
@@ -84,10 +84,11 @@ struct QuantArgs {
     int64_t rows, k, ldx;
     int64_t groups;       // ceil(k / 16): real blocks per row
     int64_t blocks_pad;   // kpad / 16: stored blocks per row
-    int64_t chunks;       // ceil(blocks_pad / 32): warps per row
+    int64_t chunks;       // ceil(blocks_pad / 64): warp items per row (a lane takes two blocks of an item)
     int mode;
     bool vec_in, vec_out;
     bool in_place;        // dequant aliases x: the input is read with ordinary (coherent) loads
+    bool any_stats;       // one of the four per-block statistics arrays is wanted
     const float* amax;
     uint8_t* codes;
     uint8_t* scales;
@@ -227,6 +228,119 @@ __device__ __forceinline__ void candidate(const float (&ax)[kGroup], const float
     }
 }
 
+// ---- The same two candidates with packed two-element fp32 operations (mul / add / fma .f32x2: each half is
+// the IEEE operation, so every value below has the bits of its one-element counterpart above) and on SIGNED
+// quotients, which is what the reference itself rounds:
+//   * a / b by the reciprocal (div_rcp) on both halves at once, with -b passed in so that the residual is
+//     one fma: q * (-b) + a has the same exact product as (-q) * b + a;
+//   * the FP4 conversion unit takes the signed quotients, so the E2M1 code nibbles come out with their sign
+//     bit, and the sign nibbles of the E0M3 codes are taken from them.  A nibble's sign is (n < 0); on this
+//     path a nonzero 16-bit x never reaches n = 0 (scales are at least 2^-9 and the tensor scale is below
+//     2^10), and x = +-0 gives +0 (the residual form returns +0 for a -0 dividend), so it equals (x < 0);
+//   * E0M3: clamp to +-7.25, then (c + 1.5 * 2^23) - 1.5 * 2^23 is round-half-even for either sign;
+//   * the error term is (d - x)^2 on the signed values (the reference's own expression).
+__device__ __forceinline__ float2 div_rcp2(float2 a, float2 neg_b, float2 r) {
+    const float2 q = __fmul2_rn(a, r);
+    const float2 rem = __ffma2_rn(q, neg_b, a);
+    return __ffma2_rn(rem, r, q);
+}
+// The nudge of e2m1_nudge for a signed pair, without a comparison.  Adding 2^-27 with the value's sign first:
+// at 0.25 and above that is at most a quarter of the spacing and rounds back to the value; between 0.125 and
+// 0.25 it is half the spacing, so values with an odd last bit move up one step -- all of them stay below 0.25
+// except the float just below 0.25, which lands on 0.25 and is then lifted above it by the last-bit nudge
+// like every exact tie (the reference rounds exactly that float up to 0.5); below 0.125 everything stays far
+// below 0.25.  mixfp4_selftest_division sweeps every fp32 magnitude of both signs against e2m1_round.
+__device__ __forceinline__ float2 e2m1_nudge_pair(float2 n) {
+    const float2 c = make_float2(__uint_as_float((__float_as_uint(n.x) & 0x80000000u) | 0x32000000u),
+                                 __uint_as_float((__float_as_uint(n.y) & 0x80000000u) | 0x32000000u));
+    const float2 t = __fadd2_rn(n, c);
+    return make_float2(__uint_as_float(__float_as_uint(t.x) | 1u), __uint_as_float(__float_as_uint(t.y) | 1u));
+}
+template <bool kE0>
+__device__ __forceinline__ void block_scale_fast(float amax_s, uint32_t& scale_byte, float& sc, float& rsc) {
+    float ideal = div_rcp(amax_s, kE0 ? 7.0f : 6.0f, kE0 ? (1.0f / 7.0f) : (1.0f / 6.0f));
+    ideal = fminf(fmaxf(ideal, 0.001953125f), 448.0f);
+    scale_byte = __nv_cvt_float_to_fp8(ideal, __NV_SATFINITE, __NV_E4M3);
+    sc = e4m3_to_float(scale_byte);
+    rsc = __frcp_rn(sc);
+}
+__device__ __forceinline__ float error_sum(const float2 (&sq)[8]) {
+    // pairs (j, j + 8) first, then the eight sums left to right.  One-element adds on purpose: the assembler
+    // was seen to merge a packed multiply with a packed add that consumes it into one fused operation
+    // (different bits), which it never does with the one-element round-to-nearest forms.
+    float acc = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float p0 = __fadd_rn(sq[j].x, sq[j + 4].x), p1 = __fadd_rn(sq[j].y, sq[j + 4].y);
+        acc = j == 0 ? __fadd_rn(p0, p1) : __fadd_rn(__fadd_rn(acc, p0), p1);
+    }
+    return acc;
+}
+// x2[j] = elements (2j, 2j+1) of the block.  d2 / d0: signed dequantized values (kKeep).
+template <bool kPack, bool kKeep>
+__device__ __forceinline__ void candidates_fast(const float2 (&x2)[8], float gs, float rgs, uint32_t& lo2, uint32_t& hi2,
+                                                uint32_t& b2, float& sc2, float& err2, float2 (&d2)[8], uint32_t& lo0,
+                                                uint32_t& hi0, uint32_t& b0, float& sc0, float& err0, float2 (&d0)[8]) {
+    const float2 rgs2 = make_float2(rgs, rgs), ngs2 = make_float2(-gs, -gs), gs2 = make_float2(gs, gs);
+    const float2 neg1 = make_float2(-1.0f, -1.0f);
+    float2 s[8];
+    float amax_s = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        s[j] = div_rcp2(x2[j], ngs2, rgs2);
+        amax_s = fmaxf(amax_s, fmaxf(fabsf(s[j].x), fabsf(s[j].y)));      // |.| folds into the (three-input) maximum
+    }
+    {   // E2M1
+        float rsc;
+        block_scale_fast<false>(amax_s, b2, sc2, rsc);
+        const float2 rsc2 = make_float2(rsc, rsc), nsc2 = make_float2(-sc2, -sc2), scv = make_float2(sc2, sc2);
+        float2 sq[8];
+        uint32_t byte[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float2 n = div_rcp2(s[j], nsc2, rsc2);
+            byte[j] = __nv_cvt_float2_to_fp4x2(e2m1_nudge_pair(n), __NV_E2M1, cudaRoundNearest);
+            const float2 d = __fmul2_rn(__fmul2_rn(e2m1_pair_levels(byte[j]), scv), gs2);
+            if constexpr (kKeep) d2[j] = d;
+            const float2 e = __ffma2_rn(x2[j], neg1, d);
+            sq[j] = __fmul2_rn(e, e);
+        }
+        err2 = error_sum(sq);
+        lo2 = hi2 = 0;
+        if constexpr (kPack) {
+            lo2 = __byte_perm(__byte_perm(byte[0], byte[1], 0x0040), __byte_perm(byte[2], byte[3], 0x0040), 0x5410);
+            hi2 = __byte_perm(__byte_perm(byte[4], byte[5], 0x0040), __byte_perm(byte[6], byte[7], 0x0040), 0x5410);
+        }
+    }
+    {   // E0M3
+        float rsc;
+        block_scale_fast<true>(amax_s, b0, sc0, rsc);
+        const float2 rsc2 = make_float2(rsc, rsc), nsc2 = make_float2(-sc0, -sc0), scv = make_float2(sc0, sc0);
+        const float2 magic = make_float2(12582912.0f, 12582912.0f), nmagic = make_float2(-12582912.0f, -12582912.0f);
+        float2 sq[8];
+        float p4[4] = {0.0f, 0.0f, 0.0f, 0.0f};         // four levels per float, 16^j weights (exact)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float2 n = div_rcp2(s[j], nsc2, rsc2);
+            const float2 c = make_float2(fminf(fmaxf(n.x, -7.25f), 7.25f), fminf(fmaxf(n.y, -7.25f), 7.25f));
+            const float2 q = __fadd2_rn(__fadd2_rn(c, magic), nmagic);
+            if constexpr (kPack)
+                p4[j >> 1] = (j & 1) == 0 ? __fmaf_rn(fabsf(q.y), 16.0f, fabsf(q.x))
+                                          : __fmaf_rn(fabsf(q.y), 4096.0f, __fmaf_rn(fabsf(q.x), 256.0f, p4[j >> 1]));
+            const float2 d = __fmul2_rn(__fmul2_rn(q, scv), gs2);
+            if constexpr (kKeep) d0[j] = d;
+            const float2 e = __ffma2_rn(x2[j], neg1, d);
+            sq[j] = __fmul2_rn(e, e);
+        }
+        err0 = error_sum(sq);
+        lo0 = hi0 = 0;
+        if constexpr (kPack) {
+            lo0 = __byte_perm(__float_as_uint(__fadd_rn(p4[0], 8388608.0f)), __float_as_uint(__fadd_rn(p4[1], 8388608.0f)), 0x5410);
+            hi0 = __byte_perm(__float_as_uint(__fadd_rn(p4[2], 8388608.0f)), __float_as_uint(__fadd_rn(p4[3], 8388608.0f)), 0x5410);
+        }
+    }
+}
+
 // Element-wise codebook rounding (project_quant/codebook.py:12-25 quantize_e2m1, :41-43 quantize_e0m3):
 // y = sign(x) * level(|x|), with the reference's signed zero (a negative x that rounds to zero gives -0,
 // x = +-0 gives +0 because sign(0) = 0).
@@ -309,6 +423,10 @@ __global__ void selftest_division_kernel(unsigned long long* mismatches) {
         const float r = __frcp_rn(b);
         bad += __float_as_uint(div_rcp(a, b, r)) != __float_as_uint(__fdiv_rn(a, b));
         bad += __float_as_uint(div_rcp(a * 0.001f, b * 6.0f, __frcp_rn(b * 6.0f))) != __float_as_uint(__fdiv_rn(a * 0.001f, b * 6.0f));
+        // the packed form, one half positive and one negative
+        const float2 q2 = div_rcp2(make_float2(a, -a * 0.37f), make_float2(-b, -b), make_float2(r, r));
+        bad += __float_as_uint(q2.x) != __float_as_uint(__fdiv_rn(a, b));
+        bad += __float_as_uint(q2.y) != __float_as_uint(__fdiv_rn(-a * 0.37f, b));
     }
     if (bad) atomicAdd(mismatches, bad);
 }
@@ -328,11 +446,19 @@ __global__ void selftest_e2m1_kernel(unsigned long long* mismatches) {
     bad += __float_as_uint(lv.y) != __float_as_uint(q1);
     bad += (byte & 15u) != (e2m1_code_at_22(q0) >> 22);
     bad += (byte >> 4) != (e2m1_code_at_22(q1) >> 22);
+    // the signed, comparison-free nudge of the packed path: first magnitude positive, second negative
+    const uint32_t sb = __nv_cvt_float2_to_fp4x2(e2m1_nudge_pair(make_float2(m0, -m1)), __NV_E2M1, cudaRoundNearest);
+    const float2 sv = e2m1_pair_levels(sb);
+    bad += __float_as_uint(sv.x) != __float_as_uint(q0);
+    bad += __float_as_uint(sv.y) != (__float_as_uint(q1) | 0x80000000u);
+    bad += (sb & 15u) != (e2m1_code_at_22(q0) >> 22);
+    bad += (sb >> 4) != ((e2m1_code_at_22(q1) >> 22) | 8u);
     if (bad) atomicAdd(mismatches, bad);
 }
 
 // kPack: write codes / scales / format bits; kDequant: write the dequantized tensor.  Each warp
-// walks over (row, 32-block chunk) items with the grid's stride.
+// walks over (row, 64-block chunk) items with the grid's stride; a lane takes the blocks lane and
+// lane + 32 of an item, so the index arithmetic of an item is shared by two blocks.
 template <typename T, bool kPack, bool kDequant>
 __global__ void __launch_bounds__(kThreads, 3) quantize_kernel(const QuantArgs a) {
     const int lane = threadIdx.x & 31;
@@ -364,7 +490,9 @@ __global__ void __launch_bounds__(kThreads, 3) quantize_kernel(const QuantArgs a
             chunk -= a.chunks;
             if (++row >= a.rows) break;
         }
-        const int64_t blk = chunk * 32 + lane;         // block index inside the row
+#pragma unroll 1
+      for (int u = 0; u < 2; ++u) {                    // the lane's two blocks of this item, 32 blocks apart
+        const int64_t blk = chunk * 64 + u * 32 + lane;         // block index inside the row
         const bool stored = blk < a.blocks_pad;
         const bool real = blk < a.groups;
 
@@ -393,21 +521,27 @@ __global__ void __launch_bounds__(kThreads, 3) quantize_kernel(const QuantArgs a
                 for (int i = 0; i < kGroup; ++i) x[i] = c0 + i < a.k ? Elem<T>::load(xr + c0 + i) : 0.0f;
             }
 
-            float s[kGroup], ax[kGroup];
-            float amax_s = 0.0f;
             uint32_t lo2, hi2, b2, lo0, hi0, b0;
             float sc2, sc0, err2, err0;
             float d2[kGroup], d0[kGroup];
+            uint32_t sl = 0, sh = 0;                     // sign nibbles of elements 0..7 and 8..15
             if (fast) {
+                float2 x2[8], dd2[8], dd0[8];
 #pragma unroll
-                for (int i = 0; i < kGroup; ++i) {
-                    s[i] = div_exact<true>(x[i], gs, rgs);
-                    ax[i] = fabsf(x[i]);
-                    amax_s = fmaxf(amax_s, fabsf(s[i]));
+                for (int j = 0; j < 8; ++j) x2[j] = make_float2(x[2 * j], x[2 * j + 1]);
+                candidates_fast<kPack, kDequant>(x2, gs, rgs, lo2, hi2, b2, sc2, err2, dd2, lo0, hi0, b0, sc0, err0, dd0);
+                if constexpr (kDequant) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        d2[2 * j] = fabsf(dd2[j].x); d2[2 * j + 1] = fabsf(dd2[j].y);
+                        d0[2 * j] = fabsf(dd0[j].x); d0[2 * j + 1] = fabsf(dd0[j].y);
+                    }
                 }
-                candidate<false, true, kPack, kDequant>(ax, s, amax_s, gs, lo2, hi2, b2, sc2, err2, d2);
-                candidate<true, true, kPack, kDequant>(ax, s, amax_s, gs, lo0, hi0, b0, sc0, err0, d0);
+                sl = lo2 & 0x88888888u;                  // the FP4 unit kept the quotients' signs
+                sh = hi2 & 0x88888888u;
             } else {
+                float s[kGroup], ax[kGroup];
+                float amax_s = 0.0f;
 #pragma unroll
                 for (int i = 0; i < kGroup; ++i) {
                     s[i] = __fdiv_rn(x[i], gs);
@@ -416,25 +550,28 @@ __global__ void __launch_bounds__(kThreads, 3) quantize_kernel(const QuantArgs a
                 }
                 candidate<false, false, kPack, kDequant>(ax, s, amax_s, gs, lo2, hi2, b2, sc2, err2, d2);
                 candidate<true, false, kPack, kDequant>(ax, s, amax_s, gs, lo0, hi0, b0, sc0, err0, d0);
+                if constexpr (kPack) {
+                    // Sign bit of a nibble = (n < 0) = (x < 0): dividing by the positive scales keeps the sign and
+                    // never reaches zero from a nonzero x; x = -0 gives n = -0, which is not below zero.
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        if (x[i] < 0.0f) sl |= 8u << (4 * i);
+                        if (x[i + 8] < 0.0f) sh |= 8u << (4 * i);
+                    }
+                }
             }
             if (a.mode != MIXFP4_MODE_GIVEN)
                 use_e0 = a.mode == MIXFP4_MODE_ORACLE16 ? (err0 < err2) : (a.mode == MIXFP4_MODE_ALL_E0M3);
 
-            const int64_t g = row * a.groups + blk;
-            if (a.e2_err) a.e2_err[g] = err2;
-            if (a.e0_err) a.e0_err[g] = err0;
-            if (a.e2_scale) a.e2_scale[g] = sc2;
-            if (a.e0_scale) a.e0_scale[g] = sc0;
+            if (a.any_stats) {
+                const int64_t g = row * a.groups + blk;
+                if (a.e2_err) a.e2_err[g] = err2;
+                if (a.e0_err) a.e0_err[g] = err0;
+                if (a.e2_scale) a.e2_scale[g] = sc2;
+                if (a.e0_scale) a.e0_scale[g] = sc0;
+            }
 
             if constexpr (kPack) {
-                // Sign bit of a nibble = (n < 0) = (x < 0): dividing by the positive scales keeps the sign and
-                // never reaches zero from a nonzero x; x = -0 gives n = -0, which is not below zero.
-                uint32_t sl = 0, sh = 0;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    if (x[i] < 0.0f) sl |= 8u << (4 * i);
-                    if (x[i + 8] < 0.0f) sh |= 8u << (4 * i);
-                }
                 lo = (use_e0 ? lo0 : lo2) | sl;
                 hi = (use_e0 ? hi0 : hi2) | sh;
                 scale_byte = use_e0 ? b0 : b2;
@@ -468,10 +605,11 @@ __global__ void __launch_bounds__(kThreads, 3) quantize_kernel(const QuantArgs a
                 a.scales[row * ld_scales + blk] = static_cast<uint8_t>(scale_byte);
             }
             const uint32_t bits = __ballot_sync(0xffffffffu, use_e0);
-            const int64_t fmt_col = chunk * 4 + lane;      // lanes 0..3 write one format byte each
+            const int64_t fmt_col = chunk * 8 + u * 4 + lane;      // lanes 0..3 write one format byte each
             if (lane < 4 && fmt_col < a.blocks_pad / 8)
                 a.fmt[row * (a.blocks_pad / 8) + fmt_col] = static_cast<uint8_t>(bits >> (8 * lane));
         }
+      }
     }
 }
 
@@ -719,13 +857,14 @@ int launch_quantize(const void* x, int dtype, int64_t rows, int64_t k, int64_t l
     a.x = x; a.rows = rows; a.k = k; a.ldx = ldx;
     a.groups = (k + kGroup - 1) / kGroup;
     a.blocks_pad = padded_k(k) / kGroup;
-    a.chunks = (a.blocks_pad + 31) / 32;
+    a.chunks = (a.blocks_pad + 63) / 64;
     a.mode = mode;
     a.vec_in = rows_vectorizable(x, ldx, dtype);
     a.vec_out = dequant && rows_vectorizable(dequant, ld_dequant, dtype);
     a.in_place = dequant == x;
     a.amax = amax; a.codes = codes; a.scales = scales; a.fmt = fmt; a.global_scale = global_scale;
     a.e2_err = e2_err; a.e0_err = e0_err; a.e2_scale = e2_scale; a.e0_scale = e0_scale;
+    a.any_stats = e2_err || e0_err || e2_scale || e0_scale;
     a.dequant = dequant; a.ld_dequant = ld_dequant;
     const int64_t warps = rows * a.chunks;
     int64_t ctas = (warps + kWarpsPerCta - 1) / kWarpsPerCta;

@@ -66,3 +66,32 @@ def test_in_place_and_involution():
     assert rot.fwht(x[:, :128].contiguous()).shape == (64, 128)
     with pytest.raises(ValueError, match="power of two"):
         rot.fwht(x[:, :100].contiguous())
+
+
+def test_single_rounding_h128_on_whole_blocks_with_special_values():
+    """K a multiple of 128, 16-bit input, one rounding: the kernel the prefill GEMM runs in front of itself
+    (a pair of lanes per block, packed fp32 operations, reciprocal-form division for a whole lane).  Rows
+    with zeros, negative zeros, constants (every output but one cancels to zero), values far below 2^-100,
+    infinities and NaN take the lane-by-lane division instead and must give the same bits as the oracle."""
+    x = synth.activations(96, 1024, 12, outlier_fraction=0.02).float()
+    x[3] = 0.0
+    x[4] = -0.0
+    x[5] = 1.5
+    x[6, ::2] = 0.0
+    x[7] *= 1e-36
+    x[8, 5] = float("inf")
+    x[9, 130] = float("nan")
+    x[10, :128] = -0.0
+    x[11, 256:384] = 3.0e38
+    xb = x.to(torch.bfloat16)
+    got = rot.apply_transform(xb.cuda(), "H128", rounding="once").cpu().view(torch.int16).numpy().view(np.uint16)
+    with np.errstate(all="ignore"):
+        ref = oracle.f32_to_bf16_bits(oracle.fwht(xb.float().numpy(), 128))
+    nan = np.isnan(oracle.bf16_bits_to_f32(ref))
+    assert np.array_equal(np.isnan(oracle.bf16_bits_to_f32(got)), nan)
+    assert np.array_equal(got[~nan], ref[~nan])
+    # the same through fp16 and against the general kernel (a K tail keeps it off the whole-block kernel)
+    xh = synth.activations(64, 512, 13).to(torch.float16)
+    whole = rot.apply_transform(xh.cuda(), "H128", rounding="once").cpu()
+    tail = rot.apply_transform(torch.cat([xh, xh[:, :16]], dim=1).cuda(), "H128", rounding="once").cpu()
+    assert torch.equal(whole, tail[:, :512])
