@@ -15,8 +15,10 @@
 //     table look-up of decode.cuh into the reference's bf16 weights, multiplied with x from shared
 //     memory; the accumulators stay in registers across the chunks of a row tile;
 //   * a warp whose run covers a whole row tile stores that tile's outputs directly; the partial
-//     head and tail of a run go to shared memory, and after one barrier the warp that holds the
-//     end of a tile adds the partials in warp order (a fixed order: results are deterministic).
+//     head and tail of a run go to shared memory (into the warp's own ring once its last chunk has
+//     been consumed; the head sums wait in registers until then), and after one barrier the warp
+//     that holds the end of a tile adds the partials in warp order (a fixed order: results are
+//     deterministic).
 // Up to three weights that share x run as one launch (their tiles are numbered through); the
 // row-parallel form sends its outputs as packets into the peers' buffers and adds the ranks'
 // partial sums in rank order (comm.cu).  Every wait is bounded and reports through a status word.
@@ -105,15 +107,17 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
     const int g = lane >> 2, t = lane & 3;
     const int m = a.m;
     const int S = static_cast<int>(a.kpad / kChunkK);          // chunks per row tile
-    // shared memory: barriers | rings | tables | x | partial sums
+    // shared memory: barriers | rings (after the main loop: the warps' partial sums) | tables | x
     const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(smem);
     const uint32_t bars = sbase + warp * (kDepth * 8);
     const uint32_t ring = sbase + kBarBytes + warp * (kDepth * kChunkBytes);
     const uint32_t lut_base = sbase + kBarBytes + kWarps * kDepth * kChunkBytes;
     const uint32_t x_base = lut_base + a.nseg * kLutBytesS;
     const uint32_t xres_rs = xres_row_bytes(a.kpad);
-    const uint32_t x_bytes = ((uint32_t)m * xres_rs + 15u) & ~15u;
-    float* pieces = reinterpret_cast<float*>(smem + (x_base - sbase) + x_bytes);   // [warp][head, tail][16 rows][m]
+    // partial sums of warp w: [head, tail][16 rows][m] floats at the start of its ring (at most 2 KB of the
+    // ring's kDepth * 1152 bytes); written only after the warp's last chunk has been consumed
+    constexpr int kPieceStride = kDepth * (int)kChunkBytes / 4;                    // floats from warp to warp
+    float* pieces = reinterpret_cast<float*>(smem + kBarBytes);
 
     // this CTA's row tiles and this warp's run of their chunks
     // (the CTAs with the lowest indices take the odd tiles: under programmatic dependent launch they
@@ -187,7 +191,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
         }
     }
     if (cnt == 0)                        // a warp without chunks adds zeros where the tile sums are collected
-        for (int v = lane; v < kRowsPerCta * m; v += 32) pieces[(size_t)(warp * 2 * kRowsPerCta) * m + v] = 0.0f;
+        for (int v = lane; v < kRowsPerCta * m; v += 32) pieces[(size_t)warp * kPieceStride + v] = 0.0f;
 
     // Without the wide table: entries go through registers, loaded here and stored after the x copies
     // have been issued, so the two latencies overlap.  (entry, copy) pairs: a warp writes 512 contiguous bytes.
@@ -214,7 +218,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
         const uint32_t chunks_per_row = (uint32_t)(a.kpad >> 3), k_lim = (uint32_t)a.k;
         for (int r = 0; r < m; ++r) {
             for (uint32_t c = threadIdx.x; c < chunks_per_row; c += kThreadsS) {
-                const uint32_t dst = x_base + (uint32_t)r * xres_rs + c * 16;
+                const uint32_t dst = x_base + (uint32_t)r * xres_rs + (c ^ ((c >> 2) & 2u)) * 16;     // see xrow_lo below
                 const __nv_bfloat16* src = a.x + (size_t)r * a.ldx + c * 8;
                 if (a.x_vec) {
                     const bool in = c * 8 < k_lim;
@@ -269,11 +273,17 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
     };
 
     bool x_ok[kNT];                                          // this lane's MMA column is a batch row
-    uint32_t xrow_off[kNT];
+    // x in shared memory: rows of kpad bf16 plus 16 bytes, so that consecutive rows start one 16-byte unit
+    // further in the banks, and inside a row unit c sits at c ^ (2 if c & 8): a quarter-warp's 128-bit loads
+    // (two rows, units 4 t + w for t = 0..3) then touch eight different units of the 128-byte bank line.
+    // A lane reads units w = 0, 1 from xrow_lo and w = 2, 3 from xrow_hi (swapped halves for t >= 2).
+    uint32_t xrow_lo[kNT], xrow_hi[kNT];
 #pragma unroll
     for (int nt = 0; nt < kNT; ++nt) {
         x_ok[nt] = g + 8 * nt < m;
-        xrow_off[nt] = x_base + (x_ok[nt] ? (uint32_t)(g + 8 * nt) * xres_rs : 0u) + t * 64;
+        const uint32_t row_off = x_base + (x_ok[nt] ? (uint32_t)(g + 8 * nt) * xres_rs : 0u) + t * 64;
+        xrow_lo[nt] = row_off + (t & 2) * 16;          // units 0, 1 of the lane's four, or 2, 3 swapped in
+        xrow_hi[nt] = row_off - (t & 2) * 16;
     }
     const uint32_t lut_lane = lut_base + (lane & (kLutRep - 1)) * 16;
     float acc[kNT][2][4];                // two independent accumulation chains per column tile
@@ -290,6 +300,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
     Cursor c = make_cursor(wa);
     int issued = cnt < kDepth ? cnt : kDepth, done = 0;
     bool head = true;                    // the sums in the accumulators include this run's first chunk
+    bool head_kept = false;              // the run began with a partial tile: its sums wait in head_v
+    float head_v[kNT][4];
     int comb_n = 0, comb_seg = 0;        // after the barrier: pieces to add to the first (0: nothing to add up)
     uint32_t comb_row0 = 0;
     const float* comb_first = pieces;
@@ -319,7 +331,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
                     decode8_kl(w == 0 ? ch.x : w == 1 ? ch.y : w == 2 ? ch.z : ch.w, th, ph);
 #pragma unroll
                     for (int nt = 0; nt < kNT; ++nt) {
-                        if (x_ok[nt]) xv[nt] = lds128(xrow_off[nt] + xsub + w * 16);   // other lanes keep zeros
+                        if (x_ok[nt]) xv[nt] = lds128((w < 2 ? xrow_lo[nt] : xrow_hi[nt]) + xsub + w * 16);   // other lanes keep zeros
                         mma_bf16(acc[nt][0], pl[0], ph[0], pl[1], ph[1], xv[nt].x, xv[nt].y);
                         mma_bf16(acc[nt][1], pl[2], ph[2], pl[3], ph[3], xv[nt].z, xv[nt].w);
                     }
@@ -343,7 +355,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
         // c2,c3 = (row g+8, same batches)
         const bool whole = sub0 == 0 && piece == S;
         const uint32_t row0 = (uint32_t)(c.tile - seg_first(c.seg)) * kRowsPerCta;
-        float* rw = pieces + (size_t)((warp * 2 + (head ? 0 : 1)) * kRowsPerCta) * m;
+        // a partial tile at the end of the run is the run's last piece: the ring is free by then
+        float* rw = pieces + (size_t)warp * kPieceStride + kRowsPerCta * m;
 #pragma unroll
         for (int nt = 0; nt < kNT; ++nt) {
             const int b0 = 8 * nt + 2 * t;
@@ -352,6 +365,9 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
             if (whole) {
                 if (b0 < m) { emit(c.seg, row0 + g, b0, v0); emit(c.seg, row0 + g + 8, b0, v2); }
                 if (b0 + 1 < m) { emit(c.seg, row0 + g, b0 + 1, v1); emit(c.seg, row0 + g + 8, b0 + 1, v3); }
+            } else if (head) {
+                head_v[nt][0] = v0; head_v[nt][1] = v1; head_v[nt][2] = v2; head_v[nt][3] = v3;
+                head_kept = true;
             } else {
                 if (b0 < m) { rw[g * m + b0] = v0; rw[(g + 8) * m + b0] = v2; }
                 if (b0 + 1 < m) { rw[g * m + b0 + 1] = v1; rw[(g + 8) * m + b0 + 1] = v3; }
@@ -373,8 +389,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
                 comb_row0 = row0;
                 // that run holds the tile as its tail piece unless it starts exactly at the tile; every run
                 // after it lies inside the tile (its head piece; zeros for a run without chunks)
-                comb_first = pieces + (size_t)((wf * 2 + (run_start(wf) < lo ? 1 : 0)) * kRowsPerCta) * m;
-                comb_next = pieces + (size_t)((wf + 1) * 2 * kRowsPerCta) * m;
+                comb_first = pieces + (size_t)wf * kPieceStride + (run_start(wf) < lo ? kRowsPerCta * m : 0);
+                comb_next = pieces + (size_t)(wf + 1) * kPieceStride;
             }
         }
         head = false;
@@ -383,6 +399,15 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
         c.sub = 0;
         ++c.tile;
         if (c.tile == seg_end(c.seg) && c.seg + 1 < a.nseg) ++c.seg;
+    }
+    if (head_kept) {                     // every chunk of the run has been consumed: the ring takes the head sums
+        float* rw = pieces + (size_t)warp * kPieceStride;
+#pragma unroll
+        for (int nt = 0; nt < kNT; ++nt) {
+            const int b0 = 8 * nt + 2 * t;
+            if (b0 < m) { rw[g * m + b0] = head_v[nt][0]; rw[(g + 8) * m + b0] = head_v[nt][2]; }
+            if (b0 + 1 < m) { rw[g * m + b0 + 1] = head_v[nt][1]; rw[(g + 8) * m + b0 + 1] = head_v[nt][3]; }
+        }
     }
     if (!__all_sync(0xffffffffu, ok)) {
         // A chunk did not arrive within the limit (the sums are then wrong; later chunks were not
@@ -396,7 +421,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream_kernel(const GemvS
     // Row tiles cut by run boundaries: the warp whose run holds the end of such a tile adds the
     // partial sums of the runs before it (ascending K) and its own head piece.
     if (comb_n > 0) {
-        const int stride = 2 * kRowsPerCta * m;
+        constexpr int stride = kPieceStride;
         for (int v = lane; v < kRowsPerCta * m; v += 32) {
             const int r = v % kRowsPerCta, b = v / kRowsPerCta;
             float sum = comb_first[r * m + b];
@@ -485,8 +510,8 @@ constexpr size_t kSmemLimit = 227 * 1024;
 template <int kWarps, int kDepth, bool kAR, int kNT, int kLutRep>
 int launch_stream(const GemvStreamArgs& a, int sms, int flags, cudaStream_t st) {
     const size_t smem = ((size_t)(kWarps * kDepth * 8 + 8 + 127) & ~(size_t)127) + (size_t)kWarps * kDepth * kChunkBytes +
-                        (size_t)a.nseg * 256 * 16 * kLutRep + (((size_t)a.m * xres_row_bytes(a.kpad) + 15) & ~(size_t)15) +
-                        (size_t)kWarps * 2 * kRowsPerCta * a.m * 4;
+                        (size_t)a.nseg * 256 * 16 * kLutRep + (((size_t)a.m * xres_row_bytes(a.kpad) + 15) & ~(size_t)15);
+    static_assert(kDepth * kChunkBytes >= 2 * kRowsPerCta * 8 * kNT * 4, "a ring must hold the warp's two partial sums");
     if (smem > kSmemLimit) return MIXFP4_E_SHAPE;
     static unsigned long long configured = 0;          // one per instantiation, one bit per device
     if (const int rc = ensure_dynamic_smem(gemv_stream_kernel<kWarps, kDepth, kAR, kNT, kLutRep>, (int)kSmemLimit, configured))
@@ -514,7 +539,9 @@ int dispatch_stream(const GemvStreamArgs& a, int sms, int flags, cudaStream_t st
         if constexpr (kAR) {
             return MIXFP4_E_SHAPE;                   // the fused all-reduce takes at most 8 rows
         } else {
-            rc = launch_stream<24, 3, false, 2, 1>(a, sms, flags, st);
+            rc = launch_stream<24, 3, false, 2, 4>(a, sms, flags, st);
+            if (rc == MIXFP4_E_SHAPE) rc = launch_stream<24, 3, false, 2, 2>(a, sms, flags, st);
+            if (rc == MIXFP4_E_SHAPE) rc = launch_stream<24, 3, false, 2, 1>(a, sms, flags, st);
             if (rc == MIXFP4_E_SHAPE) rc = launch_stream<16, 3, false, 2, 1>(a, sms, flags, st);
             return rc;
         }
@@ -587,7 +614,7 @@ extern "C" int mixfp4_gemv_x_fits(int64_t m, int64_t k, int count) {
     if (m < 1 || m > 16 || k <= 0 || count < 1 || count > kMaxSeg) return 0;
     // the smallest configuration: 16 warps, rings of 3 chunks, one table copy per weight
     const size_t smem = 512 + (size_t)16 * 3 * kChunkBytes + (size_t)count * 4096 +
-                        (((size_t)m * xres_row_bytes(padded_k(k)) + 15) & ~(size_t)15) + (size_t)16 * 2 * kRowsPerCta * m * 4;
+                        (((size_t)m * xres_row_bytes(padded_k(k)) + 15) & ~(size_t)15);
     return smem <= kSmemLimit ? 1 : 0;
 }
 
