@@ -83,6 +83,13 @@ __device__ __forceinline__ float level_value(uint32_t idx, bool e0m3) {
 
 // fwht.cu: sweep of its reciprocal-form division (called by mixfp4_selftest_division).
 int fwht_selftest_division(unsigned long long* mismatches, cudaStream_t st);
+// fwht.cu: stage-wise rounded H128 of 16-bit rows plus the output's largest magnitude in one pass
+// (MIXFP4_E_UNSUPPORTED unless the rows are whole, 16-byte aligned blocks of 128).
+int fwht128_stagewise_amax(const void* x, void* y, int dtype, int64_t rows, int64_t k, int64_t ldx, int64_t ldy,
+                           float* amax, cudaStream_t st);
+// quantize.cu: the activation fake-quantization with the tensor maximum already in *amax.
+int fake_quantize_with_amax(const void* x, int dtype, int64_t rows, int64_t k, int64_t ldx, int mode, const float* amax,
+                            void* y, int64_t ldy, cudaStream_t st);
 
 // comm.cu: the parts of a communicator the fused GEMV + all-reduce kernel needs (peers: 8 entries).
 int comm_view(const mixfp4_comm* c, int* rank, int* world, int64_t* slot_packets, uint2** recv, uint2** peers,

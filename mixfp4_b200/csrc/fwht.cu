@@ -170,8 +170,8 @@ __global__ void __launch_bounds__(kFastThreads) fwht128_kernel(const T* __restri
     for (int i = 0; i < 4; ++i) {
         uint4 w[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
         if (live) {
-            w[0] = __ldg(reinterpret_cast<const uint4*>(src + 16 * (h + 2 * i)));
-            w[1] = __ldg(reinterpret_cast<const uint4*>(src + 16 * (h + 2 * i)) + 1);
+            w[0] = *reinterpret_cast<const uint4*>(src + 16 * (h + 2 * i));          // (x may alias y: no read-only path)
+            w[1] = *(reinterpret_cast<const uint4*>(src + 16 * (h + 2 * i)) + 1);
         }
         const T* e = reinterpret_cast<const T*>(w);
 #pragma unroll
@@ -247,6 +247,150 @@ __global__ void __launch_bounds__(kFastThreads) fwht128_kernel(const T* __restri
     }
 }
 
+// The same block size on 16-bit inputs with EVERY stage rounded to the input type -- what the reference's
+// activation hook computes on a bf16 tensor (project_quant/rotation.py:51-58 inside modeling.py:662-668) --
+// in packed two-element 16-bit arithmetic.  A stage output is RN16(a +- b); the reference rounds the fp32 sum
+// of two 16-bit values to 16 bits, and with 24 >= 2 * 11 + 2 significand bits that double rounding equals the
+// single one of the packed add / fma.  Layout as in fwht128_kernel (a pair of lanes per block, groups h, h+2,
+// h+4, h+6 per lane), values kept as words of two neighbouring elements: stride 1 pairs the halves of a word
+// ((l, l) + (r, r) * (1, -1) in one fma), strides 2..8 pair words of a group, stride 16 the neighbouring
+// lane's word, strides 32 and 64 the groups.  The final division is the fp32 one of fwht128_kernel, rounded
+// once more to the input type.  amax (optional): the largest output magnitude, for the activation
+// quantizer that follows (one atomic maximum per CTA on the float's bit pattern).
+template <typename T> struct Pair;
+template <> struct Pair<__nv_bfloat16> {
+    using type = __nv_bfloat162;
+    __device__ static type make(float a, float b) { return __floats2bfloat162_rn(a, b); }
+    __device__ static type low2(type v) { return __low2bfloat162(v); }
+    __device__ static type high2(type v) { return __high2bfloat162(v); }
+    __device__ static float2 to_float2(type v) { return __bfloat1622float2(v); }
+};
+template <> struct Pair<__half> {
+    using type = __half2;
+    __device__ static type make(float a, float b) { return __floats2half2_rn(a, b); }
+    __device__ static type low2(type v) { return __low2half2(v); }
+    __device__ static type high2(type v) { return __high2half2(v); }
+    __device__ static float2 to_float2(type v) { return __half22float2(v); }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kFastThreads) fwht128_stagewise_kernel(const T* __restrict__ x, T* __restrict__ y,
+                                                                         int64_t ldx, int64_t ldy, int64_t blocks_per_row,
+                                                                         int64_t total_blocks, float root,
+                                                                         unsigned int* __restrict__ amax) {
+    using P = Pair<T>;
+    using T2 = typename P::type;
+    const int lane = threadIdx.x & 31, h = lane & 1;
+    const int64_t warp = (int64_t)blockIdx.x * (kFastThreads / 32) + (threadIdx.x >> 5);
+    const int64_t blk = warp * kFastBlocksPerWarp + (lane >> 1);
+    const bool live = blk < total_blocks;        // dead lanes still take part in the shuffles
+    const int64_t row = live ? blk / blocks_per_row : 0;
+    const int64_t col = live ? (blk - row * blocks_per_row) * 128 : 0;
+    const T* src = x + row * ldx + col;
+    T* dst = y + row * ldy + col;
+
+    const T2 plus_minus = P::make(1.0f, -1.0f);
+    T2 v[4][8];                                  // [group][word]: elements 16 * (h + 2 i) + 2 j, + 1
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint4 w[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+        if (live) {
+            w[0] = *reinterpret_cast<const uint4*>(src + 16 * (h + 2 * i));          // (x may alias y: no read-only path)
+            w[1] = *(reinterpret_cast<const uint4*>(src + 16 * (h + 2 * i)) + 1);
+        }
+        const T2* e = reinterpret_cast<const T2*>(w);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] = __hfma2(P::high2(e[j]), plus_minus, P::low2(e[j]));   // stride 1
+#pragma unroll
+        for (int s = 1; s < 8; s <<= 1)          // strides 2, 4, 8: word j with word j + s
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (!(j & s)) {
+                    const T2 a = v[i][j], b = v[i][j | s];
+                    v[i][j] = __hadd2(a, b);
+                    v[i][j | s] = __hsub2(a, b);
+                }
+    }
+    // stride 16: the even lane keeps l + r, the odd one l - r
+    const T2 sgn = h ? P::make(-1.0f, -1.0f) : P::make(1.0f, 1.0f);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t mine = *reinterpret_cast<const uint32_t*>(&v[i][j]);
+            const uint32_t other = __shfl_xor_sync(0xffffffffu, mine, 1);
+            v[i][j] = __hfma2(v[i][j], sgn, *reinterpret_cast<const T2*>(&other));
+        }
+    // strides 32 and 64
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        T2 a = v[0][j], b = v[1][j], c = v[2][j], d = v[3][j];
+        const T2 ab = __hadd2(a, b), amb = __hsub2(a, b), cd = __hadd2(c, d), cmd = __hsub2(c, d);
+        v[0][j] = __hadd2(ab, cd);
+        v[2][j] = __hsub2(ab, cd);
+        v[1][j] = __hadd2(amb, cmd);
+        v[3][j] = __hsub2(amb, cmd);
+    }
+    // division by sqrt(128) in fp32, one more rounding to the input type
+    const float inv = __frcp_rn(root);
+    const float2 inv2 = make_float2(inv, inv), nroot2 = make_float2(-root, -root);
+    float2 f[4][8];
+    float hi = 0.0f, lo = 3.0e38f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            f[i][j] = P::to_float2(v[i][j]);
+            const float ax = fabsf(f[i][j].x), ay = fabsf(f[i][j].y);
+            hi = fmaxf(hi, fmaxf(ax, ay));
+            lo = fminf(lo, fminf(ax, ay));
+        }
+    if (lo >= 7.888609e-31f && hi <= 1.2676506e30f) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float2 t = __fmul2_rn(f[i][j], inv2);
+                const float2 rem = __ffma2_rn(t, nroot2, f[i][j]);
+                f[i][j] = __ffma2_rn(rem, inv2, t);
+            }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                f[i][j] = make_float2(div_root(f[i][j].x, root, inv, false), div_root(f[i][j].y, root, inv, false));
+    }
+    float top = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        T2 o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            o[j] = P::make(f[i][j].x, f[i][j].y);
+            const float2 r = P::to_float2(o[j]);
+            top = fmaxf(top, fmaxf(fabsf(r.x), fabsf(r.y)));
+        }
+        if (live) {
+            reinterpret_cast<uint4*>(dst + 16 * (h + 2 * i))[0] = reinterpret_cast<const uint4*>(o)[0];
+            reinterpret_cast<uint4*>(dst + 16 * (h + 2 * i))[1] = reinterpret_cast<const uint4*>(o)[1];
+        }
+    }
+    if (amax) {
+        if (!live) top = 0.0f;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, off));
+        __shared__ float warp_top[kFastThreads / 32];
+        if (lane == 0) warp_top[threadIdx.x >> 5] = top;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+#pragma unroll
+            for (int w = 1; w < kFastThreads / 32; ++w) top = fmaxf(top, warp_top[w]);
+            if (top > 0.0f) atomicMax(amax, __float_as_uint(top));       // non-negative floats order like their bits
+        }
+    }
+}
+
 // Sweep of div_root's reciprocal form against IEEE division: all 2^23 significands of the
 // dividend for both irrational roots.
 __global__ void fwht_selftest_kernel(unsigned long long* mismatches) {
@@ -265,7 +409,7 @@ __global__ void fwht_selftest_kernel(unsigned long long* mismatches) {
 
 template <typename T>
 int launch(const void* x, void* y, int64_t rows, int64_t k, int64_t ldx, int64_t ldy, int size,
-           const float* signs, int stagewise, cudaStream_t st) {
+           const float* signs, int stagewise, cudaStream_t st, unsigned int* amax = nullptr) {
     const int64_t chunks = (k + 32 * kE - 1) / (32 * kE);
     const int64_t warps = rows * chunks;
     const int64_t ctas = (warps + kThreads / 32 - 1) / (kThreads / 32);
@@ -283,6 +427,18 @@ int launch(const void* x, void* y, int64_t rows, int64_t k, int64_t ldx, int64_t
             return check_launch("fwht128_kernel");
         }
     }
+    if constexpr (sizeof(T) == 2) {
+        if (size == 128 && stagewise && !signs && vec && k % 128 == 0) {
+            const int64_t blocks_per_row = k / 128, total = rows * blocks_per_row;
+            const int64_t per_cta = (kFastThreads / 32) * kFastBlocksPerWarp;
+            const int64_t fast_ctas = (total + per_cta - 1) / per_cta;
+            if (fast_ctas > 0x7fffffffLL) return MIXFP4_E_SHAPE;
+            fwht128_stagewise_kernel<T><<<(unsigned)fast_ctas, kFastThreads, 0, st>>>(
+                static_cast<const T*>(x), static_cast<T*>(y), ldx, ldy, blocks_per_row, total, root, amax);
+            return check_launch("fwht128_stagewise_kernel");
+        }
+    }
+    if (amax) return MIXFP4_E_UNSUPPORTED;           // only the kernel above reports the maximum
     if (stagewise && sizeof(T) == 2)
         fwht_kernel<T, true><<<(unsigned)ctas, kThreads, 0, st>>>(static_cast<const T*>(x), static_cast<T*>(y), rows, k,
                                                                   ldx, ldy, size, root, signs, vec, chunks);
@@ -298,6 +454,20 @@ int launch(const void* x, void* y, int64_t rows, int64_t k, int64_t ldx, int64_t
 int fwht_selftest_division(unsigned long long* mismatches, cudaStream_t st) {
     fwht_selftest_kernel<<<(1u << 23) / 256, 256, 0, st>>>(mismatches);
     return check_launch("fwht_selftest_kernel");
+}
+
+// H128 with every stage rounded (the activation hook's arithmetic) plus the largest output magnitude in
+// *amax (zeroed here first), in one pass; MIXFP4_E_UNSUPPORTED when the rows are not whole 16-byte
+// aligned blocks of 128 (the caller then runs the two passes separately).
+int fwht128_stagewise_amax(const void* x, void* y, int dtype, int64_t rows, int64_t k, int64_t ldx, int64_t ldy,
+                           float* amax, cudaStream_t st) {
+    if (dtype != MIXFP4_BF16 && dtype != MIXFP4_F16) return MIXFP4_E_UNSUPPORTED;
+    const bool vec = aligned(x, 16) && aligned(y, 16) && (ldx * 2) % 16 == 0 && (ldy * 2) % 16 == 0;
+    if (!vec || k % 128 != 0) return MIXFP4_E_UNSUPPORTED;
+    MIXFP4_CUDA_CHECK(cudaMemsetAsync(amax, 0, sizeof(float), st));
+    unsigned int* out = reinterpret_cast<unsigned int*>(amax);
+    return dtype == MIXFP4_BF16 ? launch<__nv_bfloat16>(x, y, rows, k, ldx, ldy, 128, nullptr, 1, st, out)
+                                : launch<__half>(x, y, rows, k, ldx, ldy, 128, nullptr, 1, st, out);
 }
 
 }  // namespace mixfp4

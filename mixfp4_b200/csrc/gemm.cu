@@ -1120,11 +1120,12 @@ extern "C" int64_t mixfp4_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k) 
     return bytes + kAmaxSlotBytes;      // last: the activation amax word of mixfp4_gemm_a4
 }
 
-extern "C" int mixfp4_gemm(const void* x, int64_t m, int64_t ldx, const uint8_t* codes, const uint8_t* scales,
-                           const uint8_t* fmt, const float* global_scale, int64_t n, int64_t k, int layout,
-                           const void* lut, int rotation_block, void* y, int out_dtype, int64_t ldy, void* workspace,
-                           int64_t workspace_bytes, int* status, int flags, void* stream) {
-    (void)flags;
+// x_from_previous_kernel: x (16-byte aligned rows) was written by the kernel launched just before on this
+// stream, which signals its dependents early and writes nothing else this call reads.
+static int gemm_run(const void* x, int64_t m, int64_t ldx, const uint8_t* codes, const uint8_t* scales,
+                    const uint8_t* fmt, const float* global_scale, int64_t n, int64_t k, int layout, const void* lut,
+                    int rotation_block, void* y, int out_dtype, int64_t ldy, void* workspace, int64_t workspace_bytes,
+                    int* status, void* stream, bool x_from_previous_kernel) {
     if (const int rc = check_gemm_args(x, m, ldx, codes, scales, fmt, global_scale, n, k, layout, lut, rotation_block, y,
                                        out_dtype, ldy))
         return rc;
@@ -1173,7 +1174,8 @@ extern "C" int mixfp4_gemm(const void* x, int64_t m, int64_t ldx, const uint8_t*
     // Pairs of 256-row CTAs unless pairs of 128-row CTAs pad the token rows noticeably less.  With at
     // most 256 tokens a pair's second CTA would hold no rows and still decode: measured 88 us against 51
     // for the single-CTA kernel at M = 17 .. 128 on a 28672 x 4096 weight.
-    const bool dep = rotation_block == 128;              // the rotation pass above is this launch's only producer
+    // the rotation pass above (or the caller's last kernel) is this launch's only producer
+    const bool dep = rotation_block == 128 || (x_from_previous_kernel && xa == x);
     if (m > 256) {
         const int64_t tiles_n = (n + 255) / 256;
         const int64_t rows2 = (m + 511) / 512 * 512, rows1 = (m + 255) / 256 * 256;
@@ -1186,6 +1188,15 @@ extern "C" int mixfp4_gemm(const void* x, int64_t m, int64_t ldx, const uint8_t*
     if (mt == 1 && bn == 256) return kl ? launch_gemm<1, 256, true>(xa, lda, a, st, dep) : launch_gemm<1, 256, false>(xa, lda, a, st, dep);
     if (mt == 2 && bn == 128) return kl ? launch_gemm<2, 128, true>(xa, lda, a, st, dep) : launch_gemm<2, 128, false>(xa, lda, a, st, dep);
     return kl ? launch_gemm<2, 256, true>(xa, lda, a, st, dep) : launch_gemm<2, 256, false>(xa, lda, a, st, dep);
+}
+
+extern "C" int mixfp4_gemm(const void* x, int64_t m, int64_t ldx, const uint8_t* codes, const uint8_t* scales,
+                           const uint8_t* fmt, const float* global_scale, int64_t n, int64_t k, int layout,
+                           const void* lut, int rotation_block, void* y, int out_dtype, int64_t ldy, void* workspace,
+                           int64_t workspace_bytes, int* status, int flags, void* stream) {
+    (void)flags;
+    return gemm_run(x, m, ldx, codes, scales, fmt, global_scale, n, k, layout, lut, rotation_block, y, out_dtype, ldy,
+                    workspace, workspace_bytes, status, stream, false);
 }
 
 extern "C" int mixfp4_gemm_a4(const void* x, int64_t m, int64_t ldx, const uint8_t* codes, const uint8_t* scales,
@@ -1205,16 +1216,24 @@ extern "C" int mixfp4_gemm_a4(const void* x, int64_t m, int64_t ldx, const uint8
     float* amax = reinterpret_cast<float*>(static_cast<char*>(workspace) + total - kAmaxSlotBytes);
     const void* src = x;
     int64_t lds = ldx;
+    bool have_amax = false;
     if (rotation_block == 128) {
-        const int rc = mixfp4_fwht(x, workspace, MIXFP4_BF16, m, k, ldx, lda, 128, nullptr, 1, stream);
+        // one pass for the rotation and the rotated tensor's maximum where the rows allow it
+        int rc = fwht128_stagewise_amax(x, workspace, MIXFP4_BF16, m, k, ldx, lda, amax, static_cast<cudaStream_t>(stream));
+        have_amax = rc == MIXFP4_OK;
+        if (rc == MIXFP4_E_UNSUPPORTED) rc = mixfp4_fwht(x, workspace, MIXFP4_BF16, m, k, ldx, lda, 128, nullptr, 1, stream);
         if (rc != MIXFP4_OK) return rc;
         src = workspace;
         lds = lda;
     }
-    const int rc = mixfp4_fake_quantize(src, MIXFP4_BF16, m, k, lds, act_mode, amax, workspace, lda, stream);
+    const int rc = have_amax ? fake_quantize_with_amax(src, MIXFP4_BF16, m, k, lds, act_mode, amax, workspace, lda,
+                                                       static_cast<cudaStream_t>(stream))
+                             : mixfp4_fake_quantize(src, MIXFP4_BF16, m, k, lds, act_mode, amax, workspace, lda, stream);
     if (rc != MIXFP4_OK) return rc;
-    return mixfp4_gemm(workspace, m, lda, codes, scales, fmt, global_scale, n, k, layout, lut, 0, y, out_dtype, ldy,
-                       workspace, total - kAmaxSlotBytes, status, flags, stream);
+    (void)flags;
+    // the quantizer's kernel is the only producer of the staged activations and lets its dependents start early
+    return gemm_run(workspace, m, lda, codes, scales, fmt, global_scale, n, k, layout, lut, 0, y, out_dtype, ldy, workspace,
+                    total - kAmaxSlotBytes, status, stream, true);
 }
 
 

@@ -461,6 +461,9 @@ __global__ void selftest_e2m1_kernel(unsigned long long* mismatches) {
 // lane + 32 of an item, so the index arithmetic of an item is shared by two blocks.
 template <typename T, bool kPack, bool kDequant>
 __global__ void __launch_bounds__(kThreads, 3) quantize_kernel(const QuantArgs a) {
+    // a kernel launched behind this one with programmatic dependent launch (the W4A4 GEMM) may set itself up
+    // while this grid runs; it waits for this grid's end before it reads the outputs
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int lane = threadIdx.x & 31;
     const int warp_in_cta = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);   // provably warp-uniform
     const float amax = *a.amax;
@@ -884,6 +887,12 @@ int launch_quantize(const void* x, int dtype, int64_t rows, int64_t k, int64_t l
     return check_launch("quantize_kernel");
 }
 }  // namespace
+
+int fake_quantize_with_amax(const void* x, int dtype, int64_t rows, int64_t k, int64_t ldx, int mode, const float* amax,
+                            void* y, int64_t ldy, cudaStream_t st) {
+    return launch_quantize(x, dtype, rows, k, ldx, mode, amax, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
+                           nullptr, nullptr, y, ldy, st);
+}
 }  // namespace mixfp4
 
 extern "C" int mixfp4_quantize(const void* x, int dtype, int64_t rows, int64_t k, int64_t ldx, int mode,
