@@ -133,9 +133,9 @@ __global__ void __launch_bounds__(kThreads) fwht_kernel(const T* __restrict__ x,
 // Block size 128 on 16-bit inputs, one rounding at the end, no sign vector: what the prefill GEMM
 // runs in front of itself.  Same stages, same order and the same single-add outputs as fwht_kernel
 // (so the same bits), arranged for fewer instructions: a pair of lanes owns one 128-element block;
-// a lane keeps the four 16-element groups h, h+2, h+4, h+6 (h = lane parity), so strides 1..8 and
-// 32, 64 stay in its registers and only stride 16 crosses to the neighbouring lane (one shuffle
-// per element instead of three).  Strides above 1 and the division run as packed two-element
+// a lane keeps the eight 16-byte chunks h, h+2, ..., h+14 of the block (h = lane parity: the pair reads
+// and writes whole 32-byte sectors), so strides 1..4 and 16..64 stay in its registers and only stride 8
+// crosses to the neighbouring lane (one shuffle per element instead of three).  Strides above 1 and the division run as packed two-element
 // fp32 operations (add/fma .f32x2: each half is the IEEE operation).  The division by sqrt(128)
 // takes the reciprocal form for the whole lane when every value lies inside the range for which
 // that form was swept; a lane holding a zero, a tiny or an infinite value redoes its 64 divisions one by
@@ -165,84 +165,79 @@ __global__ void __launch_bounds__(kFastThreads) fwht128_kernel(const T* __restri
     const T* src = x + row * ldx + col;
     T* dst = y + row * ldy + col;
 
-    float2 v[4][8];                              // [group][pair]: elements 16 * (h + 2 i) + 2 j, + 1
+    float2 v[8][4];                              // [chunk c][pair p]: elements 8 * (2 c + h) + 2 p, + 1
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        uint4 w[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-        if (live) {
-            w[0] = *reinterpret_cast<const uint4*>(src + 16 * (h + 2 * i));          // (x may alias y: no read-only path)
-            w[1] = *(reinterpret_cast<const uint4*>(src + 16 * (h + 2 * i)) + 1);
+    for (int c = 0; c < 8; ++c) {
+        uint4 w = make_uint4(0, 0, 0, 0);
+        if (live) w = *reinterpret_cast<const uint4*>(src + 8 * (2 * c + h));      // (x may alias y: no read-only path)
+        const T* e = reinterpret_cast<const T*>(&w);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float l = Elem<T>::load(e + 2 * q), r = Elem<T>::load(e + 2 * q + 1);
+            v[c][q] = make_float2(__fadd_rn(l, r), __fsub_rn(l, r));       // stride 1
         }
-        const T* e = reinterpret_cast<const T*>(w);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const float l = Elem<T>::load(e + 2 * j), r = Elem<T>::load(e + 2 * j + 1);
-            v[i][j] = make_float2(__fadd_rn(l, r), __fsub_rn(l, r));       // stride 1
-        }
-#pragma unroll
-        for (int s = 1; s < 8; s <<= 1)          // strides 2, 4, 8: pair j with pair j + s
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-                if (!(j & s)) butterfly2(v[i][j], v[i][j | s]);
+        butterfly2(v[c][0], v[c][1]);            // stride 2
+        butterfly2(v[c][2], v[c][3]);
+        butterfly2(v[c][0], v[c][2]);            // stride 4
+        butterfly2(v[c][1], v[c][3]);
     }
-    // stride 16: the neighbouring lane holds the partner group; the even lane keeps l + r, the odd one l - r
+    // stride 8: the neighbouring lane holds the partner chunk; the even lane keeps l + r, the odd one l - r
     const float2 sgn = h ? make_float2(-1.0f, -1.0f) : make_float2(1.0f, 1.0f);
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int c = 0; c < 8; ++c)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int q = 0; q < 4; ++q) {
             float2 o;
-            o.x = __shfl_xor_sync(0xffffffffu, v[i][j].x, 1);
-            o.y = __shfl_xor_sync(0xffffffffu, v[i][j].y, 1);
-            v[i][j] = __ffma2_rn(v[i][j], sgn, o);       // v + o, or o - v: one rounding either way
+            o.x = __shfl_xor_sync(0xffffffffu, v[c][q].x, 1);
+            o.y = __shfl_xor_sync(0xffffffffu, v[c][q].y, 1);
+            v[c][q] = __ffma2_rn(v[c][q], sgn, o);       // v + o, or o - v: one rounding either way
         }
-    // strides 32 and 64: groups i, i + 1 and i, i + 2
+    // strides 16, 32, 64: chunks c and c + 1, + 2, + 4
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        butterfly2(v[0][j], v[1][j]);
-        butterfly2(v[2][j], v[3][j]);
-        butterfly2(v[0][j], v[2][j]);
-        butterfly2(v[1][j], v[3][j]);
-    }
+    for (int st = 1; st < 8; st <<= 1)
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+            if (!(c & st))
+#pragma unroll
+                for (int q = 0; q < 4; ++q) butterfly2(v[c][q], v[c | st][q]);
     // division by sqrt(128)
     const float inv = __frcp_rn(root);
     const float2 inv2 = make_float2(inv, inv), nroot2 = make_float2(-root, -root);
     float hi = 0.0f, lo = 3.0e38f;
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < 8; ++i)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < 4; ++j) {
             const float ax = fabsf(v[i][j].x), ay = fabsf(v[i][j].y);      // |.| folds into the comparisons
             hi = fmaxf(hi, fmaxf(ax, ay));
             lo = fminf(lo, fminf(ax, ay));
         }
     if (lo >= 7.888609e-31f && hi <= 1.2676506e30f) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+        for (int i = 0; i < 8; ++i)
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < 4; ++j) {
                 const float2 t = __fmul2_rn(v[i][j], inv2);
                 const float2 rem = __ffma2_rn(t, nroot2, v[i][j]);
                 v[i][j] = __ffma2_rn(rem, inv2, t);
             }
     } else {
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+        for (int i = 0; i < 8; ++i)
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
+            for (int j = 0; j < 4; ++j)
                 v[i][j] = make_float2(div_root(v[i][j].x, root, inv, false), div_root(v[i][j].y, root, inv, false));
     }
     if (live) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            T o[16];
+        for (int c = 0; c < 8; ++c) {
+            T o[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                o[2 * j] = Elem<T>::round(v[i][j].x);
-                o[2 * j + 1] = Elem<T>::round(v[i][j].y);
+            for (int q = 0; q < 4; ++q) {
+                o[2 * q] = Elem<T>::round(v[c][q].x);
+                o[2 * q + 1] = Elem<T>::round(v[c][q].y);
             }
-            reinterpret_cast<uint4*>(dst + 16 * (h + 2 * i))[0] = reinterpret_cast<const uint4*>(o)[0];
-            reinterpret_cast<uint4*>(dst + 16 * (h + 2 * i))[1] = reinterpret_cast<const uint4*>(o)[1];
+            *reinterpret_cast<uint4*>(dst + 8 * (2 * c + h)) = *reinterpret_cast<const uint4*>(o);
         }
     }
 }
@@ -251,10 +246,10 @@ __global__ void __launch_bounds__(kFastThreads) fwht128_kernel(const T* __restri
 // activation hook computes on a bf16 tensor (project_quant/rotation.py:51-58 inside modeling.py:662-668) --
 // in packed two-element 16-bit arithmetic.  A stage output is RN16(a +- b); the reference rounds the fp32 sum
 // of two 16-bit values to 16 bits, and with 24 >= 2 * 11 + 2 significand bits that double rounding equals the
-// single one of the packed add / fma.  Layout as in fwht128_kernel (a pair of lanes per block, groups h, h+2,
-// h+4, h+6 per lane), values kept as words of two neighbouring elements: stride 1 pairs the halves of a word
-// ((l, l) + (r, r) * (1, -1) in one fma), strides 2..8 pair words of a group, stride 16 the neighbouring
-// lane's word, strides 32 and 64 the groups.  The final division is the fp32 one of fwht128_kernel, rounded
+// single one of the packed add / fma.  Layout as in fwht128_kernel (a pair of lanes per block, chunks h, h+2,
+// ... per lane), values kept as words of two neighbouring elements: stride 1 pairs the halves of a word
+// ((l, l) + (r, r) * (1, -1) in one fma), strides 2 and 4 pair words of a chunk, stride 8 the neighbouring
+// lane's word, strides 16 to 64 the chunks.  The final division is the fp32 one of fwht128_kernel, rounded
 // once more to the input type.  amax (optional): the largest output magnitude, for the activation
 // quantizer that follows (one atomic maximum per CTA on the float's bit pattern).
 template <typename T> struct Pair;
@@ -290,56 +285,55 @@ __global__ void __launch_bounds__(kFastThreads) fwht128_stagewise_kernel(const T
     T* dst = y + row * ldy + col;
 
     const T2 plus_minus = P::make(1.0f, -1.0f);
-    T2 v[4][8];                                  // [group][word]: elements 16 * (h + 2 i) + 2 j, + 1
+    T2 v[8][4];                                  // [chunk c][word p]: elements 8 * (2 c + h) + 2 p, + 1
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        uint4 w[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-        if (live) {
-            w[0] = *reinterpret_cast<const uint4*>(src + 16 * (h + 2 * i));          // (x may alias y: no read-only path)
-            w[1] = *(reinterpret_cast<const uint4*>(src + 16 * (h + 2 * i)) + 1);
-        }
-        const T2* e = reinterpret_cast<const T2*>(w);
+    for (int c = 0; c < 8; ++c) {
+        uint4 w = make_uint4(0, 0, 0, 0);
+        if (live) w = *reinterpret_cast<const uint4*>(src + 8 * (2 * c + h));      // (x may alias y: no read-only path)
+        const T2* e = reinterpret_cast<const T2*>(&w);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[i][j] = __hfma2(P::high2(e[j]), plus_minus, P::low2(e[j]));   // stride 1
+        for (int q = 0; q < 4; ++q) v[c][q] = __hfma2(P::high2(e[q]), plus_minus, P::low2(e[q]));   // stride 1
 #pragma unroll
-        for (int s = 1; s < 8; s <<= 1)          // strides 2, 4, 8: word j with word j + s
+        for (int st = 1; st < 4; st <<= 1)       // strides 2, 4: word q with word q + 1, + 2
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-                if (!(j & s)) {
-                    const T2 a = v[i][j], b = v[i][j | s];
-                    v[i][j] = __hadd2(a, b);
-                    v[i][j | s] = __hsub2(a, b);
+            for (int q = 0; q < 4; ++q)
+                if (!(q & st)) {
+                    const T2 a = v[c][q], b = v[c][q | st];
+                    v[c][q] = __hadd2(a, b);
+                    v[c][q | st] = __hsub2(a, b);
                 }
     }
-    // stride 16: the even lane keeps l + r, the odd one l - r
+    // stride 8: the even lane keeps l + r, the odd one l - r
     const T2 sgn = h ? P::make(-1.0f, -1.0f) : P::make(1.0f, 1.0f);
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int c = 0; c < 8; ++c)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const uint32_t mine = *reinterpret_cast<const uint32_t*>(&v[i][j]);
+        for (int q = 0; q < 4; ++q) {
+            const uint32_t mine = *reinterpret_cast<const uint32_t*>(&v[c][q]);
             const uint32_t other = __shfl_xor_sync(0xffffffffu, mine, 1);
-            v[i][j] = __hfma2(v[i][j], sgn, *reinterpret_cast<const T2*>(&other));
+            v[c][q] = __hfma2(v[c][q], sgn, *reinterpret_cast<const T2*>(&other));
         }
-    // strides 32 and 64
+    // strides 16, 32, 64: chunks c and c + 1, + 2, + 4
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        T2 a = v[0][j], b = v[1][j], c = v[2][j], d = v[3][j];
-        const T2 ab = __hadd2(a, b), amb = __hsub2(a, b), cd = __hadd2(c, d), cmd = __hsub2(c, d);
-        v[0][j] = __hadd2(ab, cd);
-        v[2][j] = __hsub2(ab, cd);
-        v[1][j] = __hadd2(amb, cmd);
-        v[3][j] = __hsub2(amb, cmd);
-    }
+    for (int st = 1; st < 8; st <<= 1)
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+            if (!(c & st))
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const T2 a = v[c][q], b = v[c | st][q];
+                    v[c][q] = __hadd2(a, b);
+                    v[c | st][q] = __hsub2(a, b);
+                }
     // division by sqrt(128) in fp32, one more rounding to the input type
     const float inv = __frcp_rn(root);
     const float2 inv2 = make_float2(inv, inv), nroot2 = make_float2(-root, -root);
-    float2 f[4][8];
+    float2 f[8][4];
     float hi = 0.0f, lo = 3.0e38f;
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < 8; ++i)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < 4; ++j) {
             f[i][j] = P::to_float2(v[i][j]);
             const float ax = fabsf(f[i][j].x), ay = fabsf(f[i][j].y);
             hi = fmaxf(hi, fmaxf(ax, ay));
@@ -347,34 +341,31 @@ __global__ void __launch_bounds__(kFastThreads) fwht128_stagewise_kernel(const T
         }
     if (lo >= 7.888609e-31f && hi <= 1.2676506e30f) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+        for (int i = 0; i < 8; ++i)
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < 4; ++j) {
                 const float2 t = __fmul2_rn(f[i][j], inv2);
                 const float2 rem = __ffma2_rn(t, nroot2, f[i][j]);
                 f[i][j] = __ffma2_rn(rem, inv2, t);
             }
     } else {
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+        for (int i = 0; i < 8; ++i)
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
+            for (int j = 0; j < 4; ++j)
                 f[i][j] = make_float2(div_root(f[i][j].x, root, inv, false), div_root(f[i][j].y, root, inv, false));
     }
     float top = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        T2 o[8];
+    for (int c = 0; c < 8; ++c) {
+        T2 o[4];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            o[j] = P::make(f[i][j].x, f[i][j].y);
-            const float2 r = P::to_float2(o[j]);
+        for (int q = 0; q < 4; ++q) {
+            o[q] = P::make(f[c][q].x, f[c][q].y);
+            const float2 r = P::to_float2(o[q]);
             top = fmaxf(top, fmaxf(fabsf(r.x), fabsf(r.y)));
         }
-        if (live) {
-            reinterpret_cast<uint4*>(dst + 16 * (h + 2 * i))[0] = reinterpret_cast<const uint4*>(o)[0];
-            reinterpret_cast<uint4*>(dst + 16 * (h + 2 * i))[1] = reinterpret_cast<const uint4*>(o)[1];
-        }
+        if (live) *reinterpret_cast<uint4*>(dst + 8 * (2 * c + h)) = *reinterpret_cast<const uint4*>(o);
     }
     if (amax) {
         if (!live) top = 0.0f;
