@@ -291,9 +291,11 @@ MIXFP4_API int mixfp4_set_wait_limit_ns(uint64_t ns);
 MIXFP4_API int mixfp4_check_status(const int* dev_status, int* value, void* stream);
 
 /* Prefill-shape dequant-linear on the tcgen05 tensor cores (any M >= 1, meant for
- * M >= 128).  rotation_block: 0, or 128 to apply the block-Hadamard H128 to x on the
- * fly (the reference's forward-pre-hook, modeling.py:662-668) -- the rotated operand is
- * bf16(FWHT_fp32(x)).  workspace: device scratch of at least
+ * M >= 128).  rotation_block: 0, or 128 to apply the block-Hadamard H128 to x first (the
+ * reference's forward-pre-hook, modeling.py:662-668): a rotation kernel of its own writes
+ * bf16(FWHT_fp32(x)) into the workspace and the GEMM kernel, launched behind it as a programmatic
+ * dependent, reads that (its set-up and weight loads overlap the rotation's tail; the rotation is
+ * not part of the GEMM kernel).  workspace: device scratch of at least
  * mixfp4_gemm_workspace_bytes(m, n, k) bytes: a staging area for x (needed with rotation_block =
  * 128 or an x that TMA cannot address: MIXFP4_E_WORKSPACE without it) followed by room for
  * split-K partial sums (problems with few output tiles and a long K run several CTAs per tile;

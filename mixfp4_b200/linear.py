@@ -74,8 +74,9 @@ def mixfp4_linear(x: torch.Tensor, packed: PackedWeight, *, bias: torch.Tensor |
     or whole-tensor mode run as one ``mixfp4_gemm_a4`` call.
 
     rotate: apply the weight's folded K-transform to x first (default: yes when the packed
-    weight records one).  H128 is fused into the GEMM prologue; the GEMV path and other
-    block sizes run the stand-alone FWHT kernel (fp32 stages, one rounding).
+    weight records one).  For H128 at prefill shapes ``mixfp4_gemm`` runs the rotation as a pass of
+    its own into the workspace and starts the GEMM kernel under that pass's tail; the GEMV path
+    and other block sizes call the FWHT kernel here (fp32 stages, one rounding, in both cases).
     out_dtype: torch.float32 or torch.bfloat16 (default: x.dtype).
     overlap_previous: launch the decode kernel as a programmatic dependent of the previous
     kernel in the stream (its weight prefetch overlaps that kernel's tail).  Only valid when

@@ -7,7 +7,7 @@ fwht :47-58, apply_transform :61-75, hadamard_matrix :78-84, dense_transform_mat
 same errors.  ``apply_transform`` on a bf16/fp16 tensor reproduces the reference
 bit for bit (it rounds to the tensor dtype after every butterfly stage, as eager
 PyTorch does); ``rounding="once"`` keeps fp32 through all stages and rounds once,
-which is what the fused GEMM prologue computes.
+which is what the rotation pass in front of the prefill GEMM computes.
 """
 
 from __future__ import annotations
