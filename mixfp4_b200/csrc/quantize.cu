@@ -39,12 +39,13 @@ __global__ void __launch_bounds__(kThreads) amax_kernel(const T* __restrict__ x,
         constexpr int kPer = 16 / sizeof(T);
         const int64_t words_per_row = k / kPer;
         const int64_t total = rows * words_per_row;
-        // four independent 16-byte loads in flight per thread and trip
+        // eight independent 16-byte loads in flight per thread and trip
+        constexpr int kInFlight = 8;
         const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-        for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += 4 * stride) {
-            uint4 v[4];
+        for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += kInFlight * stride) {
+            uint4 v[kInFlight];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < kInFlight; ++u) {
                 const int64_t iu = i + u * stride;
                 const uint4* src = reinterpret_cast<const uint4*>(x) + iu;         // dense rows: one flat array
                 if (ldx != k) {
@@ -55,7 +56,7 @@ __global__ void __launch_bounds__(kThreads) amax_kernel(const T* __restrict__ x,
             }
             const T* e = reinterpret_cast<const T*>(v);
 #pragma unroll
-            for (int j = 0; j < 4 * kPer; ++j) m = fmaxf(m, fabsf(Elem<T>::load(e + j)));
+            for (int j = 0; j < kInFlight * kPer; ++j) m = fmaxf(m, fabsf(Elem<T>::load(e + j)));
         }
     } else {
         const int64_t total = rows * k;
@@ -460,7 +461,7 @@ __global__ void selftest_e2m1_kernel(unsigned long long* mismatches) {
 // walks over (row, 64-block chunk) items with the grid's stride; a lane takes the blocks lane and
 // lane + 32 of an item, so the index arithmetic of an item is shared by two blocks.
 template <typename T, bool kPack, bool kDequant>
-__global__ void __launch_bounds__(kThreads, 3) quantize_kernel(const QuantArgs a) {
+__global__ void __launch_bounds__(kThreads, (kPack && !kDequant) ? 3 : 2) quantize_kernel(const QuantArgs a) {
     // a kernel launched behind this one with programmatic dependent launch (the W4A4 GEMM) may set itself up
     // while this grid runs; it waits for this grid's end before it reads the outputs
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -797,7 +798,7 @@ extern "C" int mixfp4_amax(const void* x, int dtype, int64_t rows, int64_t k, in
     MIXFP4_CUDA_CHECK(cudaMemsetAsync(amax, 0, sizeof(float), st));
     const bool vec = rows_vectorizable(x, ldx, dtype) && (k * (int64_t)elem_size(dtype)) % 16 == 0;
     const int64_t items = vec ? rows * (k * (int64_t)elem_size(dtype) / 16) : rows * k;
-    int64_t ctas = (items + kThreads * 4 - 1) / (kThreads * 4);
+    int64_t ctas = (items + kThreads * 8 - 1) / (kThreads * 8);
     if (ctas < 1) ctas = 1;
     if (ctas > 148 * 8) ctas = 148 * 8;   // a few waves of grid-stride CTAs
     unsigned int* out = reinterpret_cast<unsigned int*>(amax);
