@@ -156,3 +156,46 @@ def test_c_abi_workspace_contract():
                          packed.fmt.data_ptr(), packed.global_scale.data_ptr(), 128, 256, 0, None, 128, y.data_ptr(),
                          nat.F32, 128, None, 0, None, 0, torch.cuda.current_stream().cuda_stream)
     assert st == -7        # rotation requested without a workspace
+
+
+def test_gemm_cta_pairs_with_h128_rotation_started_early():
+    """A shape the CTA-pair kernel takes, with the rotation pass in front: the GEMM is launched as a programmatic
+    dependent of the rotation kernel (set-up and weight loads under the rotation's tail, x loads after its end).
+    Six calls back to back on different activations, no synchronisation between them: every result equals the
+    allocation-free entry point's (rotation and GEMM as two ordinary launches) bit for bit, and the oracle's
+    within the tolerance."""
+    from mixfp4_b200 import _native as nat
+    m, n, k = 1024, 7168, 1024
+    w = synth.student_t_weight(n, k, 77)
+    wr = mx.apply_transform(w.cuda(), "H128")
+    packed = mx.quantize_packed(wr, rotation="H128")[0].to_stream_layout()
+    lib = nat.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    nbytes = lib.mixfp4_gemm_workspace_bytes(m, n, k)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    xs = [synth.activations(m, k, 90 + i, outlier_fraction=0.01).cuda() for i in range(6)]
+    ys = [torch.empty((m, n), dtype=torch.bfloat16, device="cuda") for _ in xs]
+    args = (packed.codes.data_ptr(), nat.ptr(packed.scales), nat.ptr(packed.fmt), packed.global_scale.data_ptr(), n, k,
+            packed.layout_code, nat.ptr(packed.lut))
+    for x, y in zip(xs, ys):
+        rc = lib.mixfp4_gemm(x.data_ptr(), m, k, *args, 128, y.data_ptr(), nat.BF16, n, ws.data_ptr(), nbytes,
+                             status.data_ptr(), 0, stream)
+        assert rc == 0, lib.mixfp4_status_string(rc)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for i, (x, y) in enumerate(zip(xs, ys)):
+        y_two = torch.empty_like(y)
+        rc = lib.mixfp4_gemm_h128_static(x.data_ptr(), m, k, *args, y_two.data_ptr(), nat.BF16, n, status.data_ptr(), stream)
+        assert rc == 0, lib.mixfp4_status_string(rc)
+        assert torch.equal(y, y_two), f"call {i}"
+    wq = oracle.bf16_bits_to_f32(oracle.dequant(oracle.quantize(wr.float().cpu().numpy()), "bf16"))
+    xr = oracle.bf16_bits_to_f32(oracle.f32_to_bf16_bits(oracle.fwht(xs[0].float().cpu().numpy(), 128)))
+    y32 = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    rc = lib.mixfp4_gemm(xs[0].data_ptr(), m, k, *args, 128, y32.data_ptr(), nat.F32, n, ws.data_ptr(), nbytes,
+                         status.data_ptr(), 0, stream)
+    assert rc == 0, lib.mixfp4_status_string(rc)
+    ystar = oracle.linear(xr, wq)
+    assert oracle.relative_l2(y32.cpu().numpy(), ystar) <= TOL
+    assert np.all(np.abs(ys[0].float().cpu().numpy() - ystar) <= np.abs(ystar) * 2.0 ** -7 + 1e-4 * np.abs(ystar).max())
+    assert int(status.item()) == 0
