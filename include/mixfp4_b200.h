@@ -135,10 +135,19 @@ MIXFP4_API int mixfp4_fake_quantize(const void* x, int dtype, int64_t rows, int6
  * blocks, E0M3 iff the region's summed E0M3 error is smaller (ties keep E2M1), summed in the
  * reference's fp32 order.  e2_err / e0_err: f32 [rows, ceil(k/16)] from mixfp4_quantize; fmt:
  * [rows, kpad/128] format bits out.  Follow with mixfp4_quantize(mode = MIXFP4_MODE_GIVEN) on the
- * same fmt.  region_groups 2 or 4 (k32 / k64 regions); MIXFP4_E_MODE for other widths and for
- * multi-row regions when K has a single region (the reference's sum order differs there). */
+ * same fmt.  region_groups 2 or 4 (k32 / k64 regions), or 1 with region_rows 8 or 16 (n8k16 /
+ * m16k16: the column sums follow the order PyTorch's CPU kernels use on an AVX-512 host, see
+ * quantize.cu); MIXFP4_E_MODE for other widths and for multi-row regions when K has a single
+ * region (the reference's sum order differs there).
+ * mixfp4_select_layer: the "layer" region (one format for the whole tensor, region.py:44-45):
+ * sets every format bit iff the E0M3 errors of all blocks sum to less than the E2M1 errors.  The
+ * sums are taken in double precision in *sums (device double[2] scratch, zeroed by the call); the
+ * reference's fp32 sum over the whole tensor depends on its host's thread count, the decision
+ * does not unless both sums agree to about 1e-7. */
 MIXFP4_API int mixfp4_select_regions(const float* e2_err, const float* e0_err, int64_t rows, int64_t k,
                           int region_rows, int region_groups, uint8_t* fmt, void* stream);
+MIXFP4_API int mixfp4_select_layer(const float* e2_err, const float* e0_err, int64_t rows, int64_t k,
+                          double* sums, uint8_t* fmt, void* stream);
 
 /* Diagnostic: the quantizer divides by block scales with a reciprocal-and-residual sequence
  * instead of a full IEEE division.  This runs the exhaustive proof that the two agree (all 2^23

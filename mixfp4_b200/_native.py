@@ -71,6 +71,8 @@ def _declare(h: ctypes.CDLL) -> None:
     h.mixfp4_fake_quantize.argtypes = [p, i32, i64, i64, i64, i32, p, p, i64, p]
     h.mixfp4_select_regions.restype = i32
     h.mixfp4_select_regions.argtypes = [p, p, i64, i64, i32, i32, p, p]
+    h.mixfp4_select_layer.restype = i32
+    h.mixfp4_select_layer.argtypes = [p, p, i64, i64, p, p, p]
     h.mixfp4_selftest_division.restype = i32
     h.mixfp4_selftest_division.argtypes = [p, p]
     h.mixfp4_e0_four_over_six.restype = i32
@@ -136,7 +138,7 @@ def _declare(h: ctypes.CDLL) -> None:
 # every symbol include/mixfp4_b200.h declares
 EXPORTED = (
     "mixfp4_abi_version", "mixfp4_status_string", "mixfp4_last_cuda_error", "mixfp4_padded_k",
-    "mixfp4_amax", "mixfp4_quantize", "mixfp4_fake_quantize", "mixfp4_select_regions", "mixfp4_selftest_division", "mixfp4_round_codebook", "mixfp4_e0_four_over_six", "mixfp4_dequant", "mixfp4_repack", "mixfp4_decode_table", "mixfp4_decode_table_wide", "mixfp4_fwht",
+    "mixfp4_amax", "mixfp4_quantize", "mixfp4_fake_quantize", "mixfp4_select_regions", "mixfp4_select_layer", "mixfp4_selftest_division", "mixfp4_round_codebook", "mixfp4_e0_four_over_six", "mixfp4_dequant", "mixfp4_repack", "mixfp4_decode_table", "mixfp4_decode_table_wide", "mixfp4_fwht",
     "mixfp4_stream_bytes", "mixfp4_repack_stream", "mixfp4_repack_from_stream",
     "mixfp4_gemv", "mixfp4_gemv_x_fits", "mixfp4_gemv_grouped",
     "mixfp4_comm_create", "mixfp4_comm_handle_bytes", "mixfp4_comm_handle", "mixfp4_comm_open",

@@ -819,7 +819,11 @@ extern "C" int mixfp4_amax(const void* x, int dtype, int64_t rows, int64_t k, in
 // aggregate_regions + selector.py:28-33 mse_selection): E0M3 iff the region's summed E0M3 error
 // is smaller.  The fp32 sums follow the reference's CPU reduction order: inside a row the
 // region's blocks left to right, then the rows top to bottom, cells past the tensor's edge
-// counting as zero.  One thread owns one format byte (8 blocks) of one row of regions and
+// counting as zero.  Regions one block wide (n8k16, m16k16: region_groups = 1) follow the
+// reference's reduction of a strided dimension as PyTorch's CPU kernels run it on an AVX-512
+// host: columns inside whole chunks of 32 block columns are added top to bottom, the columns
+// left after the last whole chunk go through four accumulators (row i into accumulator i mod 4)
+// added 0 + 1 + 2 + 3.  One thread owns one format byte (8 blocks) of one row of regions and
 // writes it to every row of the region.
 __global__ void __launch_bounds__(kThreads) select_regions_kernel(const float* __restrict__ e2_err,
                                                                   const float* __restrict__ e0_err, int64_t rows,
@@ -834,15 +838,29 @@ __global__ void __launch_bounds__(kThreads) select_regions_kernel(const float* _
         const int64_t g0 = col * 8 + sub * region_groups;
         if (g0 >= groups) break;
         float sum2 = 0.0f, sum0 = 0.0f;
-        for (int r = 0; r < region_rows; ++r) {
-            float t2 = 0.0f, t0 = 0.0f;
-            for (int g = 0; g < region_groups; ++g) {
-                const bool in = r0 + r < rows && g0 + g < groups;
-                t2 = __fadd_rn(t2, in ? __ldg(e2_err + (r0 + r) * groups + g0 + g) : 0.0f);
-                t0 = __fadd_rn(t0, in ? __ldg(e0_err + (r0 + r) * groups + g0 + g) : 0.0f);
+        if (region_groups == 1 && g0 >= groups / 32 * 32) {
+            float a2[4] = {0.0f, 0.0f, 0.0f, 0.0f}, a0[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            for (int r = 0; r < region_rows && r0 + r < rows; r += 4) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const bool in = r + q < region_rows && r0 + r + q < rows;
+                    a2[q] = __fadd_rn(a2[q], in ? __ldg(e2_err + (r0 + r + q) * groups + g0) : 0.0f);
+                    a0[q] = __fadd_rn(a0[q], in ? __ldg(e0_err + (r0 + r + q) * groups + g0) : 0.0f);
+                }
             }
-            sum2 = __fadd_rn(sum2, t2);
-            sum0 = __fadd_rn(sum0, t0);
+            sum2 = __fadd_rn(__fadd_rn(__fadd_rn(a2[0], a2[1]), a2[2]), a2[3]);
+            sum0 = __fadd_rn(__fadd_rn(__fadd_rn(a0[0], a0[1]), a0[2]), a0[3]);
+        } else {
+            for (int r = 0; r < region_rows; ++r) {
+                float t2 = 0.0f, t0 = 0.0f;
+                for (int g = 0; g < region_groups; ++g) {
+                    const bool in = r0 + r < rows && g0 + g < groups;
+                    t2 = __fadd_rn(t2, in ? __ldg(e2_err + (r0 + r) * groups + g0 + g) : 0.0f);
+                    t0 = __fadd_rn(t0, in ? __ldg(e0_err + (r0 + r) * groups + g0 + g) : 0.0f);
+                }
+                sum2 = __fadd_rn(sum2, t2);
+                sum0 = __fadd_rn(sum0, t0);
+            }
         }
         if (sum0 < sum2) {
             for (int g = 0; g < region_groups; ++g)
@@ -850,6 +868,35 @@ __global__ void __launch_bounds__(kThreads) select_regions_kernel(const float* _
         }
     }
     for (int r = 0; r < region_rows && r0 + r < rows; ++r) fmt[(r0 + r) * fmt_cols + col] = static_cast<uint8_t>(byte);
+}
+
+// "layer" (one format for the whole tensor, project_quant/region.py:44-45): both error sums in double
+// precision (one atomic add per warp), then every format byte set or cleared.  The reference's own fp32
+// sum of all blocks depends on its host's thread count; the decision does not unless the two sums agree
+// to about 1e-7.
+__global__ void __launch_bounds__(kThreads) sum_errors_kernel(const float* __restrict__ e2_err,
+                                                              const float* __restrict__ e0_err, int64_t count,
+                                                              double* __restrict__ sums) {
+    double s2 = 0.0, s0 = 0.0;
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < count; i += (int64_t)gridDim.x * kThreads) {
+        s2 += static_cast<double>(__ldg(e2_err + i));
+        s0 += static_cast<double>(__ldg(e0_err + i));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+        s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+    }
+    if ((threadIdx.x & 31) == 0) {
+        atomicAdd(sums, s2);
+        atomicAdd(sums + 1, s0);
+    }
+}
+__global__ void __launch_bounds__(kThreads) fill_format_kernel(const double* __restrict__ sums, uint8_t* __restrict__ fmt,
+                                                               int64_t bytes) {
+    const uint8_t value = sums[1] < sums[0] ? 0xff : 0x00;
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < bytes; i += (int64_t)gridDim.x * kThreads)
+        fmt[i] = value;
 }
 
 namespace mixfp4 {
@@ -1060,7 +1107,8 @@ extern "C" int mixfp4_select_regions(const float* e2_err, const float* e0_err, i
                                      int region_rows, int region_groups, uint8_t* fmt, void* stream) {
     if (!e2_err || !e0_err || !fmt) return MIXFP4_E_NULL;
     if (rows <= 0 || k <= 0 || region_rows <= 0) return MIXFP4_E_SHAPE;
-    if (region_groups != 2 && region_groups != 4) return MIXFP4_E_MODE;
+    if (region_groups != 1 && region_groups != 2 && region_groups != 4) return MIXFP4_E_MODE;
+    if (region_groups == 1 && region_rows < 2) return MIXFP4_E_MODE;         // 1 x 1 is the per-block mode
     const int64_t groups = (k + 15) / 16;
     // with a single region along K the reference's reduction takes another order (not reproduced)
     if (region_rows > 1 && (groups + region_groups - 1) / region_groups == 1) return MIXFP4_E_MODE;
@@ -1071,4 +1119,22 @@ extern "C" int mixfp4_select_regions(const float* e2_err, const float* e0_err, i
     select_regions_kernel<<<(unsigned)ctas, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
         e2_err, e0_err, rows, groups, fmt_cols, region_rows, region_groups, fmt);
     return check_launch("select_regions_kernel");
+}
+
+extern "C" int mixfp4_select_layer(const float* e2_err, const float* e0_err, int64_t rows, int64_t k, double* sums,
+                                   uint8_t* fmt, void* stream) {
+    if (!e2_err || !e0_err || !sums || !fmt) return MIXFP4_E_NULL;
+    if (rows <= 0 || k <= 0) return MIXFP4_E_SHAPE;
+    if (!aligned(sums, 8)) return MIXFP4_E_ALIGN;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int64_t count = rows * ((k + 15) / 16), bytes = rows * (padded_k(k) / 128);
+    MIXFP4_CUDA_CHECK(cudaMemsetAsync(sums, 0, 2 * sizeof(double), st));
+    int64_t ctas = (count + kThreads * 8 - 1) / (kThreads * 8);
+    if (ctas > 148 * 4) ctas = 148 * 4;
+    sum_errors_kernel<<<(unsigned)ctas, kThreads, 0, st>>>(e2_err, e0_err, count, sums);
+    if (const int rc = check_launch("sum_errors_kernel")) return rc;
+    int64_t fill = (bytes + kThreads - 1) / kThreads;
+    if (fill > 148 * 8) fill = 148 * 8;
+    fill_format_kernel<<<(unsigned)fill, kThreads, 0, st>>>(sums, fmt, bytes);
+    return check_launch("fill_format_kernel");
 }

@@ -31,12 +31,11 @@ TAIL_POLICY = (
 
 _MODE_CODE = {"oracle16": nat.MODE_ORACLE16, "all_e2m1": nat.MODE_ALL_E2M1, "all_e0m3": nat.MODE_ALL_E0M3}
 # coarse format regions (project_quant/region.py:42-70): name -> (rows, K16 blocks) of a region
+# (rows, 0) stands for "layer": one format for the whole tensor
 _WEIGHT_REGIONS = {"k32_row": (1, 2), "k64_row": (1, 4), "n2k64": (2, 4), "n4k64": (4, 4), "n8k64": (8, 4),
-                   "n16k64": (16, 4), "n32k64": (32, 4), "n64k64": (64, 4)}
-_ACTIVATION_REGIONS = {"k64_row": (1, 4), "m4k64": (4, 4), "m8k64": (8, 4), "m16k64": (16, 4), "m32k64": (32, 4)}
-# regions whose fp32 error sum the reference reduces in an order that depends on the host's
-# vector width (16-wide columns, whole-tensor cascade): not reproduced
-_UNSUPPORTED_REGIONS = {"layer", "n8k16", "m16k16"}
+                   "n16k64": (16, 4), "n32k64": (32, 4), "n64k64": (64, 4), "n8k16": (8, 1), "layer": (1, 0)}
+_ACTIVATION_REGIONS = {"k64_row": (1, 4), "m4k64": (4, 4), "m8k64": (8, 4), "m16k64": (16, 4), "m32k64": (32, 4),
+                       "m16k16": (16, 1), "layer": (1, 0)}
 
 
 def region_shape(mode: str, operand_role: str) -> tuple[int, int] | None:
@@ -46,9 +45,6 @@ def region_shape(mode: str, operand_role: str) -> tuple[int, int] | None:
     table = _WEIGHT_REGIONS if operand_role == "weight_b" else _ACTIVATION_REGIONS
     if mode in table:
         return table[mode]
-    if mode in _UNSUPPORTED_REGIONS and (mode != "m16k16" or operand_role == "activation_a") \
-            and (mode != "n8k16" or operand_role == "weight_b"):
-        raise NotImplementedError(f"format_region={mode!r}: this region's error sum order is not reproduced")
     raise ValueError(f"format_region={mode!r} is invalid for {operand_role}")
 
 
@@ -310,7 +306,7 @@ def quantize_packed(x: torch.Tensor, *, mode: str = "oracle16", amax: torch.Tens
     dq = torch.empty((rows, k), dtype=x2.dtype, device=dev) if want_dequant else None
     mode_code = _MODE_CODE[mode] if region is None else nat.MODE_GIVEN
     if region is not None:
-        if region[0] > 1 and -(-groups // region[1]) == 1:
+        if region[1] > 0 and region[0] > 1 and -(-groups // region[1]) == 1:
             raise NotImplementedError("coarse regions over several rows need more than one region along K")
         e2e = stats["e2_errors"] if stats else torch.empty((rows, groups), dtype=torch.float32, device=dev)
         e0e = stats["e0_errors"] if stats else torch.empty((rows, groups), dtype=torch.float32, device=dev)
@@ -320,9 +316,15 @@ def quantize_packed(x: torch.Tensor, *, mode: str = "oracle16", amax: torch.Tens
                 codes.data_ptr(), scales.data_ptr(), fmt.data_ptr(), gs.data_ptr(), e2e.data_ptr(), e0e.data_ptr(),
                 None, None, None, k, nat.stream_ptr(dev))
             nat.check("mixfp4_quantize", st)
-            st = nat.lib().mixfp4_select_regions(e2e.data_ptr(), e0e.data_ptr(), rows, k, region[0], region[1],
-                                                 fmt.data_ptr(), nat.stream_ptr(dev))
-            nat.check("mixfp4_select_regions", st)
+            if region[1] == 0:          # "layer": both error sums of the whole tensor, one decision
+                sums = torch.empty(2, dtype=torch.float64, device=dev)
+                st = nat.lib().mixfp4_select_layer(e2e.data_ptr(), e0e.data_ptr(), rows, k, sums.data_ptr(),
+                                                   fmt.data_ptr(), nat.stream_ptr(dev))
+                nat.check("mixfp4_select_layer", st)
+            else:
+                st = nat.lib().mixfp4_select_regions(e2e.data_ptr(), e0e.data_ptr(), rows, k, region[0], region[1],
+                                                     fmt.data_ptr(), nat.stream_ptr(dev))
+                nat.check("mixfp4_select_regions", st)
     with torch.cuda.device(dev):
         st = nat.lib().mixfp4_quantize(
             x2.data_ptr(), nat.DTYPE_CODE[x2.dtype], rows, k, x2.stride(0), mode_code, amax.data_ptr(),
@@ -595,7 +597,8 @@ def quant_mixfp4_granularity(
     ``x.shape`` / ``x.dtype`` (or a GranularityResult with ``return_stats=True``).
     Supported here: format_region oracle16 / all_e2m1 / all_e0m3 and the coarse regions
     k32_row, k64_row, n2k64 ... n64k64 (weights), m4k64 ... m32k64 (activations) with
-    selector "mse" and scale_rule "standard"; layer / n8k16 / m16k16 regions, the
+    selector "mse" and scale_rule "standard" (n8k16 / m16k16 sum their columns in the order
+    PyTorch's CPU kernels use on an AVX-512 host, "layer" decides on double-precision sums); the
     output-aware selector and the four_over_six rule raise NotImplementedError.
     """
     working = x
@@ -646,12 +649,13 @@ def quant_mixfp4_granularity(
                          margin.median(), oracle_err, selected_err, e2e.sum(), e0e.sum(),
                          packed.global_scale[0]]).tolist()
     e0_count, oracle_e0 = int(small[0]), int(small[1])
+    coarse = region is not None and region[1] > 0          # "layer" reports the whole tensor as its region
     summary: dict[str, Any] = {
         **_tensor_error_metrics(working, dq.reshape(working.shape)),
         "scale_group_size": scale_group_size, "scale_rule": scale_rule, "format_granularity": mode,
-        "format_region_rows": region[0] if region else (1 if mode == "oracle16" else rows),
-        "format_region_k16_groups": region[1] if region else (1 if mode == "oracle16" else packed.groups),
-        "format_region_k_values": 16 * (region[1] if region else (1 if mode == "oracle16" else packed.groups)),
+        "format_region_rows": region[0] if coarse else (1 if mode == "oracle16" else rows),
+        "format_region_k16_groups": region[1] if coarse else (1 if mode == "oracle16" else packed.groups),
+        "format_region_k_values": 16 * (region[1] if coarse else (1 if mode == "oracle16" else packed.groups)),
         "operand_role": operand_role, "selector": "mse", "tail_policy": TAIL_POLICY,
         "tail_padding_values": (-k) % 16, "rows": rows, "N_or_M": rows, "K": k, "numel": numel,
         "num_scale_blocks": blocks, "e0_count": e0_count, "e2_count": blocks - e0_count,

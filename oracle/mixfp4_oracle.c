@@ -215,6 +215,16 @@ int mixfp4_oracle_quantize(const float* x, int64_t rows, int64_t k, int64_t ldx,
  * region's blocks left to right, then the rows top to bottom; cells past the
  * tensor's edge count as zero.  (Checked against the reference for region_groups
  * in {2, 4} and more than one region along K.)
+ * region_groups == 1 (n8k16, m16k16: a column of region_rows blocks): torch's
+ * reduction of a non-contiguous dimension, as PyTorch 2.11 runs it on an AVX-512
+ * host: block columns inside whole chunks of 32 columns are added top to bottom;
+ * the columns left over after the last whole chunk go through four accumulators
+ * (row i into accumulator i mod 4) that are then added 0 + 1 + 2 + 3.  (Checked
+ * against the reference for 8 and 16 rows and 2 to 896 columns, 1 and 8 threads;
+ * a single column takes yet another path and is refused.)
+ * region_groups == 0 ("layer": one format for the whole tensor): the two sums are
+ * taken in double precision; the reference's own fp32 sum of all blocks depends on
+ * the host's thread count, the decision does not unless the sums agree to ~1e-7.
  * Inputs: the per-block candidate errors, nibbles and scales written by
  * mixfp4_oracle_quantize.  Outputs: the packed bytes. */
 int mixfp4_oracle_apply_regions(const float* e2_err, const float* e0_err,
@@ -222,27 +232,49 @@ int mixfp4_oracle_apply_regions(const float* e2_err, const float* e0_err,
                                 const float* e2_scale, const float* e0_scale,
                                 int64_t rows, int64_t k, int region_rows, int region_groups,
                                 uint8_t* codes, uint8_t* scales, uint8_t* fmt) {
-    if (rows <= 0 || k <= 0 || region_rows <= 0 || region_groups <= 0) return -1;
+    if (rows <= 0 || k <= 0 || region_rows <= 0 || region_groups < 0) return -1;
     const int64_t groups = (k + 15) / 16;
     const int64_t kpad = (k + 127) / 128 * 128;
     const int64_t ld_codes = kpad / 2, ld_scales = kpad / 16, ld_fmt = kpad / 128;
+    int layer_e0 = 0, is_layer = 0;
+    if (region_groups == 0) {                       /* "layer" */
+        is_layer = 1;
+        double d2 = 0.0, d0 = 0.0;
+        for (int64_t i = 0; i < rows * groups; ++i) { d2 += e2_err[i]; d0 += e0_err[i]; }
+        layer_e0 = d0 < d2;
+        region_rows = 1;
+        region_groups = 1;
+    } else if (region_groups == 1 && region_rows > 1 && groups < 2) {
+        return -2;
+    }
+    const int64_t whole_chunks = region_groups == 1 ? groups / 32 * 32 : 0;
     memset(codes, 0, (size_t)(rows * ld_codes));
     memset(scales, 0x01, (size_t)(rows * ld_scales));
     memset(fmt, 0, (size_t)(rows * ld_fmt));
     for (int64_t r0 = 0; r0 < rows; r0 += region_rows) {
         for (int64_t g0 = 0; g0 < groups; g0 += region_groups) {
             float sum2 = 0.0f, sum0 = 0.0f;
-            for (int64_t r = r0; r < r0 + region_rows; ++r) {
-                float t2 = 0.0f, t0 = 0.0f;
-                for (int64_t g = g0; g < g0 + region_groups; ++g) {
-                    const int in = r < rows && g < groups;
-                    t2 = t2 + (in ? e2_err[r * groups + g] : 0.0f);
-                    t0 = t0 + (in ? e0_err[r * groups + g] : 0.0f);
+            if (region_groups == 1 && region_rows > 1 && g0 >= whole_chunks) {
+                float a2[4] = {0.0f, 0.0f, 0.0f, 0.0f}, a0[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                for (int64_t r = r0; r < r0 + region_rows && r < rows; ++r) {
+                    a2[(r - r0) & 3] = a2[(r - r0) & 3] + e2_err[r * groups + g0];
+                    a0[(r - r0) & 3] = a0[(r - r0) & 3] + e0_err[r * groups + g0];
                 }
-                sum2 = sum2 + t2;
-                sum0 = sum0 + t0;
+                sum2 = ((a2[0] + a2[1]) + a2[2]) + a2[3];
+                sum0 = ((a0[0] + a0[1]) + a0[2]) + a0[3];
+            } else {
+                for (int64_t r = r0; r < r0 + region_rows; ++r) {
+                    float t2 = 0.0f, t0 = 0.0f;
+                    for (int64_t g = g0; g < g0 + region_groups; ++g) {
+                        const int in = r < rows && g < groups;
+                        t2 = t2 + (in ? e2_err[r * groups + g] : 0.0f);
+                        t0 = t0 + (in ? e0_err[r * groups + g] : 0.0f);
+                    }
+                    sum2 = sum2 + t2;
+                    sum0 = sum0 + t0;
+                }
             }
-            const int use_e0 = sum0 < sum2;
+            const int use_e0 = is_layer ? layer_e0 : sum0 < sum2;
             for (int64_t r = r0; r < r0 + region_rows && r < rows; ++r) {
                 for (int64_t g = g0; g < g0 + region_groups && g < groups; ++g) {
                     const uint8_t* nib = (use_e0 ? e0_nib : e2_nib) + (r * groups + g) * 16;

@@ -159,6 +159,14 @@ def quant_case_list():
         ("reg_130x328_s27_n64k64", s((130, 328), 27), "n64k64", "weight_b"),
         ("reg_2x17x200_s28_act_m8k64", s((2, 17, 200), 28), "m8k64", "activation_a"),
         ("reg_33x256_act_k64row_bf16", synth.activations(33, 256, 3, outlier_fraction=0.02), "k64_row", "activation_a"),
+        # regions one block wide (columns left of / inside / right of the whole 32-column chunks) and "layer"
+        ("reg_64x384_s31_n8k16", s((64, 384), 31), "n8k16", "weight_b"),
+        ("reg_70x1120_s32_n8k16", s((70, 1120), 32), "n8k16", "weight_b"),
+        ("reg_48x512_st_bf16_n8k16", synth.student_t_weight(48, 512, 2), "n8k16", "weight_b"),
+        ("reg_2x17x200_s33_act_m16k16", s((2, 17, 200), 33), "m16k16", "activation_a"),
+        ("reg_40x1104_act_m16k16_bf16", synth.activations(40, 1104, 4, outlier_fraction=0.02), "m16k16", "activation_a"),
+        ("reg_64x256_s34_layer", s((64, 256), 34), "layer", "weight_b"),
+        ("reg_33x200_s35_act_layer", s((33, 200), 35), "layer", "activation_a"),
     ]
     neg_zero = torch.zeros((4, 32))
     neg_zero[:, ::2] = -0.0

@@ -142,10 +142,8 @@ def test_reference_error_conventions():
         mx.quant_mixfp4_granularity(x, format_region="n3k7")
     with pytest.raises(ValueError, match="invalid for"):
         mx.quant_mixfp4_granularity(x, format_region="m8k64")            # an activation region on a weight
-    with pytest.raises(NotImplementedError):
-        mx.quant_mixfp4_granularity(x, format_region="n8k16")            # sum order not reproduced
-    with pytest.raises(NotImplementedError):
-        mx.quant_mixfp4_granularity(x, format_region="layer")
+    with pytest.raises(ValueError, match="invalid for"):
+        mx.quant_mixfp4_granularity(x, format_region="m16k16")           # an activation region on a weight
     with pytest.raises(NotImplementedError):
         mx.quant_mixfp4_granularity(x, scale_rule="four_over_six")
     with pytest.raises(ValueError, match="unknown transform"):
@@ -201,6 +199,9 @@ def test_activation_modes_follow_the_reference_tables():
         assert quant.fake_quantize_activations(x, mode) is x          # the hook leaves these alone (modeling.py:669)
     with pytest.raises(ValueError):
         quant.fake_quantize_activations(x, "n8k64")                   # a weight region (region.py:42-70)
-    with pytest.raises(NotImplementedError):
-        quant.fake_quantize_activations(x, "m16k16")
+    with pytest.raises(ValueError):
+        quant.fake_quantize_activations(x, "n8k16")                   # a weight region too
     assert quant.region_shape("m8k64", "activation_a") == (8, 4)
+    assert quant.region_shape("m16k16", "activation_a") == (16, 1)
+    assert quant.region_shape("n8k16", "weight_b") == (8, 1)
+    assert quant.region_shape("layer", "weight_b") == quant.region_shape("layer", "activation_a") == (1, 0)

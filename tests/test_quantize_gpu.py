@@ -159,7 +159,7 @@ def test_largest_8b_layer_against_oracle():
     assert err2 <= err1 * 1.05       # re-quantizing a quantized tensor does not drift
 
 
-@pytest.mark.parametrize("mode", ["n8k64", "k64_row", "n64k64"])
+@pytest.mark.parametrize("mode", ["n8k64", "k64_row", "n64k64", "n8k16", "layer"])
 def test_coarse_regions_full_size_against_oracle(mode):
     """q projection shape 4096 x 4096: region choices, bytes and dequantized tensor equal to the
     oracle's; every block of a region carries the region's format; a coarse choice is never
@@ -172,13 +172,28 @@ def test_coarse_regions_full_size_against_oracle(mode):
     assert np.array_equal(packed.scales.cpu().numpy(), ref.scales)
     assert np.array_equal(packed.fmt.cpu().numpy(), ref.fmt)
     assert np.array_equal(raw_bits(dq), oracle.dequant(ref, "bf16"))
-    rr, rg = oracle.REGIONS[mode]
+    rr, rg = oracle.REGIONS[mode] if mode != "layer" else (4096, 256)
     ids = packed.format_ids()
     tiles = ids.reshape(4096 // rr, rr, 256 // rg, rg)
     assert torch.equal(tiles, tiles[:, :1, :, :1].expand_as(tiles))
     e2, e0 = stats["e2_errors"].double(), stats["e0_errors"].double()
     chosen = torch.where(ids.bool(), e0, e2).sum().item()
     assert torch.minimum(e2, e0).sum().item() <= chosen <= min(e2.sum().item(), e0.sum().item()) * (1 + 1e-9)
+
+
+def test_column_regions_on_an_activation_with_ragged_edges_against_oracle():
+    """m16k16 on a [M, K] activation whose rows do not fill the last region and whose block columns leave a
+    remainder after the whole chunks of 32 (K = 1104 + 8: 70 columns, the last block partial): both summation
+    orders of the column sums are in play."""
+    x = synth.activations(200, 1112, 9, outlier_fraction=0.02)
+    packed, dq, _ = mx.quantize_packed(x.cuda(), mode="m16k16", want_dequant=True, region=(16, 1))
+    ref = oracle.quantize(x.float().numpy(), "m16k16")
+    assert np.array_equal(packed.codes.cpu().numpy(), ref.codes)
+    assert np.array_equal(packed.scales.cpu().numpy(), ref.scales)
+    assert np.array_equal(packed.fmt.cpu().numpy(), ref.fmt)
+    assert np.array_equal(raw_bits(dq), oracle.dequant(ref, "bf16"))
+    got = mx.fake_quantize_activations(x.cuda(), "m16k16")
+    assert np.array_equal(raw_bits(got), oracle.dequant(ref, "bf16"))
 
 
 def test_reciprocal_division_is_ieee_exact():
