@@ -574,8 +574,8 @@ def tp70b(dev, rank: int, world: int, layout: str) -> dict:
 def prefill_sweep(dev) -> dict:
     """BASELINE config 3: the Llama-3-8B layer shapes at M = 512, 2048 and 8192 through the tcgen05
     GEMM with the H128 rotation of x applied inside the call (weights rotated before quantization),
-    activations N(0,1) with 1 % of the channels scaled by 30, bf16 out.  TFLOP/s and the fraction of
-    the measured dense bf16 peak."""
+    activations N(0,1) with 1 % of the channels scaled by 30, bf16 out, replayed as CUDA graphs (device
+    time of rotation pass + GEMM).  TFLOP/s and the fraction of the measured dense bf16 peak."""
     import mixfp4_b200 as mx
     from mixfp4_b200 import synth
     try:
@@ -590,17 +590,17 @@ def prefill_sweep(dev) -> dict:
         packed = mx.quantize_packed(mx.apply_transform(w, "H128"), rotation="H128")[0].to_stream_layout()
         for m in (512, 2048, 8192):
             x = synth.activations(m, k, seed=m, outlier_fraction=0.01).to(dev)
-            fn = lambda: mx.mixfp4_linear(x, packed)
-            for _ in range(3):
+            # captured as a CUDA graph: at the small shapes a call's host side (argument marshalling, three
+            # tensor-map encodings, two or three launches; about 40 us) is longer than its kernels
+            reps = 4 if m <= 512 else (2 if m <= 2048 else 1)
+
+            def fn():
+                for _ in range(reps):
+                    mx.mixfp4_linear(x, packed)
+
+            for _ in range(2):
                 fn()
-            torch.cuda.synchronize(dev)
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            for _ in range(6):
-                fn()
-            b.record()
-            torch.cuda.synchronize(dev)
-            t = a.elapsed_time(b) / 6 * 1e-3
+            t = graph_time(fn, dev, 6) / reps
             tf = 2.0 * m * n * k / t / 1e12
             out["%s_%dx%d_m%d" % (name, n, k, m)] = {"tflops": round(tf, 1), "frac_bf16_peak": round(tf / peak_tf, 3)}
         del w, packed
@@ -635,7 +635,12 @@ def secondary_numbers(dev) -> dict:
         state["i"] = (state["i"] + 1) % len(ws)
         mx.quantize_packed(ws[state["i"]])
 
-    t = timeit(quant, 12)
+    def quant_all():
+        for _ in ws:
+            quant()
+
+    # device time of amax + quantize per weight: one CUDA graph over the four weights
+    t = graph_time(quant_all, dev, 6) / len(ws)
     out["quantize_gbs_14336x4096"] = round((2 * n * k + mx.packed_nbytes(n, k)) / t / 1e9, 1)
     out["quantize_ms_14336x4096"] = round(t * 1e3, 4)
 
@@ -673,18 +678,19 @@ def secondary_numbers(dev) -> dict:
         w = (torch.randn((gn, gk), device=dev) * 0.02).to(torch.bfloat16)
         packed = mx.quantize_packed(w)[0].to_kernel_layout()
         x = torch.randn((4096, gk), device=dev).to(torch.bfloat16)
-        t = timeit(lambda: mx.mixfp4_linear(x, packed), 8)
+        # device time (CUDA graph replays; eager calls leave a few microseconds between the kernels)
+        t = graph_time(lambda: mx.mixfp4_linear(x, packed), dev, 8)
         tf = 2.0 * 4096 * gn * gk / t / 1e12
         out["gemm_tflops_m4096_" + name] = round(tf, 1)
         out["gemm_frac_bf16_peak_m4096_" + name] = round(tf / peak_tf, 3)
         if name == "q_4096x4096":
             rot = mx.quantize_packed(mx.apply_transform(w, "H128"), rotation="H128")[0].to_kernel_layout()
-            t = timeit(lambda: mx.mixfp4_linear(x, rot), 8)
+            t = graph_time(lambda: mx.mixfp4_linear(x, rot), dev, 8)
             out["gemm_tflops_m4096_q_4096x4096_h128_rotation"] = round(2.0 * 4096 * gn * gk / t / 1e12, 1)
             # W4A4 in the reference's sense: rotation, activation fake-quantization and GEMM in one call
-            t = timeit(lambda: mx.mixfp4_linear(x, rot, activation_mode="oracle16"), 8)
+            t = graph_time(lambda: mx.mixfp4_linear(x, rot, activation_mode="oracle16"), dev, 8)
             out["gemm_tflops_m4096_q_4096x4096_h128_w4a4"] = round(2.0 * 4096 * gn * gk / t / 1e12, 1)
-            t = timeit(lambda: mx.fake_quantize_activations(x, "oracle16"), 8)
+            t = graph_time(lambda: mx.fake_quantize_activations(x, "oracle16"), dev, 8)
             out["fake_quantize_gbs_4096x4096"] = round(4.0 * 4096 * gk / t / 1e9, 1)     # bf16 in + bf16 out
         del w, packed, x
     out["bf16_peak_tflops"] = peak_tf
@@ -821,10 +827,14 @@ def run_kernel(args):
         else:
             packed = to_layout(mx.quantize_packed(w)[0], args.layout)
         x = torch.randn((m, k), device="cuda").to(torch.bfloat16)
-        t = timed(lambda: mx.mixfp4_linear(x, packed), args.steps)
+        t_eager = timed(lambda: mx.mixfp4_linear(x, packed), args.steps)
+        # device time: the same call replayed as a CUDA graph (a call's host side costs about 40 us, more
+        # than the kernels of a small problem)
+        reps = 4 if 2.0 * m * n * k < 4e11 else 1
+        t = graph_time(lambda: [mx.mixfp4_linear(x, packed) for _ in range(reps)], torch.device("cuda", 0), args.steps) / reps
         print(json.dumps({"kernel": "gemm", "layout": args.layout, "n": n, "k": k, "m": m, "h128": bool(args.rotate),
                           "us": round(t * 1e6, 1), "tflops": round(2.0 * m * n * k / t / 1e12, 1),
-                          "gemm_status": mx.gemm_status()}))
+                          "us_eager_calls": round(t_eager * 1e6, 1), "gemm_status": mx.gemm_status()}))
     else:
         ws = [weight(i) for i in range(max(2, int(400e6 // (2 * n * k))))]
         state = {"i": 0}
