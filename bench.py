@@ -253,11 +253,23 @@ def run_ours(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        # stdout carries the one result line: keep NCCL's version banner (printed to stdout at the VERSION
-        # and INFO levels) out of it unless someone asked for more than that
-        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"
+        # stdout carries the one result line and nothing else: libraries that write to file descriptor 1
+        # (NCCL prints its version banner there) get standard error instead, the result line goes to the
+        # original descriptor
+        sys.stdout.flush()
+        result_fd = os.dup(1)
+        os.dup2(2, 1)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        result_fd = None
+
+    def emit(text: str) -> None:
+        if result_fd is None:
+            print(text, flush=True)
+        else:
+            sys.stdout.flush()
+            os.write(result_fd, (text + "\n").encode())
+
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     m = args.m
@@ -280,7 +292,7 @@ def run_ours(args):
     check = correctness_check(model, world, rank, m, comm, dev)
     if not check["ok"]:
         if rank == 0:
-            print(json.dumps({"metric": METRIC, "error": "correctness check failed", "check": check}), flush=True)
+            emit(json.dumps({"metric": METRIC, "error": "correctness check failed", "check": check}))
         os._exit(3)
 
     side = torch.cuda.Stream(dev)
@@ -390,7 +402,7 @@ def run_ours(args):
             "cpu_baseline": cpu_baseline(m, budget_s=12.0) if world == 1 and not args.no_cpu else None,
             "extra": extra,
         }
-        print(json.dumps(line), flush=True)
+        emit(json.dumps(line))
     if world > 1:
         # Leave without tearing NCCL down: destroying a process group while a CUDA graph that
         # captured its collectives is alive can block forever.  All ranks are past their last
