@@ -539,7 +539,8 @@ int dispatch_stream(const GemvStreamArgs& a, int sms, int flags, cudaStream_t st
         if constexpr (kAR) {
             return MIXFP4_E_SHAPE;                   // the fused all-reduce takes at most 8 rows
         } else {
-            rc = launch_stream<24, 3, false, 2, 4>(a, sms, flags, st);
+            rc = launch_stream<24, 2, false, 2, 8>(a, sms, flags, st);      // rings of two leave room for the eightfold table
+            if (rc == MIXFP4_E_SHAPE) rc = launch_stream<24, 3, false, 2, 4>(a, sms, flags, st);
             if (rc == MIXFP4_E_SHAPE) rc = launch_stream<24, 3, false, 2, 2>(a, sms, flags, st);
             if (rc == MIXFP4_E_SHAPE) rc = launch_stream<24, 3, false, 2, 1>(a, sms, flags, st);
             if (rc == MIXFP4_E_SHAPE) rc = launch_stream<16, 3, false, 2, 1>(a, sms, flags, st);
